@@ -1,0 +1,381 @@
+#!/usr/bin/env python
+"""Benchmark of the composed-format SpMM: GFLOP/s (2 * nnz * N / t) and HBM-roofline fraction.
+
+    python bench.py [--gpus N --steps K --warmup W] [--workload powerlaw|zipf|uniform|skew|blocks]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+    python bench.py --impl reference ...      # SciPy on the host cores, same metric and config
+
+A step is one SpMM C = A B over the whole (row-sharded) matrix with the format and B resident in
+HBM.  The default workload is the power-law graph (2^20 rows, N = 128).  Rank 0 prints one JSON
+line.  Inputs are synthetic and seeded; B plus the format exceed the 126 MB L2, so consecutive
+steps cannot be served from cache.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from liteform_ae_b200 import synth  # noqa: E402
+
+METRIC = "spmm_gflops"
+UNIT = "GFLOP/s"
+
+WORKLOADS = {
+    # name: (description, generator(rows) -> Csr, full rows, N)
+    "zipf": ("config 1: 16384^2 Zipf(1.8) rows, mean 16 nnz/row", lambda m: synth.zipf_rows(M=m), 16384, 32),
+    "powerlaw": ("config 2: 2^20 power-law graph, mean 14 nnz/row, row-normalised", lambda m: synth.power_law_graph(M=m), 1 << 20, 128),
+    "uniform": ("config 3: 4194304^2, exactly 32 nnz/row", lambda m: synth.uniform_rows(M=m), 1 << 22, 64),
+    "skew": ("config 4: 2^20, 64 rows of 100k nnz + log-normal rest", lambda m: synth.skewed_rows(M=m), 1 << 20, 256),
+    "blocks": ("config 5: 2097152^2 dense 8x8 blocks on a band (as element CSR)",
+               lambda m: synth.bsr_to_csr(*synth.banded_blocks(M=m)), 1 << 21, 128),
+}
+
+
+# ------------------------------------------------------------------------------------------------
+def compulsory_bytes(nnz, rows, touched_cols, N):
+    """Index 4 B + value 4 B per stored entry, one row id per matrix row, every touched row of B
+    once, every row of C once."""
+    return nnz * 8 + 4 * (rows + 1) + touched_cols * N * 4 + rows * N * 4
+
+
+def gather_bytes(nnz, rows, N):
+    """Same, but every stored entry fetches its own row of B (no reuse)."""
+    return nnz * 8 + 4 * (rows + 1) + nnz * N * 4 + rows * N * 4
+
+
+def measured_peak_gbs():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons of one GPU through NVML (read-only)."""
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown",
+               0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown", 0x2: "applications_clocks_setting"}
+
+    def __init__(self, index, period=0.02):
+        super().__init__(daemon=True)
+        self.index, self.period = index, period
+        self.samples = []      # (time, sm_mhz, reasons bitmask)
+        self.sm_max = None
+        self.error = None
+        self._halt = threading.Event()
+
+    def run(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            h = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.sm_max = int(pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM))
+            while not self._halt.is_set():
+                try:
+                    reasons = int(pynvml.nvmlDeviceGetCurrentClocksEventReasons(h))
+                except Exception:
+                    reasons = int(pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(h))
+                self.samples.append((time.perf_counter(), int(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)), reasons))
+                time.sleep(self.period)
+        except Exception as e:  # NVML missing: report it, do not fail the measurement
+            self.error = repr(e)
+
+    def stop(self):
+        self._halt.set()
+        self.join(timeout=2)
+
+    def summary(self, t0, t1):
+        inside = [s for s in self.samples if t0 <= s[0] <= t1] or self.samples[-1:]
+        if not inside:
+            return {"sm_mhz": None, "sm_max_mhz": self.sm_max, "reasons": [], "error": self.error or "no samples"}
+        bits = 0
+        for s in inside:
+            bits |= s[2]
+        return {"sm_mhz": statistics.median(s[1] for s in inside), "sm_max_mhz": self.sm_max,
+                "reasons": sorted(v for k, v in self.REASONS.items() if bits & k), "samples": len(inside)}
+
+
+def physical_gpu_index(local_index):
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local_index])
+        except Exception:
+            return local_index
+    return local_index
+
+
+# ------------------------------------------------------------------------------------------------
+def time_cpu(A_csr, B, threads, budget_s, reps_min=1):
+    """Time SciPy's product on a leading row block sized to fit `budget_s`; returns
+    (GFLOP/s, seconds per pass, rows used, nnz used, passes)."""
+    from concurrent.futures import ThreadPoolExecutor
+    M, N = A_csr.shape[0], B.shape[1]
+    probe_rows = max(1, min(M, 1 << 14))
+    t0 = time.perf_counter()
+    _ = A_csr[:probe_rows] @ B
+    per_nnz = (time.perf_counter() - t0) / max(1, A_csr.indptr[probe_rows]) / max(1, min(threads, 4))
+    want_nnz = min(A_csr.nnz, max(1, int(budget_s / max(per_nnz, 1e-12) / max(reps_min, 1))))
+    rows = int(np.searchsorted(A_csr.indptr, want_nnz, side="right"))
+    rows = max(1, min(M, rows))
+    sub = A_csr[:rows]
+    cuts = np.searchsorted(sub.indptr, np.linspace(0, sub.nnz, threads + 1)).astype(np.int64)
+    cuts[0], cuts[-1] = 0, rows
+    parts = [sub[a:b] for a, b in zip(cuts[:-1], cuts[1:]) if b > a]
+    times = []
+    with ThreadPoolExecutor(max(1, threads)) as ex:
+        for _ in range(max(reps_min, 1)):
+            t0 = time.perf_counter()
+            list(ex.map(lambda P: P @ B, parts))
+            times.append(time.perf_counter() - t0)
+    t = statistics.median(times)
+    return 2.0 * sub.nnz * N / t / 1e9, t, rows, int(sub.nnz), len(times)
+
+
+# ------------------------------------------------------------------------------------------------
+def run_reference(args, rank, world):
+    """The reference's CPU product (SciPy, what MTX.dot calls) on the host cores."""
+    if rank != 0:
+        return
+    desc, gen, full_rows, N0 = WORKLOADS[args.workload]
+    rows = args.rows or full_rows
+    N = args.feat or N0
+    csr = gen(rows)
+    A = csr.toscipy()
+    B = synth.dense_features(csr.shape[1], N, args.seed)
+    threads = os.cpu_count() or 1
+    total_budget = 150.0
+    per_step = total_budget / (args.steps + args.warmup)
+    gf0, t_pass, used_rows, used_nnz, _ = time_cpu(A, B, threads, per_step, 1)
+    sub = A[:used_rows]
+    from concurrent.futures import ThreadPoolExecutor
+    cuts = np.searchsorted(sub.indptr, np.linspace(0, sub.nnz, threads + 1)).astype(np.int64)
+    cuts[0], cuts[-1] = 0, used_rows
+    parts = [sub[a:b] for a, b in zip(cuts[:-1], cuts[1:]) if b > a]
+    with ThreadPoolExecutor(threads) as ex:
+        for _ in range(args.warmup):
+            list(ex.map(lambda P: P @ B, parts))
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            list(ex.map(lambda P: P @ B, parts))
+        t = time.perf_counter() - t0
+    value = 2.0 * used_nnz * N * args.steps / t / 1e9
+    sample = f"first {used_rows} of {csr.shape[0]} rows ({used_nnz} of {csr.nnz} nnz) per step, scipy csr @ dense split over {threads} threads"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": t / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic (seeded)",
+        "config": {"workload": f"{args.workload}: {desc}", "rows": csr.shape[0], "nnz": csr.nnz, "N": N},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------
+def run_ours(args, rank, local_rank, world):
+    import torch
+    import torch.distributed as dist
+
+    from liteform_ae_b200 import hyb, width_search
+    from liteform_ae_b200.sharding import my_range
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    desc, gen, full_rows, N0 = WORKLOADS[args.workload]
+    rows = args.rows or full_rows
+    N = args.feat or N0
+    P = args.parts
+
+    t_gen = time.perf_counter()
+    csr = gen(rows)
+    M, K = csr.shape
+    B_host = synth.dense_features(K, N, args.seed)
+    t_gen = time.perf_counter() - t_gen
+
+    d_csr = hyb.DeviceCsr.from_host(csr.indptr, csr.indices, csr.data, csr.shape, dev)
+    torch.cuda.synchronize(dev)
+    t0 = time.perf_counter()
+    stats, hist = hyb.hyb_stats(d_csr, P)
+    widths = width_search.search_from_stats(stats, hist, N, P)
+    torch.cuda.synchronize(dev)
+    t_search = time.perf_counter() - t0
+    cuts = hyb.shard_rows(d_csr, world)
+    r0, r1 = my_range(cuts, rank)
+    t0 = time.perf_counter()
+    fmt = hyb.build_hyb_device(d_csr, widths, row_range=(r0, r1), with_mask=False)
+    torch.cuda.synchronize(dev)
+    t_build = time.perf_counter() - t0
+
+    B = torch.from_numpy(B_host).to(dev)
+    C = torch.empty((r1 - r0, N), dtype=torch.float32, device=dev)
+    launches_per_step = 1 + (1 if (P == 1 and fmt.num_zero_rows > 0) else 0) + (1 if P > 1 else 0)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    sampler = ClockSampler(physical_gpu_index(local_rank))
+    sampler.start()
+    for _ in range(args.warmup):
+        hyb.spmm_hyb(fmt, B, out=C)
+    barrier()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    t_wall0 = time.perf_counter()
+    ev[0].record()
+    for i in range(args.steps):
+        hyb.spmm_hyb(fmt, B, out=C)
+        ev[i + 1].record()
+    barrier()
+    t_wall1 = time.perf_counter()
+    sampler.stop()
+    total_ms = ev[0].elapsed_time(ev[-1])
+    step_ms = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps)]
+    t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms_max = float(t.item())
+    clocks = sampler.summary(t_wall0, t_wall1)
+
+    # ---- end to end: host buffers in, host buffer out, through the host-memory C entry point ----
+    e2e = None
+    try:
+        if args.no_e2e:
+            raise RuntimeError("skipped (--no-e2e)")
+        r_nd, c_nd, _, v_nd = fmt.to_nested_numpy(with_values=True)
+        ell_rows, row_off, slot_off, h_rows, h_cols, h_vals, h_zero = hyb.HybFormat.host_layout(
+            fmt.bucket_widths, r_nd, c_nd, v_nd, M, (r0, r1))
+        del r_nd, c_nd, v_nd
+        pin = lambda a: torch.from_numpy(a).pin_memory().numpy()
+        h_rows, h_cols, h_vals, h_zero, Bp = pin(h_rows), pin(h_cols), pin(h_vals), pin(h_zero), pin(B_host)
+        Cp = torch.empty((r1 - r0, N), dtype=torch.float32).pin_memory().numpy()
+        host_fmt = hyb.HybFormat((M, K), (r0, r1), fmt.bucket_widths, ell_rows, row_off, slot_off,
+                                 None, None, None, None, h_zero)
+        ws = torch.empty(hyb.host_workspace_bytes(host_fmt, N), dtype=torch.uint8, device=dev)
+        e2e_steps = max(3, min(args.steps, 20))
+        for _ in range(2):
+            hyb.spmm_hyb_host((h_rows, h_cols, h_vals, h_zero), host_fmt, Bp, Cp, ws)
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            hyb.spmm_hyb_host((h_rows, h_cols, h_vals, h_zero), host_fmt, Bp, Cp, ws)
+        barrier()
+        te = torch.tensor([(time.perf_counter() - t0) / e2e_steps], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(te, op=dist.ReduceOp.MAX)
+        h2d = h_rows.nbytes + h_cols.nbytes + h_vals.nbytes + h_zero.nbytes + Bp.nbytes
+        d2h = Cp.nbytes
+        e2e = {"value": 2.0 * csr.nnz * N / float(te.item()) / 1e9, "unit": UNIT,
+               "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
+               "ms_per_step": float(te.item()) * 1e3, "steps": e2e_steps,
+               "call": "lf_spmm_hyb_f32_host (pinned host format + B in, C out, per rank)"}
+        check = np.abs(Cp - C.cpu().numpy()).max()
+        e2e["max_abs_diff_vs_resident_run"] = float(check)
+        del ws
+    except Exception as exc:  # keep the device-resident numbers, say what went wrong
+        e2e = {"value": None, "unit": UNIT, "error": repr(exc)}
+
+    if rank != 0:
+        return
+    peak, peak_kind = measured_peak_gbs()
+    my_nnz = int(csr.indptr[r1] - csr.indptr[r0])
+    touched = int(np.unique(csr.indices[csr.indptr[r0]:csr.indptr[r1]]).size)
+    launch_ms = statistics.fmean(step_ms)
+    alg = compulsory_bytes(my_nnz, r1 - r0, touched, N)
+    achieved = alg / (launch_ms * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                "traffic": TRAFFIC_BYTES_PER_LAUNCH.get((args.workload, N, P, world)),
+                "peak_kind": f"of {peak_kind}", "kernel": "spmm_hyb_kernel",
+                "algorithmic_bytes_per_launch": int(alg), "launch_ms": launch_ms,
+                "launch_ms_median": statistics.median(step_ms),
+                "gather_model_bytes_per_launch": int(gather_bytes(my_nnz, r1 - r0, N)),
+                "gather_model_gbs": gather_bytes(my_nnz, r1 - r0, N) / (launch_ms * 1e-3) / 1e9}
+
+    cpu = None
+    if world == 1 and not args.no_cpu:
+        A = csr.toscipy()
+        gf, t_pass, used_rows, used_nnz, passes = time_cpu(A, B_host, 1, 12.0, 2)
+        cpu = {"value": gf, "unit": UNIT, "cores": 1, "kind": "port",
+               "sample": f"scipy csr @ dense (float32), first {used_rows} of {M} rows ({used_nnz} nnz), median of {passes} passes, {t_pass:.2f} s per pass"}
+        threads = os.cpu_count() or 1
+        if threads > 1:
+            gfm, tm, ur, un, ps = time_cpu(A, B_host, threads, 6.0, 2)
+            cpu["all_cores"] = {"value": gfm, "cores": threads, "sample": f"{ur} rows split over {threads} threads, {tm:.2f} s per pass"}
+
+    line = {
+        "metric": METRIC, "value": 2.0 * csr.nnz * N * args.steps / (total_ms_max * 1e-3) / 1e9, "unit": UNIT,
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms_max / args.steps,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic (seeded, numpy default_rng)",
+        "config": {"workload": f"{args.workload}: {desc}", "rows": M, "cols": K, "nnz": csr.nnz, "N": N,
+                   "num_parts": P, "bucket_widths": widths, "sharding": f"rows, nnz-balanced, {world} rank(s), B replicated, C left sharded",
+                   "l2": "inputs exceed L2 (B %.0f MB + format %.0f MB per rank); no flush between steps" % (
+                       B_host.nbytes / 1e6, (fmt.cols.numel() * 8 + fmt.rows.numel() * 4) / 1e6)},
+        "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks,
+        "gpu_launches": launches_per_step * args.steps,
+        "format_build_ms": t_build * 1e3, "width_search_ms": t_search * 1e3, "generate_s": t_gen,
+        "padded_slots": fmt.total_slots, "zero_rows": fmt.num_zero_rows,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# DRAM bytes (read + write) of one spmm_hyb_kernel launch taken from the ncu captures summarised
+# under profiles/; keyed by (workload, N, num_parts, n_gpus).  Absent entries are reported as null.
+TRAFFIC_BYTES_PER_LAUNCH = {}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="powerlaw", choices=sorted(WORKLOADS))
+    ap.add_argument("--rows", type=int, default=0, help="override the matrix dimension (tests)")
+    ap.add_argument("--feat", type=int, default=0, help="override the feature width N")
+    ap.add_argument("--parts", type=int, default=1, help="number of column partitions")
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-memory end-to-end leg (profiling runs)")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    elif args.gpus > 1:
+        print(f"bench.py: --gpus {args.gpus} needs torchrun (one process per GPU); running 1 rank", file=sys.stderr)
+    try:
+        run_ours(args, rank, local_rank, world)
+    finally:
+        if world > 1:
+            import torch.distributed as dist
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,186 @@
+/*
+ * liteform_b200 -- C ABI of the B200 (sm_100a) implementation of LiteForm's composed-format SpMM.
+ *
+ * The reference project (johnpzh/liteform_ae) is pure Python and has no native boundary of its
+ * own: its format builder is interpreted Python and its kernels are generated at run time by an
+ * external TVM/SparseTIR fork.  Each entry point below therefore cites the Python function (path
+ * inside the reference project, file:line) whose work it takes over.  A binding for the
+ * reference's pipeline is a handful of ctypes calls; see INTEGRATION.md.
+ *
+ * Conventions
+ *   - every function returns 0 on success or a negative lf_status; lf_last_error() returns a
+ *     thread-local, human-readable message for the last failure on the calling thread;
+ *   - nothing throws, nothing allocates device memory: every device buffer, including scratch
+ *     ("workspace"), is owned by the caller, who obtains the required size from the matching
+ *     *_workspace_bytes() query;
+ *   - pointers are marked [dev] (device memory of the current CUDA device) or [host];
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream); functions
+ *     that return host-side results synchronise that stream before returning, all others only
+ *     enqueue work;
+ *   - matrices are CSR with int64 row pointers, int32 column indices sorted and distinct inside a
+ *     row, float values; dense operands are row-major with an explicit leading dimension.
+ */
+#ifndef LITEFORM_B200_H_
+#define LITEFORM_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  LF_OK = 0,
+  LF_ERR_INVALID_ARGUMENT = -1,
+  LF_ERR_CUDA = -2,
+  LF_ERR_WORKSPACE_TOO_SMALL = -3,
+  LF_ERR_UNSUPPORTED = -4,
+  LF_ERR_KERNEL_TIMEOUT = -5
+} lf_status;
+
+#define LF_NUM_WIDTH_CLASSES 11   /* widths 1, 2, 4 ... 1024 (format_algos.py:821) */
+#define LF_COLMASK_BINS 2048      /* 2^LF_NUM_WIDTH_CLASSES */
+#define LF_MAX_BUCKETS_PER_LAUNCH 256
+
+/* flags for the SpMM entry points */
+#define LF_SPMM_OVERWRITE 0       /* C = A * B   (every row of C is written)            */
+#define LF_SPMM_ACCUMULATE 1      /* C += A * B  (what the generated reference kernel does,
+                                     format_algos.py:508-515, 550, 595)                     */
+
+int lf_version(void);
+const char* lf_last_error(void);
+
+/* Process-wide tuning knobs of the SpMM launch (no counterpart in the reference, whose launch
+ * shape is fixed by its code generator, format_algos.py:503-539).  Results do not depend on them. */
+#define LF_OPT_SPMM_SLOTS_PER_GROUP 1  /* ELL slots one thread group walks (default 128)          */
+#define LF_OPT_SPMM_CACHE_POLICY 2     /* 0 default; 1 stream slots and C; 2 also pin B rows in L2 */
+int lf_set_option(int32_t option, int32_t value);
+
+/* ---------------------------------------------------------------------------------------------
+ * Bucket statistics for the width search.
+ * Replaces the per-nonzero Python loops of get_init_buckets (playground_pipline/
+ * format_algos.py:819-900).  For every column partition p (partition size ceil(K/P),
+ * format_algos.py:836) and width class k (width 2^k = 2^ceil(log2 degree) clipped to 1024,
+ * format_algos.py:875-882) it produces what the cost model reads from a Bucket
+ * (format_matrix_market.py:12-37):
+ *   class_stats[(p*11 + k)*3 + 0] = num_rows  (a clipped row counts 2^ceil(log2 d)/1024 times)
+ *   class_stats[(p*11 + k)*3 + 1] = nnz
+ *   class_stats[(p*11 + k)*3 + 2] = number of rows in the class  (len(row_indices))
+ * and, instead of Python sets of column ids, a histogram over per-column class bitmasks:
+ *   colmask_hist[p*2048 + m] = number of columns of partition p whose set of touching classes is m
+ * so that len(col_indices) of any merged bucket is a sum over the bins that intersect its classes.
+ * Both outputs are device arrays that the call overwrites.
+ * ------------------------------------------------------------------------------------------- */
+size_t lf_hyb_stats_workspace_bytes(int64_t num_rows, int64_t num_cols, int32_t num_parts);
+int lf_hyb_stats(const int64_t* indptr /*[dev] M+1*/, const int32_t* indices /*[dev] nnz*/,
+                 int64_t num_rows, int64_t num_cols, int32_t num_parts,
+                 int64_t* class_stats /*[dev] P*11*3*/, int64_t* colmask_hist /*[dev] P*2048*/,
+                 void* workspace /*[dev]*/, size_t workspace_bytes, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Description of a composed (column-partitioned, bucketed ELL) matrix in device memory.
+ * This is the device form of build_hyb_format's return value (format_algos.py:226-237, 385):
+ * for partition p and bucket b (global bucket index i = part_bucket_off[p] + b, width widths[i])
+ *   rows + row_off[i]  : int32[ell_rows[i]]            == row_indices_nd[p][b]
+ *   cols + slot_off[i] : int32[ell_rows[i]][widths[i]] == col_indices_nd[p][b]
+ *   mask + slot_off[i] : uint8 [ell_rows[i]][widths[i]] == mask_nd[p][b]
+ *   vals + slot_off[i] : float [ell_rows[i]][widths[i]]   the matrix values where mask is 1 and
+ *                        0 in the padding (the reference stores no values: its matrices are all
+ *                        ones and the mask itself is uploaded as A, format_algos.py:568-570)
+ * Bucket starts are aligned to 64 elements; the gaps hold zeros.
+ * zero_rows lists the matrix rows of [row_begin,row_end) that the SpMM must clear before it
+ * accumulates: rows without any entry and rows held by more than one ELL row.
+ * ------------------------------------------------------------------------------------------- */
+typedef struct lf_hyb {
+  int64_t num_rows;                 /* M of the whole matrix                               */
+  int64_t num_cols;                 /* K                                                   */
+  int64_t row_begin, row_end;       /* matrix rows covered by this (shard of the) format   */
+  int32_t num_parts;                /* P                                                   */
+  int32_t num_buckets;              /* total over partitions                               */
+  const int32_t* part_bucket_off;   /* [host] P+1                                          */
+  const int32_t* widths;            /* [host] num_buckets, ascending powers of two per part */
+  const int64_t* ell_rows;          /* [host] num_buckets                                  */
+  const int64_t* row_off;           /* [host] num_buckets+1                                */
+  const int64_t* slot_off;          /* [host] num_buckets+1                                */
+  const int32_t* rows;              /* [dev] row_off[num_buckets]                          */
+  const int32_t* cols;              /* [dev] slot_off[num_buckets]                         */
+  const float* vals;                /* [dev] slot_off[num_buckets]                         */
+  const uint8_t* mask;              /* [dev] slot_off[num_buckets] or NULL                 */
+  const int32_t* zero_rows;         /* [dev] num_zero_rows or NULL                         */
+  int64_t num_zero_rows;
+} lf_hyb;
+
+/* ---------------------------------------------------------------------------------------------
+ * Format construction, split in two calls so the caller can allocate the outputs in between.
+ * Together they replace build_hyb_format (playground_pipline/format_algos.py:226-385): rows of
+ * [row_begin,row_end) are placed, per partition, in the bucket bisect_left(widths, degree) clamped
+ * to the widest (format_algos.py:275-278); a row longer than its bucket width becomes consecutive
+ * ELL rows carrying the same row id (format_algos.py:286-305); unfinished ELL rows are padded with
+ * column 0 / mask 0 (format_algos.py:297-299, 344-350).  Inside a bucket ELL rows are ordered by
+ * matrix row, so a row range yields a contiguous slice of every bucket of the whole-matrix format.
+ *
+ * lf_hyb_plan counts: it fills ell_rows[], row_off[], slot_off[] (host) and *num_zero_rows, and
+ * leaves per-block offsets in `workspace` for lf_hyb_fill, which must be given the same
+ * workspace contents, the same matrix, widths and row range.
+ * ------------------------------------------------------------------------------------------- */
+size_t lf_hyb_build_workspace_bytes(int64_t row_begin, int64_t row_end, int32_t num_parts,
+                                    int32_t num_buckets);
+/* extra scratch lf_hyb_fill needs once the plan is known (appended by the caller's allocation) */
+size_t lf_hyb_fill_scratch_bytes(int64_t total_ell_rows);
+int lf_hyb_plan(const int64_t* indptr /*[dev]*/, const int32_t* indices /*[dev]*/,
+                int64_t num_rows, int64_t num_cols, int64_t row_begin, int64_t row_end,
+                int32_t num_parts, const int32_t* part_bucket_off /*[host] P+1*/,
+                const int32_t* widths /*[host]*/,
+                int64_t* ell_rows /*[host] out*/, int64_t* row_off /*[host] out*/,
+                int64_t* slot_off /*[host] out*/, int64_t* num_zero_rows /*[host] out*/,
+                void* workspace /*[dev]*/, size_t workspace_bytes, void* stream);
+int lf_hyb_fill(const int64_t* indptr /*[dev]*/, const int32_t* indices /*[dev]*/,
+                const float* data /*[dev] or NULL: all ones*/,
+                const lf_hyb* layout /* host arrays from lf_hyb_plan; device outputs written */,
+                void* workspace /*[dev]*/, size_t workspace_bytes,
+                void* scratch /*[dev]*/, size_t scratch_bytes, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * SpMM on the composed format: C[row_begin:row_end, 0:N] (=|+=) A[row_begin:row_end, :] * B.
+ * Replaces the kernel that bench_hyb_with_config generates, compiles and launches
+ * (playground_pipline/format_algos.py:388-605; arithmetic format_algos.py:99-102; launch shape
+ * format_algos.py:503-539).  All buckets of all partitions run in one launch.  C points at the
+ * first row of the shard (row row_begin), ldb/ldc are in elements.
+ * ------------------------------------------------------------------------------------------- */
+int lf_spmm_hyb_f32(const lf_hyb* A, const float* B /*[dev] K x N*/, int64_t ldb,
+                    float* C /*[dev] (row_end-row_begin) x N*/, int64_t ldc, int32_t N,
+                    int32_t flags, void* stream);
+
+/* Same product with every operand in HOST memory: the arrays of build_hyb_format as NumPy holds
+ * them after the int32/float32 casts of format_algos.py:568-577, B and C row-major.  The call
+ * copies the format and B into `device_workspace`, runs lf_spmm_hyb_f32 and copies C back, all on
+ * `stream`, and synchronises.  It is what one call of bench_hyb_with_config does between
+ * format_algos.py:546 and format_algos.py:595, without the run-time code generation. */
+size_t lf_spmm_hyb_f32_host_workspace_bytes(const lf_hyb* A_host, int32_t N);
+int lf_spmm_hyb_f32_host(const lf_hyb* A_host /* rows/cols/vals/zero_rows are [host] here */,
+                         const float* B /*[host]*/, float* C /*[host]*/, int32_t N, int32_t flags,
+                         void* device_workspace, size_t workspace_bytes, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * CSR SpMM, C = A * B.  Replaces the kernel of bench_naive (playground_pipline/
+ * format_algos.py:1660-1755); also the fallback the reference pipeline takes when the block
+ * format fails (proc05.spmm.end-to-end.py:237-249).
+ * ------------------------------------------------------------------------------------------- */
+int lf_spmm_csr_f32(const int64_t* indptr /*[dev]*/, const int32_t* indices /*[dev]*/,
+                    const float* data /*[dev] or NULL: all ones*/, int64_t row_begin, int64_t row_end,
+                    const float* B /*[dev]*/, int64_t ldb, float* C /*[dev]*/, int64_t ldc,
+                    int32_t N, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * nnz-balanced contiguous row ranges for G devices: splits[g] = first row r with
+ * indptr[r] >= g*nnz/G, splits[0] = 0, splits[G] = M.  (No counterpart in the reference, which
+ * runs on device 0 only, format_algos.py:548.)
+ * ------------------------------------------------------------------------------------------- */
+int lf_shard_rows(const int64_t* indptr /*[dev]*/, int64_t num_rows, int32_t num_shards,
+                  int64_t* splits /*[dev] G+1, written asynchronously on `stream`*/, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LITEFORM_B200_H_ */

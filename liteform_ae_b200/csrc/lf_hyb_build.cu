@@ -1,0 +1,544 @@
+// Device-side construction of LiteForm's composed format (column partitions x power-of-two ELL
+// buckets) from CSR: statistics for the width search, then count -> scan -> scatter.
+//
+// What the reference does on the host, one Python iteration per nonzero:
+//   get_init_buckets   playground_pipline/format_algos.py:819-900   -> lf_hyb_stats
+//   build_hyb_format   playground_pipline/format_algos.py:226-385   -> lf_hyb_plan + lf_hyb_fill
+//
+// None of the kernels below waits on another thread block: offsets across blocks come from a
+// separate scan launch, never from a look-back spin.
+#include "lf_common.cuh"
+
+namespace lf {
+
+static thread_local char g_err[512] = "";
+char* error_buffer() { return g_err; }
+int fail(int status, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return status;
+}
+
+namespace {
+
+constexpr int kRowsPerBlock = 256;   // one thread per matrix row in the count / fill kernels
+constexpr int kClasses = LF_NUM_WIDTH_CLASSES;
+constexpr int kLongRowChunks = 32;   // rows with more ELL rows than this are written by the whole block
+
+// First position in [pos, end) whose column is >= bound (columns ascend inside a row).
+__device__ __forceinline__ int64_t segment_end(const int32_t* __restrict__ indices, int64_t pos,
+                                               int64_t end, int64_t bound) {
+  if (pos >= end || indices[pos] >= bound) return pos;
+  int64_t lo = pos + 1, hi = end;  // indices[lo-1] < bound
+  while (lo < hi) {
+    int64_t mid = (lo + hi) >> 1;
+    if (indices[mid] < bound) lo = mid + 1; else hi = mid;
+  }
+  return lo;
+}
+
+// ------------------------------------------------------------------------------------------
+// statistics
+// ------------------------------------------------------------------------------------------
+// One warp per matrix row.  For each column partition the row touches: degree -> width class,
+// three counters per (partition, class), and the class bit OR-ed into every touched column.
+__global__ void __launch_bounds__(256)
+stats_rows_kernel(const int64_t* __restrict__ indptr, const int32_t* __restrict__ indices,
+                  int64_t num_rows, int64_t psz, int num_parts,
+                  unsigned long long* __restrict__ class_stats, uint32_t* __restrict__ colmask,
+                  int use_smem) {
+  extern __shared__ unsigned long long s_stats[];
+  const int n_stat = num_parts * kClasses * 3;
+  if (use_smem) {
+    for (int i = threadIdx.x; i < n_stat; i += blockDim.x) s_stats[i] = 0ull;
+    __syncthreads();
+  }
+  unsigned long long* acc = use_smem ? s_stats : class_stats;
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int64_t n_warps = (int64_t)gridDim.x * (blockDim.x >> 5);
+  for (int64_t r = warp; r < num_rows; r += n_warps) {
+    const int64_t s = indptr[r], e = indptr[r + 1];
+    int64_t pos = s;
+    while (pos < e) {
+      int64_t nxt;
+      int p;
+      if (num_parts == 1) {
+        p = 0;
+        nxt = e;
+      } else {
+        p = (int)(indices[pos] / psz);
+        nxt = segment_end(indices, pos, e, (int64_t)(p + 1) * psz);
+      }
+      const uint32_t deg = (uint32_t)(nxt - pos);
+      const int k = ceil_log2_u32(deg);
+      const int kc = k > kClasses - 1 ? kClasses - 1 : k;
+      if (lane == 0) {
+        const unsigned long long reps = k > kClasses - 1 ? (1ull << (k - (kClasses - 1))) : 1ull;
+        unsigned long long* a = acc + (p * kClasses + kc) * 3;
+        atomicAdd(a + 0, reps);
+        atomicAdd(a + 1, (unsigned long long)deg);
+        atomicAdd(a + 2, 1ull);
+      }
+      const uint32_t bit = 1u << kc;
+      for (int64_t i = pos + lane; i < nxt; i += 32) {
+        const int32_t c = indices[i];
+        if (!(colmask[c] & bit)) atomicOr(colmask + c, bit);
+      }
+      pos = nxt;
+    }
+  }
+  if (use_smem) {
+    __syncthreads();
+    for (int i = threadIdx.x; i < n_stat; i += blockDim.x)
+      if (s_stats[i]) atomicAdd(class_stats + i, s_stats[i]);
+  }
+}
+
+// blockIdx.y = partition; histogram of the 11-bit class masks of that partition's columns.
+__global__ void __launch_bounds__(256)
+colmask_hist_kernel(const uint32_t* __restrict__ colmask, int64_t num_cols, int64_t psz,
+                    unsigned long long* __restrict__ hist) {
+  __shared__ uint32_t s_hist[LF_COLMASK_BINS];
+  for (int i = threadIdx.x; i < LF_COLMASK_BINS; i += blockDim.x) s_hist[i] = 0u;
+  __syncthreads();
+  const int p = blockIdx.y;
+  const int64_t lo = (int64_t)p * psz;
+  int64_t hi = lo + psz;
+  if (hi > num_cols) hi = num_cols;
+  for (int64_t c = lo + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; c < hi;
+       c += (int64_t)gridDim.x * blockDim.x) {
+    const uint32_t m = colmask[c];
+    if (m) atomicAdd(&s_hist[m & (LF_COLMASK_BINS - 1)], 1u);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < LF_COLMASK_BINS; i += blockDim.x)
+    if (s_hist[i]) atomicAdd(hist + (size_t)p * LF_COLMASK_BINS + i, (unsigned long long)s_hist[i]);
+}
+
+// ------------------------------------------------------------------------------------------
+// plan / fill
+// ------------------------------------------------------------------------------------------
+struct BuildMeta {            // device copy of the per-call tables, at the head of the workspace
+  const int32_t* pbo;         // [P+1]
+  const int32_t* widths;      // [nb]
+  const int64_t* row_off;     // [nb+1]   (valid after lf_hyb_fill uploaded them)
+  const int64_t* slot_off;    // [nb+1]
+  const int64_t* ell_rows;    // [nb]
+};
+
+// bucket of a row of `deg` entries inside partition with widths w[0..n): bisect_left clamped.
+__device__ __forceinline__ int pick_bucket(const int32_t* __restrict__ w, int n, int deg) {
+  int b = 0;
+  while (b < n - 1 && w[b] < deg) ++b;
+  return b;
+}
+
+// One thread per matrix row: ELL rows it contributes to every (partition, bucket).
+__global__ void __launch_bounds__(kRowsPerBlock)
+hyb_count_kernel(const int64_t* __restrict__ indptr, const int32_t* __restrict__ indices,
+                 int64_t row_begin, int64_t row_end, int64_t psz, int num_parts,
+                 const int32_t* __restrict__ pbo, const int32_t* __restrict__ widths, int ncat,
+                 int32_t* __restrict__ block_counts, int32_t* __restrict__ err) {
+  extern __shared__ int32_t s_cnt[];
+  for (int i = threadIdx.x; i < ncat; i += blockDim.x) s_cnt[i] = 0;
+  __syncthreads();
+  const int64_t r = row_begin + (int64_t)blockIdx.x * kRowsPerBlock + threadIdx.x;
+  if (r < row_end) {
+    const int64_t s = indptr[r], e = indptr[r + 1];
+    int64_t pos = s;
+    int64_t total = 0;
+    while (pos < e) {
+      int p = 0;
+      int64_t nxt = e;
+      if (num_parts > 1) {
+        p = (int)(indices[pos] / psz);
+        nxt = segment_end(indices, pos, e, (int64_t)(p + 1) * psz);
+      }
+      const int deg = (int)(nxt - pos);
+      const int nb = pbo[p + 1] - pbo[p];
+      if (nb == 0) {
+        atomicExch(err, p + 1);  // entries in a partition that was given no bucket width
+      } else {
+        const int b = pick_bucket(widths + pbo[p], nb, deg);
+        const int w = widths[pbo[p] + b];
+        const int n = (deg + w - 1) / w;
+        atomicAdd(&s_cnt[pbo[p] + b], n);
+        total += n;
+      }
+      pos = nxt;
+    }
+    if (total != 1) atomicAdd(&s_cnt[ncat - 1], 1);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < ncat; i += blockDim.x)
+    block_counts[(size_t)blockIdx.x * ncat + i] = s_cnt[i];
+}
+
+// blockIdx.x = category; exclusive scan of that category's per-block counts over all blocks.
+__global__ void __launch_bounds__(256)
+scan_blocks_kernel(const int32_t* __restrict__ block_counts, int64_t num_blocks, int ncat,
+                   int64_t* __restrict__ block_offsets, int64_t* __restrict__ totals) {
+  __shared__ int s_scan[256 / 32 + 1];
+  const int cat = blockIdx.x;
+  int64_t running = 0;
+  for (int64_t base = 0; base < num_blocks; base += 256) {
+    const int64_t i = base + threadIdx.x;
+    const int v = i < num_blocks ? block_counts[(size_t)i * ncat + cat] : 0;
+    int tot;
+    const int ex = block_exclusive_scan<256>(v, s_scan, &tot);
+    if (i < num_blocks) block_offsets[(size_t)i * ncat + cat] = running + ex;
+    running += tot;
+  }
+  if (threadIdx.x == 0) totals[cat] = running;
+}
+
+// One thread per matrix row.  Writes, for every ELL row the matrix row produces: the row id, and
+// in scratch where its entries start in the CSR arrays and how many it holds.
+__global__ void __launch_bounds__(kRowsPerBlock)
+hyb_fill_rows_kernel(const int64_t* __restrict__ indptr, const int32_t* __restrict__ indices,
+                     int64_t row_begin, int64_t row_end, int64_t psz, int num_parts,
+                     BuildMeta meta, int ncat, const int32_t* __restrict__ block_counts,
+                     const int64_t* __restrict__ block_offsets, int32_t* __restrict__ ell_rows,
+                     int32_t* __restrict__ src_start, int32_t* __restrict__ src_len,
+                     int32_t* __restrict__ zero_rows) {
+  __shared__ int s_scan[kRowsPerBlock / 32 + 1];
+  __shared__ int s_nlong;
+  __shared__ int64_t s_long_dst[kRowsPerBlock];
+  __shared__ int64_t s_long_src[kRowsPerBlock];
+  __shared__ int32_t s_long_deg[kRowsPerBlock];
+  __shared__ int32_t s_long_row[kRowsPerBlock];
+
+  const int64_t r = row_begin + (int64_t)blockIdx.x * kRowsPerBlock + threadIdx.x;
+  const bool live = r < row_end;
+  const int64_t e = live ? indptr[r + 1] : 0;
+  int64_t pos = live ? indptr[r] : 0;
+  int64_t total = 0;
+  const int32_t* bc = block_counts + (size_t)blockIdx.x * ncat;
+  const int64_t* bo = block_offsets + (size_t)blockIdx.x * ncat;
+
+  for (int p = 0; p < num_parts; ++p) {
+    const int64_t seg = pos;
+    const int64_t nxt = num_parts == 1 ? e : segment_end(indices, pos, e, (int64_t)(p + 1) * psz);
+    pos = nxt;
+    const int deg = (int)(nxt - seg);
+    const int cat0 = meta.pbo[p];
+    const int nb = meta.pbo[p + 1] - cat0;
+    int my_b = -1, my_w = 1, my_n = 0;
+    if (deg > 0 && nb > 0) {
+      my_b = pick_bucket(meta.widths + cat0, nb, deg);
+      my_w = meta.widths[cat0 + my_b];
+      my_n = (deg + my_w - 1) / my_w;
+      total += my_n;
+    }
+    for (int b = 0; b < nb; ++b) {
+      if (bc[cat0 + b] == 0) continue;  // uniform: nobody in this block lands in the bucket
+      if (threadIdx.x == 0) s_nlong = 0;
+      int tot;
+      const int x = (my_b == b) ? my_n : 0;
+      const int ex = block_exclusive_scan<kRowsPerBlock>(x, s_scan, &tot);
+      if (x > 0) {
+        const int64_t dst = meta.row_off[cat0 + b] + bo[cat0 + b] + ex;
+        if (x <= kLongRowChunks) {
+          for (int c = 0; c < x; ++c) {
+            ell_rows[dst + c] = (int32_t)r;
+            src_start[dst + c] = (int32_t)(seg + (int64_t)c * my_w);
+            const int left = deg - c * my_w;
+            src_len[dst + c] = left < my_w ? left : my_w;
+          }
+        } else {
+          const int q = atomicAdd(&s_nlong, 1);
+          s_long_dst[q] = dst;
+          s_long_src[q] = seg;
+          s_long_deg[q] = deg;
+          s_long_row[q] = (int32_t)r;
+        }
+      }
+      __syncthreads();
+      const int nlong = s_nlong;
+      const int w = meta.widths[cat0 + b];
+      for (int q = 0; q < nlong; ++q) {
+        const int64_t dst = s_long_dst[q];
+        const int64_t src = s_long_src[q];
+        const int d = s_long_deg[q];
+        const int n = (d + w - 1) / w;
+        for (int c = threadIdx.x; c < n; c += kRowsPerBlock) {
+          ell_rows[dst + c] = s_long_row[q];
+          src_start[dst + c] = (int32_t)(src + (int64_t)c * w);
+          const int left = d - c * w;
+          src_len[dst + c] = left < w ? left : w;
+        }
+      }
+      __syncthreads();
+    }
+  }
+  if (bc[ncat - 1] != 0) {
+    int tot;
+    const int flag = (live && total != 1) ? 1 : 0;
+    const int ex = block_exclusive_scan<kRowsPerBlock>(flag, s_scan, &tot);
+    if (flag) zero_rows[bo[ncat - 1] + ex] = (int32_t)r;
+  }
+}
+
+// One thread per slot of the cols/vals/mask arenas (alignment gaps included, they get zeros).
+__global__ void __launch_bounds__(256)
+hyb_fill_slots_kernel(const int32_t* __restrict__ indices, const float* __restrict__ data,
+                      BuildMeta meta, int nb, const int32_t* __restrict__ src_start,
+                      const int32_t* __restrict__ src_len, int32_t* __restrict__ cols,
+                      float* __restrict__ vals, uint8_t* __restrict__ mask, int64_t total_slots) {
+  for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total_slots;
+       t += (int64_t)gridDim.x * blockDim.x) {
+    int lo = 0, hi = nb;  // last bucket i with slot_off[i] <= t
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (meta.slot_off[mid] <= t) lo = mid; else hi = mid;
+    }
+    const int w = meta.widths[lo];
+    const int64_t local = t - meta.slot_off[lo];
+    int32_t c = 0;
+    float v = 0.f;
+    uint8_t m = 0;
+    if (local < meta.ell_rows[lo] * w) {
+      const int64_t er = meta.row_off[lo] + local / w;
+      const int j = (int)(local % w);
+      if (j < src_len[er]) {
+        const int64_t src = (int64_t)src_start[er] + j;
+        c = indices[src];
+        v = data ? data[src] : 1.f;
+        m = 1;
+      }
+    }
+    cols[t] = c;
+    vals[t] = v;
+    if (mask) mask[t] = m;
+  }
+}
+
+__global__ void shard_rows_kernel(const int64_t* __restrict__ indptr, int64_t num_rows, int shards,
+                                  int64_t* __restrict__ splits) {
+  const int g = blockIdx.x * blockDim.x + threadIdx.x;
+  if (g > shards) return;
+  if (g == shards) { splits[g] = num_rows; return; }
+  const int64_t nnz = indptr[num_rows] - indptr[0];
+  const int64_t target = indptr[0] + (int64_t)(((__int128)nnz * g) / shards);
+  int64_t lo = 0, hi = num_rows;  // first r with indptr[r] >= target
+  while (lo < hi) {
+    const int64_t mid = (lo + hi) >> 1;
+    if (indptr[mid] < target) lo = mid + 1; else hi = mid;
+  }
+  splits[g] = lo;
+}
+
+// ---- workspace carving ---------------------------------------------------------------------
+struct BuildWs {
+  int32_t* pbo; int32_t* widths; int64_t* row_off; int64_t* slot_off; int64_t* ell_rows;
+  int64_t* totals; int32_t* err; int32_t* block_counts; int64_t* block_offsets;
+  size_t bytes;
+};
+
+BuildWs carve_build(void* base, int64_t rows, int num_parts, int nb) {
+  const int ncat = nb + 1;
+  const int64_t blocks = ceil_div64(rows > 0 ? rows : 1, kRowsPerBlock);
+  size_t off = 0;
+  auto take = [&](size_t bytes) { size_t o = off; off = align_up(off + bytes, 256); return (char*)base + o; };
+  BuildWs w;
+  w.pbo = (int32_t*)take(sizeof(int32_t) * (num_parts + 1));
+  w.widths = (int32_t*)take(sizeof(int32_t) * (nb > 0 ? nb : 1));
+  w.row_off = (int64_t*)take(sizeof(int64_t) * (nb + 1));
+  w.slot_off = (int64_t*)take(sizeof(int64_t) * (nb + 1));
+  w.ell_rows = (int64_t*)take(sizeof(int64_t) * (nb > 0 ? nb : 1));
+  w.totals = (int64_t*)take(sizeof(int64_t) * (ncat + 2));
+  w.err = (int32_t*)take(sizeof(int32_t) * 4);
+  w.block_counts = (int32_t*)take(sizeof(int32_t) * blocks * ncat);
+  w.block_offsets = (int64_t*)take(sizeof(int64_t) * blocks * ncat);
+  w.bytes = off;
+  return w;
+}
+
+int check_widths(int32_t num_parts, const int32_t* pbo, const int32_t* widths) {
+  LF_REQUIRE(num_parts >= 1, "num_parts must be >= 1 (got %d)", num_parts);
+  LF_REQUIRE(pbo && pbo[0] == 0, "part_bucket_off[0] must be 0");
+  for (int p = 0; p < num_parts; ++p) {
+    LF_REQUIRE(pbo[p + 1] >= pbo[p], "part_bucket_off must be non-decreasing");
+    for (int i = pbo[p]; i < pbo[p + 1]; ++i) {
+      const int w = widths[i];
+      LF_REQUIRE(w >= 1 && (w & (w - 1)) == 0, "bucket width %d (partition %d) is not a power of two", w, p);
+      LF_REQUIRE(i == pbo[p] || widths[i - 1] < w, "bucket widths of partition %d are not ascending", p);
+    }
+  }
+  return LF_OK;
+}
+
+}  // namespace
+}  // namespace lf
+
+using namespace lf;
+
+extern "C" {
+
+int lf_version(void) { return 100; }
+const char* lf_last_error(void) { return lf::error_buffer(); }
+
+size_t lf_hyb_stats_workspace_bytes(int64_t /*num_rows*/, int64_t num_cols, int32_t /*num_parts*/) {
+  return align_up(sizeof(uint32_t) * (size_t)(num_cols > 0 ? num_cols : 1), 256);
+}
+
+int lf_hyb_stats(const int64_t* indptr, const int32_t* indices, int64_t num_rows, int64_t num_cols,
+                 int32_t num_parts, int64_t* class_stats, int64_t* colmask_hist, void* workspace,
+                 size_t workspace_bytes, void* stream) {
+  LF_REQUIRE(indptr && class_stats && colmask_hist && workspace, "null pointer argument");
+  LF_REQUIRE(num_rows >= 0 && num_cols >= 1, "bad shape %lld x %lld", (long long)num_rows, (long long)num_cols);
+  LF_REQUIRE(num_parts >= 1 && num_parts <= num_cols, "num_parts %d out of range", num_parts);
+  if (workspace_bytes < lf_hyb_stats_workspace_bytes(num_rows, num_cols, num_parts))
+    return fail(LF_ERR_WORKSPACE_TOO_SMALL, "stats workspace too small");
+  cudaStream_t st = (cudaStream_t)stream;
+  const int64_t psz = ceil_div64(num_cols, num_parts);
+  uint32_t* colmask = (uint32_t*)workspace;
+  const size_t n_stat = (size_t)num_parts * kClasses * 3;
+  LF_CUDA_CHECK(cudaMemsetAsync(colmask, 0, sizeof(uint32_t) * num_cols, st));
+  LF_CUDA_CHECK(cudaMemsetAsync(class_stats, 0, sizeof(int64_t) * n_stat, st));
+  LF_CUDA_CHECK(cudaMemsetAsync(colmask_hist, 0, sizeof(int64_t) * (size_t)num_parts * LF_COLMASK_BINS, st));
+  if (num_rows > 0) {
+    const size_t smem = n_stat * sizeof(unsigned long long);
+    const int use_smem = smem <= 40 * 1024;
+    const int64_t want = ceil_div64(num_rows, 8 * 4);  // 8 warps per block, ~4 rows per warp
+    const int grid = (int)(want < 1 ? 1 : (want > 148 * 64 ? 148 * 64 : want));
+    stats_rows_kernel<<<grid, 256, use_smem ? smem : 0, st>>>(
+        indptr, indices, num_rows, psz, num_parts, (unsigned long long*)class_stats, colmask, use_smem);
+    LF_CUDA_CHECK(cudaGetLastError());
+  }
+  {
+    const int64_t want = ceil_div64(psz, 256 * 8);
+    dim3 grid((unsigned)(want < 1 ? 1 : (want > 1024 ? 1024 : want)), (unsigned)num_parts);
+    LF_REQUIRE(num_parts <= 65535, "num_parts %d exceeds the grid limit", num_parts);
+    colmask_hist_kernel<<<grid, 256, 0, st>>>(colmask, num_cols, psz, (unsigned long long*)colmask_hist);
+    LF_CUDA_CHECK(cudaGetLastError());
+  }
+  return LF_OK;
+}
+
+size_t lf_hyb_build_workspace_bytes(int64_t row_begin, int64_t row_end, int32_t num_parts,
+                                    int32_t num_buckets) {
+  return carve_build(nullptr, row_end - row_begin, num_parts, num_buckets).bytes;
+}
+
+size_t lf_hyb_fill_scratch_bytes(int64_t total_ell_rows) {
+  return 2 * align_up(sizeof(int32_t) * (size_t)(total_ell_rows > 0 ? total_ell_rows : 1), 256);
+}
+
+int lf_hyb_plan(const int64_t* indptr, const int32_t* indices, int64_t num_rows, int64_t num_cols,
+                int64_t row_begin, int64_t row_end, int32_t num_parts,
+                const int32_t* part_bucket_off, const int32_t* widths, int64_t* ell_rows,
+                int64_t* row_off, int64_t* slot_off, int64_t* num_zero_rows, void* workspace,
+                size_t workspace_bytes, void* stream) {
+  LF_REQUIRE(indptr && part_bucket_off && ell_rows && row_off && slot_off && num_zero_rows && workspace,
+             "null pointer argument");
+  LF_REQUIRE(num_cols >= 1 && 0 <= row_begin && row_begin <= row_end && row_end <= num_rows,
+             "bad shape or row range");
+  if (int s = check_widths(num_parts, part_bucket_off, widths)) return s;
+  LF_REQUIRE(num_parts <= num_cols, "num_parts %d exceeds the number of columns", num_parts);
+  const int nb = part_bucket_off[num_parts];
+  const int ncat = nb + 1;
+  LF_REQUIRE((size_t)ncat * sizeof(int32_t) <= 40 * 1024, "too many buckets (%d)", nb);
+  const int64_t rows = row_end - row_begin;
+  BuildWs ws = carve_build(workspace, rows, num_parts, nb);
+  if (workspace_bytes < ws.bytes) return fail(LF_ERR_WORKSPACE_TOO_SMALL, "build workspace too small");
+  cudaStream_t st = (cudaStream_t)stream;
+  const int64_t psz = ceil_div64(num_cols, num_parts);
+  const int64_t blocks = ceil_div64(rows > 0 ? rows : 1, kRowsPerBlock);
+  LF_REQUIRE(blocks < (1ll << 31), "row range too large");
+
+  LF_CUDA_CHECK(cudaMemcpyAsync(ws.pbo, part_bucket_off, sizeof(int32_t) * (num_parts + 1), cudaMemcpyHostToDevice, st));
+  if (nb) LF_CUDA_CHECK(cudaMemcpyAsync(ws.widths, widths, sizeof(int32_t) * nb, cudaMemcpyHostToDevice, st));
+  LF_CUDA_CHECK(cudaMemsetAsync(ws.err, 0, sizeof(int32_t) * 4, st));
+  hyb_count_kernel<<<(unsigned)blocks, kRowsPerBlock, sizeof(int32_t) * ncat, st>>>(
+      indptr, indices, row_begin, row_end, psz, num_parts, ws.pbo, ws.widths, ncat, ws.block_counts, ws.err);
+  LF_CUDA_CHECK(cudaGetLastError());
+  scan_blocks_kernel<<<ncat, 256, 0, st>>>(ws.block_counts, blocks, ncat, ws.block_offsets, ws.totals);
+  LF_CUDA_CHECK(cudaGetLastError());
+
+  // host results: totals per category, the error flag and the entry range (for the int32 guard)
+  int64_t h_tot_small[64];
+  int64_t* h_tot = ncat <= 64 ? h_tot_small : (int64_t*)malloc(sizeof(int64_t) * ncat);
+  int32_t h_err = 0;
+  int64_t h_ptr[2] = {0, 0};
+  cudaError_t ce = cudaMemcpyAsync(h_tot, ws.totals, sizeof(int64_t) * ncat, cudaMemcpyDeviceToHost, st);
+  if (ce == cudaSuccess) ce = cudaMemcpyAsync(&h_err, ws.err, sizeof(int32_t), cudaMemcpyDeviceToHost, st);
+  if (ce == cudaSuccess) ce = cudaMemcpyAsync(&h_ptr[0], indptr + row_begin, sizeof(int64_t), cudaMemcpyDeviceToHost, st);
+  if (ce == cudaSuccess) ce = cudaMemcpyAsync(&h_ptr[1], indptr + row_end, sizeof(int64_t), cudaMemcpyDeviceToHost, st);
+  if (ce == cudaSuccess) ce = cudaStreamSynchronize(st);
+  int status = LF_OK;
+  if (ce != cudaSuccess) {
+    status = fail(LF_ERR_CUDA, "lf_hyb_plan: %s", cudaGetErrorString(ce));
+  } else if (h_err) {
+    status = fail(LF_ERR_INVALID_ARGUMENT, "partition %d holds entries but was given no bucket width", h_err - 1);
+  } else if (h_ptr[1] > 0x7fffffffll) {
+    status = fail(LF_ERR_UNSUPPORTED, "more than 2^31-1 stored entries are not supported");
+  } else {
+    row_off[0] = slot_off[0] = 0;
+    for (int i = 0; i < nb; ++i) {
+      ell_rows[i] = h_tot[i];
+      row_off[i + 1] = row_off[i] + (int64_t)align_up((size_t)h_tot[i], kBucketAlign);
+      slot_off[i + 1] = slot_off[i] + (int64_t)align_up((size_t)h_tot[i] * widths[i], kBucketAlign);
+    }
+    *num_zero_rows = h_tot[nb];
+  }
+  if (h_tot != h_tot_small) free(h_tot);
+  return status;
+}
+
+int lf_hyb_fill(const int64_t* indptr, const int32_t* indices, const float* data,
+                const lf_hyb* L, void* workspace, size_t workspace_bytes, void* scratch,
+                size_t scratch_bytes, void* stream) {
+  LF_REQUIRE(indptr && L && workspace && scratch, "null pointer argument");
+  LF_REQUIRE(L->part_bucket_off && L->ell_rows && L->row_off && L->slot_off, "layout host arrays missing");
+  if (int s = check_widths(L->num_parts, L->part_bucket_off, L->widths)) return s;
+  const int nb = L->num_buckets;
+  LF_REQUIRE(nb == L->part_bucket_off[L->num_parts], "num_buckets does not match part_bucket_off");
+  const int ncat = nb + 1;
+  const int64_t rows = L->row_end - L->row_begin;
+  LF_REQUIRE(rows >= 0 && L->row_end <= L->num_rows && L->num_cols >= 1, "bad row range");
+  const int64_t total_rows = L->row_off[nb], total_slots = L->slot_off[nb];
+  LF_REQUIRE((total_rows == 0 || L->rows) && (total_slots == 0 || (L->cols && L->vals)), "output arrays missing");
+  LF_REQUIRE(L->num_zero_rows == 0 || L->zero_rows, "zero_rows array missing");
+  BuildWs ws = carve_build(workspace, rows, L->num_parts, nb);
+  if (workspace_bytes < ws.bytes) return fail(LF_ERR_WORKSPACE_TOO_SMALL, "build workspace too small");
+  if (scratch_bytes < lf_hyb_fill_scratch_bytes(total_rows)) return fail(LF_ERR_WORKSPACE_TOO_SMALL, "fill scratch too small");
+  cudaStream_t st = (cudaStream_t)stream;
+  const int64_t psz = ceil_div64(L->num_cols, L->num_parts);
+  const int64_t blocks = ceil_div64(rows > 0 ? rows : 1, kRowsPerBlock);
+  int32_t* src_start = (int32_t*)scratch;
+  int32_t* src_len = (int32_t*)((char*)scratch + lf_hyb_fill_scratch_bytes(total_rows) / 2);
+
+  LF_CUDA_CHECK(cudaMemcpyAsync(ws.row_off, L->row_off, sizeof(int64_t) * (nb + 1), cudaMemcpyHostToDevice, st));
+  LF_CUDA_CHECK(cudaMemcpyAsync(ws.slot_off, L->slot_off, sizeof(int64_t) * (nb + 1), cudaMemcpyHostToDevice, st));
+  if (nb) LF_CUDA_CHECK(cudaMemcpyAsync(ws.ell_rows, L->ell_rows, sizeof(int64_t) * nb, cudaMemcpyHostToDevice, st));
+  if (total_rows) LF_CUDA_CHECK(cudaMemsetAsync((void*)L->rows, 0, sizeof(int32_t) * total_rows, st));
+  BuildMeta meta{ws.pbo, ws.widths, ws.row_off, ws.slot_off, ws.ell_rows};
+  if (rows > 0) {
+    hyb_fill_rows_kernel<<<(unsigned)blocks, kRowsPerBlock, 0, st>>>(
+        indptr, indices, L->row_begin, L->row_end, psz, L->num_parts, meta, ncat, ws.block_counts,
+        ws.block_offsets, (int32_t*)L->rows, src_start, src_len, (int32_t*)L->zero_rows);
+    LF_CUDA_CHECK(cudaGetLastError());
+  }
+  if (total_slots > 0) {
+    const int64_t want = ceil_div64(total_slots, 256 * 4);
+    const int grid = (int)(want > 148 * 32 ? 148 * 32 : want);
+    hyb_fill_slots_kernel<<<grid, 256, 0, st>>>(indices, data, meta, nb, src_start, src_len,
+                                                (int32_t*)L->cols, (float*)L->vals, (uint8_t*)L->mask, total_slots);
+    LF_CUDA_CHECK(cudaGetLastError());
+  }
+  return LF_OK;
+}
+
+int lf_shard_rows(const int64_t* indptr, int64_t num_rows, int32_t num_shards, int64_t* splits, void* stream) {
+  LF_REQUIRE(indptr && splits && num_rows >= 0, "bad arguments");
+  LF_REQUIRE(num_shards >= 1 && num_shards <= 1024, "num_shards %d out of range", num_shards);
+  shard_rows_kernel<<<(num_shards + 1 + 63) / 64, 64, 0, (cudaStream_t)stream>>>(indptr, num_rows, num_shards, splits);
+  LF_CUDA_CHECK(cudaGetLastError());
+  return LF_OK;
+}
+
+}  // extern "C"

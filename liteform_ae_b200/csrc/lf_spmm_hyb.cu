@@ -1,0 +1,526 @@
+// SpMM over the composed format: C[r, :] (=|+=) sum over the ELL rows carrying row id r of
+// sum_j vals[i, j] * B[cols[i, j], :].
+//
+// Takes over the kernel the reference generates through SparseTIR/TVM at run time
+// (playground_pipline/format_algos.py:388-605; the arithmetic is format_algos.py:99-102 over the
+// ELL axes of format_algos.py:55-70, the launch shape format_algos.py:503-539).  Like the
+// reference, every (partition, bucket) pair runs inside ONE launch; unlike it, a thread group
+// walks a contiguous run of ELL rows and keeps the running sum in registers while the row id does
+// not change, so that only runs cut by a group boundary (or by column partitioning) need an
+// atomic: the reference issues one atomicAdd per ELL row of every widest bucket
+// (format_algos.py:508-515).
+//
+// Work decomposition (hand-written for sm_100a, HBM/L2-bound):
+//   * G lanes (8, 16 or 32) form a group; lane l of the group owns features [f0 + 4*l, +4) of V
+//     consecutive G*4-wide feature chunks, so one B-row gather is a 128-bit load per lane and a
+//     fully coalesced 128..512 B segment per group;
+//   * the group reads the (col, val) slots of its ELL rows G at a time, coalesced, and broadcasts
+//     them with shuffles; U gathers are issued back to back before any FMA consumes them;
+//   * padded slots (val == 0) issue no gather.
+#include "lf_common.cuh"
+
+namespace lf {
+namespace {
+
+constexpr int kThreads = 256;
+
+struct BucketDesc {
+  int64_t row_off;        // first element of this bucket in the rows arena
+  int64_t slot_off;       // first element in the cols / vals arenas
+  int64_t ell_rows;       // R
+  int64_t tile_begin;     // first thread block of this bucket
+  int32_t wlog;           // log2(width)
+  int32_t rows_per_group; // ELL rows one group walks
+  int32_t force_atomic;   // every flush of this bucket must be an atomic add
+  int32_t pad_;
+};
+
+template <int MAXB>
+struct SpmmTable {
+  int32_t n;
+  int32_t pad_;
+  BucketDesc b[MAXB];
+};
+
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+// L2 eviction policies (sm_80+ createpolicy): B rows are the only data with reuse, everything
+// else (slots, row ids, C) streams through once.
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+
+template <int VEC> struct Chunk;
+template <> struct Chunk<4> {
+  float4 v;
+  __device__ __forceinline__ void zero() { v = make_float4(0.f, 0.f, 0.f, 0.f); }
+  __device__ __forceinline__ void load(const float* p) { v = __ldg(reinterpret_cast<const float4*>(p)); }
+  __device__ __forceinline__ void load_keep(const float* p, uint64_t pol) {
+    asm volatile("ld.global.nc.L2::cache_hint.v4.f32 {%0, %1, %2, %3}, [%4], %5;"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p), "l"(pol));
+  }
+  __device__ __forceinline__ void store_stream(float* p) const { __stcs(reinterpret_cast<float4*>(p), v); }
+  __device__ __forceinline__ void fma(float a, const Chunk& x) {
+    v.x = fmaf(a, x.v.x, v.x); v.y = fmaf(a, x.v.y, v.y); v.z = fmaf(a, x.v.z, v.z); v.w = fmaf(a, x.v.w, v.w);
+  }
+  __device__ __forceinline__ void store(float* p) const { *reinterpret_cast<float4*>(p) = v; }
+  __device__ __forceinline__ void red(float* p) const { red_add_v4(p, v.x, v.y, v.z, v.w); }
+};
+template <> struct Chunk<1> {
+  float v;
+  __device__ __forceinline__ void zero() { v = 0.f; }
+  __device__ __forceinline__ void load(const float* p) { v = __ldg(p); }
+  __device__ __forceinline__ void load_keep(const float* p, uint64_t pol) {
+    asm volatile("ld.global.nc.L2::cache_hint.f32 %0, [%1], %2;" : "=f"(v) : "l"(p), "l"(pol));
+  }
+  __device__ __forceinline__ void store_stream(float* p) const { __stcs(p, v); }
+  __device__ __forceinline__ void fma(float a, const Chunk& x) { v = fmaf(a, x.v, v); }
+  __device__ __forceinline__ void store(float* p) const { *p = v; }
+  __device__ __forceinline__ void red(float* p) const { atomicAdd(p, v); }
+};
+
+// G lanes per group, V chunks of VEC floats per lane: one pass covers G*V*VEC features.
+// POL selects cache behaviour: 0 = default loads/stores; 1 = slots, row ids and C use streaming
+// (evict-first) accesses; 2 = as 1, and B rows are loaded with an L2 evict-last policy.
+template <int G, int V, int VEC, int MAXB, int POL>
+__global__ void __launch_bounds__(kThreads)
+spmm_hyb_kernel(const __grid_constant__ SpmmTable<MAXB> tbl, const int32_t* __restrict__ rows_arena,
+                const int32_t* __restrict__ cols_arena, const float* __restrict__ vals_arena,
+                const float* __restrict__ B, int64_t ldb, float* __restrict__ C, int64_t ldc, int N,
+                int64_t row_base) {
+  constexpr int GPC = kThreads / G;                 // groups per thread block
+  constexpr int U = V == 1 ? 8 : (V == 2 ? 4 : 2);  // gathers in flight per lane (x V chunks)
+  static_assert(G % U == 0, "unroll must divide the group size");
+
+  // which bucket does this thread block work on?
+  const int64_t tile = blockIdx.x;
+  int lo = 0, hi = tbl.n;
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (tbl.b[mid].tile_begin <= tile) lo = mid; else hi = mid;
+  }
+  const BucketDesc& d = tbl.b[lo];
+  const int wlog = d.wlog;
+  const int g = threadIdx.x / G, lane = threadIdx.x % G;
+  const unsigned gmask = G == 32 ? 0xffffffffu : (((1u << G) - 1u) << ((threadIdx.x & 31) / G * G));
+  const int64_t e0 = ((tile - d.tile_begin) * GPC + g) * (int64_t)d.rows_per_group;
+  if (e0 >= d.ell_rows) return;
+  const int64_t e1 = min(e0 + d.rows_per_group, d.ell_rows);
+  const int32_t* __restrict__ rows = rows_arena + d.row_off;
+  const int32_t* __restrict__ cols = cols_arena + d.slot_off;
+  const float* __restrict__ vals = vals_arena + d.slot_off;
+
+  // does the first / last run of equal row ids continue in a neighbouring group?
+  const int first_row = rows[e0], last_row = rows[e1 - 1];
+  const bool all_open = d.force_atomic != 0;
+  const bool head_open = e0 > 0 && rows[e0 - 1] == first_row;
+  const bool tail_open = e1 < d.ell_rows && rows[e1] == last_row;
+
+  const int f0 = blockIdx.y * (G * V * VEC) + lane * VEC;
+  bool active[V];
+#pragma unroll
+  for (int v = 0; v < V; ++v) active[v] = f0 + v * G * VEC < N;
+
+  Chunk<VEC> acc[V];
+#pragma unroll
+  for (int v = 0; v < V; ++v) acc[v].zero();
+  int cur = first_row;
+
+  auto flush = [&](int row) {
+    const bool open = all_open || (row == first_row && head_open) || (row == last_row && tail_open);
+    float* dst = C + (int64_t)(row - row_base) * ldc + f0;
+#pragma unroll
+    for (int v = 0; v < V; ++v) {
+      if (active[v]) {
+        if (open) acc[v].red(dst + v * G * VEC);
+        else if (POL >= 1) acc[v].store_stream(dst + v * G * VEC);
+        else acc[v].store(dst + v * G * VEC);
+      }
+      acc[v].zero();
+    }
+  };
+
+  uint64_t keep = 0;
+  if (POL == 2) keep = l2_policy_evict_last();
+  const int64_t s0 = e0 << wlog, s1 = e1 << wlog;
+  for (int64_t s = s0; s < s1; s += G) {
+    const int64_t idx = s + lane;
+    const bool in = idx < s1;
+    const int64_t cidx = in ? idx : s1 - 1;
+    const int my_col = POL >= 1 ? __ldcs(cols + cidx) : cols[cidx];
+    const float my_val = in ? (POL >= 1 ? __ldcs(vals + cidx) : vals[cidx]) : 0.f;
+    const int my_rid = rows[cidx >> wlog];
+    const int nstrip = (int)min((int64_t)G, s1 - s);
+    for (int t = 0; t < nstrip; t += U) {
+      int rid[U];
+      float val[U];
+      Chunk<VEC> b[U][V];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int c = __shfl_sync(gmask, my_col, t + u, G);
+        val[u] = __shfl_sync(gmask, my_val, t + u, G);
+        rid[u] = __shfl_sync(gmask, my_rid, t + u, G);
+        const float* src = B + (int64_t)c * ldb + f0;
+#pragma unroll
+        for (int v = 0; v < V; ++v) {
+          if (val[u] != 0.f && active[v]) {
+            if (POL == 2) b[u][v].load_keep(src + v * G * VEC, keep); else b[u][v].load(src + v * G * VEC);
+          } else {
+            b[u][v].zero();
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (rid[u] != cur) {
+          flush(cur);
+          cur = rid[u];
+        }
+#pragma unroll
+        for (int v = 0; v < V; ++v) acc[v].fma(val[u], b[u][v]);
+      }
+    }
+  }
+  flush(cur);
+}
+
+// Rows that no single ELL row owns are cleared before the accumulating launch.
+template <int VEC>
+__global__ void __launch_bounds__(kThreads)
+zero_rows_kernel(const int32_t* __restrict__ zero_rows, int64_t n, float* __restrict__ C, int64_t ldc,
+                 int N, int64_t row_base) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (int64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
+  const int64_t n_warps = (int64_t)gridDim.x * (kThreads / 32);
+  for (int64_t i = warp; i < n; i += n_warps) {
+    float* dst = C + (int64_t)(zero_rows[i] - row_base) * ldc;
+    if (VEC == 4) {
+      for (int f = lane * 4; f < N; f += 128) *reinterpret_cast<float4*>(dst + f) = make_float4(0.f, 0.f, 0.f, 0.f);
+    } else {
+      for (int f = lane; f < N; f += 32) dst[f] = 0.f;
+    }
+  }
+}
+
+// CSR row-per-group SpMM (the "naive" kernel of the reference, format_algos.py:1660-1686).
+template <int G, int V, int VEC>
+__global__ void __launch_bounds__(kThreads)
+spmm_csr_kernel(const int64_t* __restrict__ indptr, const int32_t* __restrict__ indices,
+                const float* __restrict__ data, int64_t row_begin, int64_t row_end,
+                const float* __restrict__ B, int64_t ldb, float* __restrict__ C, int64_t ldc, int N) {
+  constexpr int GPC = kThreads / G;
+  constexpr int U = V == 1 ? 8 : (V == 2 ? 4 : 2);
+  const int g = threadIdx.x / G, lane = threadIdx.x % G;
+  const unsigned gmask = G == 32 ? 0xffffffffu : (((1u << G) - 1u) << ((threadIdx.x & 31) / G * G));
+  const int64_t r = row_begin + (int64_t)blockIdx.x * GPC + g;
+  if (r >= row_end) return;
+  const int f0 = blockIdx.y * (G * V * VEC) + lane * VEC;
+  bool active[V];
+  Chunk<VEC> acc[V];
+#pragma unroll
+  for (int v = 0; v < V; ++v) { active[v] = f0 + v * G * VEC < N; acc[v].zero(); }
+  const int64_t s0 = indptr[r], s1 = indptr[r + 1];
+  for (int64_t s = s0; s < s1; s += G) {
+    const int64_t idx = s + lane;
+    const bool in = idx < s1;
+    const int my_col = in ? indices[idx] : 0;
+    const float my_val = in ? (data ? data[idx] : 1.f) : 0.f;
+    const int nstrip = (int)min((int64_t)G, s1 - s);
+    for (int t = 0; t < nstrip; t += U) {
+      float val[U];
+      Chunk<VEC> b[U][V];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int c = __shfl_sync(gmask, my_col, t + u, G);
+        val[u] = __shfl_sync(gmask, my_val, t + u, G);
+        const float* src = B + (int64_t)c * ldb + f0;
+#pragma unroll
+        for (int v = 0; v < V; ++v) {
+          if (val[u] != 0.f && active[v]) b[u][v].load(src + v * G * VEC); else b[u][v].zero();
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int v = 0; v < V; ++v) acc[v].fma(val[u], b[u][v]);
+    }
+  }
+  float* dst = C + (r - row_begin) * ldc + f0;
+#pragma unroll
+  for (int v = 0; v < V; ++v)
+    if (active[v]) acc[v].store(dst + v * G * VEC);
+}
+
+struct FeatCfg { int G, V, VEC, pass; };
+
+FeatCfg pick_cfg(const void* B, int64_t ldb, const void* C, int64_t ldc, int N) {
+  const bool vec = (N % 4 == 0) && (ldb % 4 == 0) && (ldc % 4 == 0) && ((uintptr_t)B % 16 == 0) &&
+                   ((uintptr_t)C % 16 == 0);
+  FeatCfg c;
+  if (vec) {
+    c.VEC = 4;
+    if (N <= 32) { c.G = 8; c.V = 1; }
+    else if (N <= 64) { c.G = 16; c.V = 1; }
+    else if (N <= 128) { c.G = 32; c.V = 1; }
+    else if (N <= 256) { c.G = 32; c.V = 2; }
+    else { c.G = 32; c.V = 4; }
+  } else {
+    c.VEC = 1;
+    c.G = 32;
+    c.V = N <= 32 ? 1 : (N <= 64 ? 2 : 4);
+  }
+  c.pass = c.G * c.V * c.VEC;
+  return c;
+}
+
+// Process-wide tuning knobs (lf_set_option); the environment gives the initial values.
+int g_slots_per_group = 0;
+int g_cache_policy = -1;
+
+int slots_per_group() {
+  if (!g_slots_per_group) {
+    const char* e = getenv("LF_SPMM_SLOTS_PER_GROUP");
+    int v = e ? atoi(e) : 0;
+    g_slots_per_group = (v >= 8 && v <= (1 << 20)) ? v : 128;
+  }
+  return g_slots_per_group;
+}
+
+int cache_policy() {
+  if (g_cache_policy < 0) {
+    const char* e = getenv("LF_SPMM_POLICY");
+    const int v = e ? atoi(e) : 0;
+    g_cache_policy = (v >= 0 && v <= 2) ? v : 0;
+  }
+  return g_cache_policy;
+}
+
+template <int MAXB, int POL>
+int launch_hyb_pol(const SpmmTable<MAXB>& tbl, int64_t tiles, const lf_hyb* A, const float* B, int64_t ldb,
+                   float* C, int64_t ldc, int N, FeatCfg cfg, cudaStream_t st) {
+  dim3 grid((unsigned)tiles, (unsigned)((N + cfg.pass - 1) / cfg.pass));
+#define LF_LAUNCH(G_, V_, VEC_)                                                                   \
+  spmm_hyb_kernel<G_, V_, VEC_, MAXB, POL><<<grid, kThreads, 0, st>>>(tbl, A->rows, A->cols, A->vals, B, \
+                                                                     ldb, C, ldc, N, A->row_begin)
+  if (cfg.VEC == 4) {
+    if (cfg.G == 8) LF_LAUNCH(8, 1, 4);
+    else if (cfg.G == 16) LF_LAUNCH(16, 1, 4);
+    else if (cfg.V == 1) LF_LAUNCH(32, 1, 4);
+    else if (cfg.V == 2) LF_LAUNCH(32, 2, 4);
+    else LF_LAUNCH(32, 4, 4);
+  } else {
+    if (cfg.V == 1) LF_LAUNCH(32, 1, 1);
+    else if (cfg.V == 2) LF_LAUNCH(32, 2, 1);
+    else LF_LAUNCH(32, 4, 1);
+  }
+#undef LF_LAUNCH
+  LF_CUDA_CHECK(cudaGetLastError());
+  return LF_OK;
+}
+
+template <int MAXB>
+int launch_hyb(const SpmmTable<MAXB>& tbl, int64_t tiles, const lf_hyb* A, const float* B, int64_t ldb,
+               float* C, int64_t ldc, int N, FeatCfg cfg, cudaStream_t st) {
+  switch (cache_policy()) {
+    case 1: return launch_hyb_pol<MAXB, 1>(tbl, tiles, A, B, ldb, C, ldc, N, cfg, st);
+    case 2: return launch_hyb_pol<MAXB, 2>(tbl, tiles, A, B, ldb, C, ldc, N, cfg, st);
+    default: return launch_hyb_pol<MAXB, 0>(tbl, tiles, A, B, ldb, C, ldc, N, cfg, st);
+  }
+}
+
+int check_hyb(const lf_hyb* A) {
+  LF_REQUIRE(A, "null format descriptor");
+  LF_REQUIRE(A->num_parts >= 1 && A->num_buckets >= 0, "bad partition / bucket count");
+  LF_REQUIRE(A->part_bucket_off && A->ell_rows && A->row_off && A->slot_off, "format host arrays missing");
+  LF_REQUIRE(A->num_buckets == 0 || A->widths, "widths missing");
+  LF_REQUIRE(0 <= A->row_begin && A->row_begin <= A->row_end && A->row_end <= A->num_rows, "bad row range");
+  LF_REQUIRE(A->part_bucket_off[A->num_parts] == A->num_buckets, "num_buckets does not match part_bucket_off");
+  for (int i = 0; i < A->num_buckets; ++i) {
+    const int w = A->widths[i];
+    LF_REQUIRE(w >= 1 && (w & (w - 1)) == 0, "bucket width %d is not a power of two", w);
+    LF_REQUIRE(A->ell_rows[i] >= 0, "negative ELL row count");
+  }
+  return LF_OK;
+}
+
+}  // namespace
+}  // namespace lf
+
+using namespace lf;
+
+extern "C" {
+
+int lf_set_option(int32_t option, int32_t value) {
+  switch (option) {
+    case LF_OPT_SPMM_SLOTS_PER_GROUP:
+      LF_REQUIRE(value >= 8 && value <= (1 << 20), "slots per group %d out of range", value);
+      g_slots_per_group = value;
+      return LF_OK;
+    case LF_OPT_SPMM_CACHE_POLICY:
+      LF_REQUIRE(value >= 0 && value <= 2, "cache policy %d out of range", value);
+      g_cache_policy = value;
+      return LF_OK;
+    default:
+      return fail(LF_ERR_INVALID_ARGUMENT, "unknown option %d", option);
+  }
+}
+
+int lf_spmm_hyb_f32(const lf_hyb* A, const float* B, int64_t ldb, float* C, int64_t ldc, int32_t N,
+                    int32_t flags, void* stream) {
+  if (int s = check_hyb(A)) return s;
+  LF_REQUIRE(N >= 1, "N must be >= 1");
+  LF_REQUIRE(B && C && ldb >= N && ldc >= N, "bad dense operands");
+  LF_REQUIRE(flags == LF_SPMM_OVERWRITE || flags == LF_SPMM_ACCUMULATE, "unknown flags %d", flags);
+  const int64_t total_rows = A->row_off[A->num_buckets];
+  LF_REQUIRE(total_rows == 0 || (A->rows && A->cols && A->vals), "format device arrays missing");
+  cudaStream_t st = (cudaStream_t)stream;
+  const int64_t shard_rows = A->row_end - A->row_begin;
+  if (shard_rows == 0) return LF_OK;
+  const FeatCfg cfg = pick_cfg(B, ldb, C, ldc, N);
+  const bool accumulate = flags == LF_SPMM_ACCUMULATE;
+  const bool all_atomic = accumulate || A->num_parts > 1;
+
+  if (!accumulate) {
+    if (A->num_parts > 1) {
+      LF_CUDA_CHECK(cudaMemset2DAsync(C, sizeof(float) * ldc, 0, sizeof(float) * N, shard_rows, st));
+    } else if (A->num_zero_rows > 0) {
+      LF_REQUIRE(A->zero_rows, "zero_rows missing");
+      const int64_t want = ceil_div64(A->num_zero_rows, kThreads / 32);
+      const int grid = (int)(want > 148 * 16 ? 148 * 16 : want);
+      if (cfg.VEC == 4)
+        zero_rows_kernel<4><<<grid, kThreads, 0, st>>>(A->zero_rows, A->num_zero_rows, C, ldc, N, A->row_begin);
+      else
+        zero_rows_kernel<1><<<grid, kThreads, 0, st>>>(A->zero_rows, A->num_zero_rows, C, ldc, N, A->row_begin);
+      LF_CUDA_CHECK(cudaGetLastError());
+    }
+  }
+
+  // one launch per LF_MAX_BUCKETS_PER_LAUNCH non-empty buckets (one launch in every practical case)
+  const int gpc = kThreads / cfg.G;
+  const int spg = slots_per_group();
+  int i = 0;
+  while (i < A->num_buckets) {
+    static thread_local SpmmTable<LF_MAX_BUCKETS_PER_LAUNCH> big;
+    SpmmTable<16> small;
+    int n = 0;
+    int64_t tiles = 0;
+    for (; i < A->num_buckets && n < LF_MAX_BUCKETS_PER_LAUNCH; ++i) {
+      if (A->ell_rows[i] == 0) continue;
+      BucketDesc d;
+      int wlog = 0;
+      while ((1 << wlog) < A->widths[i]) ++wlog;
+      d.row_off = A->row_off[i];
+      d.slot_off = A->slot_off[i];
+      d.ell_rows = A->ell_rows[i];
+      d.tile_begin = tiles;
+      d.wlog = wlog;
+      d.rows_per_group = (spg >> wlog) > 0 ? (spg >> wlog) : 1;
+      d.force_atomic = all_atomic ? 1 : 0;
+      d.pad_ = 0;
+      tiles += ceil_div64(d.ell_rows, (int64_t)d.rows_per_group * gpc);
+      big.b[n] = d;
+      if (n < 16) small.b[n] = d;
+      ++n;
+    }
+    if (n == 0) break;
+    LF_REQUIRE(tiles < (1ll << 31), "too many thread blocks for one launch");
+    int s;
+    if (n <= 16) {
+      small.n = n; small.pad_ = 0;
+      s = launch_hyb<16>(small, tiles, A, B, ldb, C, ldc, N, cfg, st);
+    } else {
+      big.n = n; big.pad_ = 0;
+      s = launch_hyb<LF_MAX_BUCKETS_PER_LAUNCH>(big, tiles, A, B, ldb, C, ldc, N, cfg, st);
+    }
+    if (s) return s;
+  }
+  return LF_OK;
+}
+
+static size_t host_ws_layout(const lf_hyb* A, int32_t N, size_t off[7]) {
+  const int nb = A->num_buckets;
+  const size_t n_rows = (size_t)A->row_off[nb], n_slots = (size_t)A->slot_off[nb];
+  size_t o = 0;
+  auto take = [&](size_t bytes) { size_t r = o; o = align_up(o + (bytes ? bytes : 1), 256); return r; };
+  off[0] = take(n_rows * 4);                                      // rows
+  off[1] = take(n_slots * 4);                                     // cols
+  off[2] = take(n_slots * 4);                                     // vals
+  off[3] = take((size_t)A->num_zero_rows * 4);                    // zero_rows
+  off[4] = take((size_t)A->num_cols * N * 4);                     // B
+  off[5] = take((size_t)(A->row_end - A->row_begin) * N * 4);     // C
+  off[6] = o;
+  return o;
+}
+
+size_t lf_spmm_hyb_f32_host_workspace_bytes(const lf_hyb* A_host, int32_t N) {
+  if (!A_host || !A_host->row_off || !A_host->slot_off || N < 1) return 0;
+  size_t off[7];
+  return host_ws_layout(A_host, N, off);
+}
+
+int lf_spmm_hyb_f32_host(const lf_hyb* A, const float* B, float* C, int32_t N, int32_t flags,
+                         void* device_workspace, size_t workspace_bytes, void* stream) {
+  if (int s = check_hyb(A)) return s;
+  LF_REQUIRE(B && C && N >= 1 && device_workspace, "bad arguments");
+  size_t off[7];
+  if (workspace_bytes < host_ws_layout(A, N, off)) return fail(LF_ERR_WORKSPACE_TOO_SMALL, "host-call workspace too small");
+  cudaStream_t st = (cudaStream_t)stream;
+  char* ws = (char*)device_workspace;
+  const int nb = A->num_buckets;
+  const size_t n_rows = (size_t)A->row_off[nb], n_slots = (size_t)A->slot_off[nb];
+  const size_t c_bytes = (size_t)(A->row_end - A->row_begin) * N * 4;
+  if (n_rows) LF_CUDA_CHECK(cudaMemcpyAsync(ws + off[0], A->rows, n_rows * 4, cudaMemcpyHostToDevice, st));
+  if (n_slots) {
+    LF_CUDA_CHECK(cudaMemcpyAsync(ws + off[1], A->cols, n_slots * 4, cudaMemcpyHostToDevice, st));
+    LF_CUDA_CHECK(cudaMemcpyAsync(ws + off[2], A->vals, n_slots * 4, cudaMemcpyHostToDevice, st));
+  }
+  if (A->num_zero_rows) LF_CUDA_CHECK(cudaMemcpyAsync(ws + off[3], A->zero_rows, (size_t)A->num_zero_rows * 4, cudaMemcpyHostToDevice, st));
+  LF_CUDA_CHECK(cudaMemcpyAsync(ws + off[4], B, (size_t)A->num_cols * N * 4, cudaMemcpyHostToDevice, st));
+  if (flags == LF_SPMM_ACCUMULATE && c_bytes) LF_CUDA_CHECK(cudaMemcpyAsync(ws + off[5], C, c_bytes, cudaMemcpyHostToDevice, st));
+  lf_hyb dev = *A;
+  dev.rows = (const int32_t*)(ws + off[0]);
+  dev.cols = (const int32_t*)(ws + off[1]);
+  dev.vals = (const float*)(ws + off[2]);
+  dev.mask = nullptr;
+  dev.zero_rows = (const int32_t*)(ws + off[3]);
+  if (int s = lf_spmm_hyb_f32(&dev, (const float*)(ws + off[4]), N, (float*)(ws + off[5]), N, N, flags, st)) return s;
+  if (c_bytes) LF_CUDA_CHECK(cudaMemcpyAsync(C, ws + off[5], c_bytes, cudaMemcpyDeviceToHost, st));
+  LF_CUDA_CHECK(cudaStreamSynchronize(st));
+  return LF_OK;
+}
+
+int lf_spmm_csr_f32(const int64_t* indptr, const int32_t* indices, const float* data, int64_t row_begin,
+                    int64_t row_end, const float* B, int64_t ldb, float* C, int64_t ldc, int32_t N,
+                    void* stream) {
+  LF_REQUIRE(indptr && B && C && N >= 1 && ldb >= N && ldc >= N, "bad arguments");
+  LF_REQUIRE(0 <= row_begin && row_begin <= row_end, "bad row range");
+  if (row_begin == row_end) return LF_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const FeatCfg cfg = pick_cfg(B, ldb, C, ldc, N);
+  const int gpc = kThreads / cfg.G;
+  const int64_t blocks = ceil_div64(row_end - row_begin, gpc);
+  LF_REQUIRE(blocks < (1ll << 31), "row range too large");
+  dim3 grid((unsigned)blocks, (unsigned)((N + cfg.pass - 1) / cfg.pass));
+#define LF_LAUNCH(G_, V_, VEC_) \
+  spmm_csr_kernel<G_, V_, VEC_><<<grid, kThreads, 0, st>>>(indptr, indices, data, row_begin, row_end, B, ldb, C, ldc, N)
+  if (cfg.VEC == 4) {
+    if (cfg.G == 8) LF_LAUNCH(8, 1, 4);
+    else if (cfg.G == 16) LF_LAUNCH(16, 1, 4);
+    else if (cfg.V == 1) LF_LAUNCH(32, 1, 4);
+    else if (cfg.V == 2) LF_LAUNCH(32, 2, 4);
+    else LF_LAUNCH(32, 4, 4);
+  } else {
+    if (cfg.V == 1) LF_LAUNCH(32, 1, 1);
+    else if (cfg.V == 2) LF_LAUNCH(32, 2, 1);
+    else LF_LAUNCH(32, 4, 1);
+  }
+#undef LF_LAUNCH
+  LF_CUDA_CHECK(cudaGetLastError());
+  return LF_OK;
+}
+
+}  // extern "C"

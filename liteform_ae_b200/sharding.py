@@ -1,0 +1,74 @@
+"""Row sharding over the GPUs of one node (one process per GPU, ``torch.distributed``).
+
+The reference runs on device 0 only (playground_pipline/format_algos.py:548).  Rows of A are
+independent in C = A B, so G ranks each own a contiguous, nnz-balanced row range: the bucket
+widths are chosen on the whole matrix, every rank builds the slice of the format for its rows
+(a contiguous slice of every bucket), B is replicated, and each rank writes only its rows of
+C.  The product itself needs no communication; the one collective is the optional all-gather
+of the row blocks of C when the caller wants the full matrix on every rank.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence, Tuple
+
+import numpy as np
+
+
+def split_points_host(indptr: np.ndarray, num_shards: int) -> List[int]:
+    """``cuts[g]`` = first row r with ``indptr[r] >= g * nnz / G`` (what ``lf_shard_rows``
+    computes on the device); ``cuts[0] = 0``, ``cuts[G] = M``."""
+    indptr = np.asarray(indptr, dtype=np.int64)
+    M = len(indptr) - 1
+    nnz = int(indptr[-1] - indptr[0])
+    cuts = [int(np.searchsorted(indptr, int(indptr[0]) + (nnz * g) // num_shards, side="left"))
+            for g in range(num_shards)]
+    return cuts + [M]
+
+
+def my_range(cuts: Sequence[int], rank: int) -> Tuple[int, int]:
+    return int(cuts[rank]), int(cuts[rank + 1])
+
+
+def all_gather_rows(C_local, cuts: Sequence[int], group=None):
+    """Full ``C`` (``cuts[-1]`` rows) on every rank from the per-rank row blocks.
+
+    Row blocks differ in size, NCCL's all-gather does not take ragged inputs: every rank pads
+    its block to the largest one, one ``all_gather`` moves them, and the valid rows are copied
+    out.  Works with the ``nccl`` (GPU) and ``gloo`` (CPU tests) back ends.
+    """
+    import torch
+    import torch.distributed as dist
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    sizes = [int(cuts[g + 1] - cuts[g]) for g in range(world)]
+    assert C_local.shape[0] == sizes[rank], "local block does not match the shard plan"
+    N = C_local.shape[1]
+    biggest = max(sizes)
+    padded = C_local
+    if sizes[rank] != biggest:
+        padded = torch.zeros((biggest, N), dtype=C_local.dtype, device=C_local.device)
+        padded[:sizes[rank]] = C_local
+    bufs = [torch.empty((biggest, N), dtype=C_local.dtype, device=C_local.device) for _ in range(world)]
+    dist.all_gather(bufs, padded.contiguous(), group=group)
+    full = torch.empty((int(cuts[-1]), N), dtype=C_local.dtype, device=C_local.device)
+    for g in range(world):
+        full[cuts[g]:cuts[g + 1]] = bufs[g][:sizes[g]]
+    return full
+
+
+class ShardedSpmm:
+    """Per-rank state of a row-sharded SpMM: the rank's slice of the format and its C block."""
+
+    def __init__(self, csr_dev, bucket_widths, rank: int, world: int, cuts: Optional[Sequence[int]] = None):
+        from . import hyb
+        self.rank, self.world = rank, world
+        self.cuts = list(cuts) if cuts is not None else hyb.shard_rows(csr_dev, world)
+        self.row_range = my_range(self.cuts, rank)
+        self.fmt = hyb.build_hyb_device(csr_dev, bucket_widths, row_range=self.row_range, with_mask=False)
+
+    def spmm(self, B, out=None):
+        from . import hyb
+        return hyb.spmm_hyb(self.fmt, B, out=out)
+
+    def gather(self, C_local, group=None):
+        return all_gather_rows(C_local, self.cuts, group)

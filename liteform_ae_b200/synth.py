@@ -45,8 +45,12 @@ def _distinct_uniform_columns(rng, lens: np.ndarray, K: int):
     ``row * K + col`` (so rows come out contiguous and columns ascending)."""
     M = len(lens)
     lens = np.asarray(lens, dtype=np.int64)
-    keys = np.empty(0, dtype=np.int64)
     need = lens.copy()
+    # rows that want a large share of all columns: rejection would crawl, cut a permutation
+    dense = np.nonzero(lens * 4 > K)[0]
+    dense_keys = [r * K + np.sort(rng.permutation(K)[:lens[r]]).astype(np.int64) for r in dense]
+    keys = np.concatenate(dense_keys) if dense_keys else np.empty(0, dtype=np.int64)
+    need[dense] = 0
     while True:
         total = int(need.sum())
         if total == 0:
