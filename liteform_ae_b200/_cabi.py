@@ -20,6 +20,7 @@ LF_ERR_KERNEL_TIMEOUT = -5
 
 LF_OPT_SPMM_SLOTS_PER_GROUP = 1
 LF_OPT_SPMM_CACHE_POLICY = 2
+LF_OPT_SPMM_MIN_BLOCKS = 3
 LF_SPMM_OVERWRITE = 0
 LF_SPMM_ACCUMULATE = 1
 NUM_WIDTH_CLASSES = 11

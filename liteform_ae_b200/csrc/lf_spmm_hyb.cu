@@ -83,20 +83,113 @@ template <> struct Chunk<1> {
   __device__ __forceinline__ void red(float* p) const { atomicAdd(p, v); }
 };
 
-// G lanes per group, V chunks of VEC floats per lane: one pass covers G*V*VEC features.
-// POL selects cache behaviour: 0 = default loads/stores; 1 = slots, row ids and C use streaming
-// (evict-first) accesses; 2 = as 1, and B rows are loaded with an L2 evict-last policy.
-template <int G, int V, int VEC, int MAXB, int POL>
-__global__ void __launch_bounds__(kThreads)
+// One thread group walks the slots [s0, s1) of whole ELL rows of one bucket.
+//   G lanes per group, V chunks of VEC floats per lane: one pass covers G*V*VEC features.
+//   WC = min(bucket width, 8): ELL rows start every WC slots at the earliest, so the row id has to
+//        be looked at only there (once per batch of 8 gathers when the bucket is 8 or wider).
+//   POL selects cache behaviour: 0 = default loads/stores; 1 = slots, row ids and C use streaming
+//        (evict-first) accesses; 2 = as 1, and B rows are loaded with an L2 evict-last policy.
+// The group stages G (column, value) pairs and row ids in shared memory with one coalesced load
+// each, then broadcasts a pair per gather with a single 64-bit shared load.
+template <int G, int V, int VEC, int WC, int POL>
+__device__ __forceinline__ void walk_slots(const int32_t* __restrict__ rows, const int32_t* __restrict__ cols,
+                                           const float* __restrict__ vals, int wlog, int64_t e0, int64_t e1,
+                                           int64_t ell_rows, bool all_open, const float* __restrict__ B,
+                                           int ldb, float* __restrict__ C, int64_t ldc, int N,
+                                           int64_t row_base, int lane, unsigned gmask, int2* cv, int* rd) {
+  constexpr int U = V == 1 ? 8 : (V == 2 ? 4 : 2);  // gathers in flight per lane (x V chunks)
+  static_assert(G % U == 0 && 8 % U == 0, "unroll must divide the group size and the batch");
+  const int first_row = rows[e0], last_row = rows[e1 - 1];
+  // does the first / last run of equal row ids continue in a neighbouring group?
+  const bool head_open = e0 > 0 && rows[e0 - 1] == first_row;
+  const bool tail_open = e1 < ell_rows && rows[e1] == last_row;
+
+  const int f0 = blockIdx.y * (G * V * VEC) + lane * VEC;
+  bool active[V];
+  Chunk<VEC> acc[V];
+#pragma unroll
+  for (int v = 0; v < V; ++v) {
+    active[v] = f0 + v * G * VEC < N;
+    acc[v].zero();
+  }
+  int cur = first_row;
+  uint64_t keep = 0;
+  if (POL == 2) keep = l2_policy_evict_last();
+
+  auto flush = [&](int row) {
+    const bool open = all_open || (row == first_row && head_open) || (row == last_row && tail_open);
+    float* dst = C + (int64_t)(row - row_base) * ldc + f0;
+#pragma unroll
+    for (int v = 0; v < V; ++v) {
+      if (active[v]) {
+        if (open) acc[v].red(dst + v * G * VEC);
+        else if (POL >= 1) acc[v].store_stream(dst + v * G * VEC);
+        else acc[v].store(dst + v * G * VEC);
+      }
+      acc[v].zero();
+    }
+  };
+
+  const float* __restrict__ Bf = B + f0;
+  const int64_t s0 = e0 << wlog, s1 = e1 << wlog;
+  for (int64_t s = s0; s < s1; s += G) {
+    const int64_t idx = s + lane;
+    const bool in = idx < s1;
+    const int64_t cidx = in ? idx : s1 - 1;
+    const int my_col = POL >= 1 ? __ldcs(cols + cidx) : cols[cidx];
+    const float my_val = in ? (POL >= 1 ? __ldcs(vals + cidx) : vals[cidx]) : 0.f;
+    const int my_rid = rows[cidx >> wlog];
+    __syncwarp(gmask);  // the previous strip has been consumed by every lane of the group
+    cv[lane] = make_int2(my_col, __float_as_int(my_val));
+    rd[lane] = my_rid;
+    __syncwarp(gmask);
+    const int nstrip = (int)min((int64_t)G, s1 - s);
+    for (int t = 0; t < nstrip; t += U) {
+      float val[U];
+      Chunk<VEC> b[U][V];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int2 p = cv[t + u];
+        val[u] = __int_as_float(p.y);
+        const float* src = Bf + (int64_t)p.x * ldb;
+#pragma unroll
+        for (int v = 0; v < V; ++v) {
+          if (val[u] != 0.f && active[v]) {
+            if (POL == 2) b[u][v].load_keep(src + v * G * VEC, keep); else b[u][v].load(src + v * G * VEC);
+          } else {
+            b[u][v].zero();
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (u % WC == 0) {  // an ELL row can only start here
+          const int r = rd[t + u];
+          if (r != cur) {
+            flush(cur);
+            cur = r;
+          }
+        }
+#pragma unroll
+        for (int v = 0; v < V; ++v) acc[v].fma(val[u], b[u][v]);
+      }
+    }
+  }
+  flush(cur);
+}
+
+// All buckets of all partitions in one launch: a thread block looks up its bucket in the table
+// passed as kernel parameter and each of its groups takes a contiguous run of that bucket's ELL rows.
+template <int G, int V, int VEC, int MAXB, int POL, int MINB>
+__global__ void __launch_bounds__(kThreads, MINB)
 spmm_hyb_kernel(const __grid_constant__ SpmmTable<MAXB> tbl, const int32_t* __restrict__ rows_arena,
                 const int32_t* __restrict__ cols_arena, const float* __restrict__ vals_arena,
-                const float* __restrict__ B, int64_t ldb, float* __restrict__ C, int64_t ldc, int N,
+                const float* __restrict__ B, int ldb, float* __restrict__ C, int64_t ldc, int N,
                 int64_t row_base) {
-  constexpr int GPC = kThreads / G;                 // groups per thread block
-  constexpr int U = V == 1 ? 8 : (V == 2 ? 4 : 2);  // gathers in flight per lane (x V chunks)
-  static_assert(G % U == 0, "unroll must divide the group size");
+  constexpr int GPC = kThreads / G;  // groups per thread block
+  __shared__ int2 s_cv[kThreads];
+  __shared__ int s_rd[kThreads];
 
-  // which bucket does this thread block work on?
   const int64_t tile = blockIdx.x;
   int lo = 0, hi = tbl.n;
   while (hi - lo > 1) {
@@ -113,79 +206,19 @@ spmm_hyb_kernel(const __grid_constant__ SpmmTable<MAXB> tbl, const int32_t* __re
   const int32_t* __restrict__ rows = rows_arena + d.row_off;
   const int32_t* __restrict__ cols = cols_arena + d.slot_off;
   const float* __restrict__ vals = vals_arena + d.slot_off;
-
-  // does the first / last run of equal row ids continue in a neighbouring group?
-  const int first_row = rows[e0], last_row = rows[e1 - 1];
   const bool all_open = d.force_atomic != 0;
-  const bool head_open = e0 > 0 && rows[e0 - 1] == first_row;
-  const bool tail_open = e1 < d.ell_rows && rows[e1] == last_row;
-
-  const int f0 = blockIdx.y * (G * V * VEC) + lane * VEC;
-  bool active[V];
-#pragma unroll
-  for (int v = 0; v < V; ++v) active[v] = f0 + v * G * VEC < N;
-
-  Chunk<VEC> acc[V];
-#pragma unroll
-  for (int v = 0; v < V; ++v) acc[v].zero();
-  int cur = first_row;
-
-  auto flush = [&](int row) {
-    const bool open = all_open || (row == first_row && head_open) || (row == last_row && tail_open);
-    float* dst = C + (int64_t)(row - row_base) * ldc + f0;
-#pragma unroll
-    for (int v = 0; v < V; ++v) {
-      if (active[v]) {
-        if (open) acc[v].red(dst + v * G * VEC);
-        else if (POL >= 1) acc[v].store_stream(dst + v * G * VEC);
-        else acc[v].store(dst + v * G * VEC);
-      }
-      acc[v].zero();
-    }
-  };
-
-  uint64_t keep = 0;
-  if (POL == 2) keep = l2_policy_evict_last();
-  const int64_t s0 = e0 << wlog, s1 = e1 << wlog;
-  for (int64_t s = s0; s < s1; s += G) {
-    const int64_t idx = s + lane;
-    const bool in = idx < s1;
-    const int64_t cidx = in ? idx : s1 - 1;
-    const int my_col = POL >= 1 ? __ldcs(cols + cidx) : cols[cidx];
-    const float my_val = in ? (POL >= 1 ? __ldcs(vals + cidx) : vals[cidx]) : 0.f;
-    const int my_rid = rows[cidx >> wlog];
-    const int nstrip = (int)min((int64_t)G, s1 - s);
-    for (int t = 0; t < nstrip; t += U) {
-      int rid[U];
-      float val[U];
-      Chunk<VEC> b[U][V];
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const int c = __shfl_sync(gmask, my_col, t + u, G);
-        val[u] = __shfl_sync(gmask, my_val, t + u, G);
-        rid[u] = __shfl_sync(gmask, my_rid, t + u, G);
-        const float* src = B + (int64_t)c * ldb + f0;
-#pragma unroll
-        for (int v = 0; v < V; ++v) {
-          if (val[u] != 0.f && active[v]) {
-            if (POL == 2) b[u][v].load_keep(src + v * G * VEC, keep); else b[u][v].load(src + v * G * VEC);
-          } else {
-            b[u][v].zero();
-          }
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        if (rid[u] != cur) {
-          flush(cur);
-          cur = rid[u];
-        }
-#pragma unroll
-        for (int v = 0; v < V; ++v) acc[v].fma(val[u], b[u][v]);
-      }
-    }
+  int2* cv = s_cv + g * G;
+  int* rd = s_rd + g * G;
+#define LF_WALK(WC_)                                                                                     \
+  walk_slots<G, V, VEC, WC_, POL>(rows, cols, vals, wlog, e0, e1, d.ell_rows, all_open, B, ldb, C, ldc, \
+                                  N, row_base, lane, gmask, cv, rd)
+  switch (wlog) {
+    case 0: LF_WALK(1); break;
+    case 1: LF_WALK(2); break;
+    case 2: LF_WALK(4); break;
+    default: LF_WALK(8); break;
   }
-  flush(cur);
+#undef LF_WALK
 }
 
 // Rows that no single ELL row owns are cleared before the accumulating launch.
@@ -285,27 +318,37 @@ int slots_per_group() {
   if (!g_slots_per_group) {
     const char* e = getenv("LF_SPMM_SLOTS_PER_GROUP");
     int v = e ? atoi(e) : 0;
-    g_slots_per_group = (v >= 8 && v <= (1 << 20)) ? v : 128;
+    g_slots_per_group = (v >= 8 && v <= (1 << 20)) ? v : 256;
   }
   return g_slots_per_group;
+}
+
+int g_min_blocks = 0;
+int min_blocks() {
+  if (!g_min_blocks) {
+    const char* e = getenv("LF_SPMM_MIN_BLOCKS");
+    const int v = e ? atoi(e) : 0;
+    g_min_blocks = (v >= 2 && v <= 4) ? v : 3;
+  }
+  return g_min_blocks;
 }
 
 int cache_policy() {
   if (g_cache_policy < 0) {
     const char* e = getenv("LF_SPMM_POLICY");
-    const int v = e ? atoi(e) : 0;
-    g_cache_policy = (v >= 0 && v <= 2) ? v : 0;
+    const int v = e ? atoi(e) : 1;
+    g_cache_policy = (v >= 0 && v <= 2) ? v : 1;
   }
   return g_cache_policy;
 }
 
-template <int MAXB, int POL>
+template <int MAXB, int POL, int MINB>
 int launch_hyb_pol(const SpmmTable<MAXB>& tbl, int64_t tiles, const lf_hyb* A, const float* B, int64_t ldb,
                    float* C, int64_t ldc, int N, FeatCfg cfg, cudaStream_t st) {
   dim3 grid((unsigned)tiles, (unsigned)((N + cfg.pass - 1) / cfg.pass));
-#define LF_LAUNCH(G_, V_, VEC_)                                                                   \
-  spmm_hyb_kernel<G_, V_, VEC_, MAXB, POL><<<grid, kThreads, 0, st>>>(tbl, A->rows, A->cols, A->vals, B, \
-                                                                     ldb, C, ldc, N, A->row_begin)
+#define LF_LAUNCH(G_, V_, VEC_)                                                                          \
+  spmm_hyb_kernel<G_, V_, VEC_, MAXB, POL, MINB><<<grid, kThreads, 0, st>>>(tbl, A->rows, A->cols, A->vals, \
+                                                                           B, (int)ldb, C, ldc, N, A->row_begin)
   if (cfg.VEC == 4) {
     if (cfg.G == 8) LF_LAUNCH(8, 1, 4);
     else if (cfg.G == 16) LF_LAUNCH(16, 1, 4);
@@ -325,11 +368,13 @@ int launch_hyb_pol(const SpmmTable<MAXB>& tbl, int64_t tiles, const lf_hyb* A, c
 template <int MAXB>
 int launch_hyb(const SpmmTable<MAXB>& tbl, int64_t tiles, const lf_hyb* A, const float* B, int64_t ldb,
                float* C, int64_t ldc, int N, FeatCfg cfg, cudaStream_t st) {
-  switch (cache_policy()) {
-    case 1: return launch_hyb_pol<MAXB, 1>(tbl, tiles, A, B, ldb, C, ldc, N, cfg, st);
-    case 2: return launch_hyb_pol<MAXB, 2>(tbl, tiles, A, B, ldb, C, ldc, N, cfg, st);
-    default: return launch_hyb_pol<MAXB, 0>(tbl, tiles, A, B, ldb, C, ldc, N, cfg, st);
-  }
+  const int pol = cache_policy(), minb = min_blocks();
+#define LF_CASE(P_, M_) if (pol == P_ && minb == M_) return launch_hyb_pol<MAXB, P_, M_>(tbl, tiles, A, B, ldb, C, ldc, N, cfg, st)
+  LF_CASE(0, 2); LF_CASE(0, 3); LF_CASE(0, 4);
+  LF_CASE(1, 2); LF_CASE(1, 3); LF_CASE(1, 4);
+  LF_CASE(2, 2); LF_CASE(2, 3); LF_CASE(2, 4);
+#undef LF_CASE
+  return fail(LF_ERR_INVALID_ARGUMENT, "bad tuning state");
 }
 
 int check_hyb(const lf_hyb* A) {
@@ -364,6 +409,10 @@ int lf_set_option(int32_t option, int32_t value) {
       LF_REQUIRE(value >= 0 && value <= 2, "cache policy %d out of range", value);
       g_cache_policy = value;
       return LF_OK;
+    case LF_OPT_SPMM_MIN_BLOCKS:
+      LF_REQUIRE(value >= 2 && value <= 4, "min blocks %d out of range", value);
+      g_min_blocks = value;
+      return LF_OK;
     default:
       return fail(LF_ERR_INVALID_ARGUMENT, "unknown option %d", option);
   }
@@ -373,7 +422,7 @@ int lf_spmm_hyb_f32(const lf_hyb* A, const float* B, int64_t ldb, float* C, int6
                     int32_t flags, void* stream) {
   if (int s = check_hyb(A)) return s;
   LF_REQUIRE(N >= 1, "N must be >= 1");
-  LF_REQUIRE(B && C && ldb >= N && ldc >= N, "bad dense operands");
+  LF_REQUIRE(B && C && ldb >= N && ldc >= N && ldb < (1ll << 31), "bad dense operands");
   LF_REQUIRE(flags == LF_SPMM_OVERWRITE || flags == LF_SPMM_ACCUMULATE, "unknown flags %d", flags);
   const int64_t total_rows = A->row_off[A->num_buckets];
   LF_REQUIRE(total_rows == 0 || (A->rows && A->cols && A->vals), "format device arrays missing");

@@ -171,7 +171,12 @@ def test_full_size_linearity_and_checksum(cuda_device):
     got = C.double().sum(dim=0).cpu().numpy()
     np.testing.assert_allclose(got, want, rtol=1e-6, atol=1e-3)
     C2 = hyb.spmm_hyb(fmt, 2.0 * Bd)
-    assert torch.equal(C2, 2.0 * C)          # scaling by 2 is exact in floating point
+    # scaling B by 2 is exact in floating point; rows owned by one ELL row are summed in a fixed
+    # order and must scale bit for bit, rows assembled with atomics may differ in the last bits
+    owned = torch.ones(csr.shape[0], dtype=torch.bool, device=cuda_device)
+    owned[fmt.zero_rows.long()] = False
+    assert torch.equal(C2[owned], 2.0 * C[owned])
+    torch.testing.assert_close(C2[~owned], 2.0 * C[~owned], rtol=1e-5, atol=1e-6)
     rng = np.random.default_rng(0)
     pick = np.unique(np.concatenate([rng.integers(0, csr.shape[0], 2000), np.argsort(np.diff(csr.indptr))[-8:]]))
     sub = synth.Csr(np.concatenate([[0], np.cumsum(np.diff(csr.indptr)[pick])]),
