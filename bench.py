@@ -187,43 +187,174 @@ def run_reference(args, rank, world):
 
 
 # ------------------------------------------------------------------------------------------------
+class HybProblem:
+    """Composed-format path: statistics + width search on the whole matrix, per-rank format slice."""
+    kernel = "spmm_hyb_kernel"
+
+    def __init__(self, args, rank, world, dev):
+        import torch
+        from liteform_ae_b200 import hyb, width_search
+        from liteform_ae_b200.sharding import my_range
+        self.hyb, self.torch, self.dev = hyb, torch, dev
+        desc, gen, full_rows, N0 = WORKLOADS[args.workload]
+        self.N = N = args.feat or N0
+        self.P = P = args.parts
+        t0 = time.perf_counter()
+        self.csr = csr = gen(args.rows or full_rows)
+        self.M, self.K = csr.shape
+        self.B_host = synth.dense_features(self.K, N, args.seed)
+        self.t_gen = time.perf_counter() - t0
+        self.nnz = csr.nnz
+        d_csr = hyb.DeviceCsr.from_host(csr.indptr, csr.indices, csr.data, csr.shape, dev)
+        torch.cuda.synchronize(dev)
+        t0 = time.perf_counter()
+        stats, hist = hyb.hyb_stats(d_csr, P)
+        self.widths = width_search.search_from_stats(stats, hist, N, P)
+        torch.cuda.synchronize(dev)
+        self.t_search = time.perf_counter() - t0
+        cuts = hyb.shard_rows(d_csr, world)
+        self.r0, self.r1 = my_range(cuts, rank)
+        t0 = time.perf_counter()
+        self.fmt = hyb.build_hyb_device(d_csr, self.widths, row_range=(self.r0, self.r1), with_mask=False)
+        torch.cuda.synchronize(dev)
+        self.t_build = time.perf_counter() - t0
+        del d_csr
+        self.B = torch.from_numpy(self.B_host).to(dev)
+        self.C = torch.empty((self.r1 - self.r0, N), dtype=torch.float32, device=dev)
+        self.launches_per_step = 1 + (1 if (P == 1 and self.fmt.num_zero_rows > 0) else 0) + (1 if P > 1 else 0)
+        self.dtype = "f32"
+        self.config = {"workload": f"{args.workload}: {desc}", "format": "hyb (composed ELL)", "rows": self.M,
+                       "cols": self.K, "nnz": self.nnz, "N": N, "num_parts": P, "bucket_widths": self.widths,
+                       "sharding": f"rows, nnz-balanced, {world} rank(s), B replicated, C left sharded",
+                       "l2": "inputs exceed L2 (B %.0f MB + format %.0f MB per rank); no flush between steps" % (
+                           self.B_host.nbytes / 1e6, (self.fmt.cols.numel() * 8 + self.fmt.rows.numel() * 4) / 1e6)}
+        self.extra = {"format_build_ms": self.t_build * 1e3, "width_search_ms": self.t_search * 1e3,
+                      "generate_s": self.t_gen, "padded_slots": self.fmt.total_slots, "zero_rows": self.fmt.num_zero_rows}
+
+    def step(self):
+        self.hyb.spmm_hyb(self.fmt, self.B, out=self.C)
+
+    def bytes_models(self):
+        csr, r0, r1 = self.csr, self.r0, self.r1
+        my_nnz = int(csr.indptr[r1] - csr.indptr[r0])
+        touched = int(np.unique(csr.indices[csr.indptr[r0]:csr.indptr[r1]]).size)
+        return compulsory_bytes(my_nnz, r1 - r0, touched, self.N), gather_bytes(my_nnz, r1 - r0, self.N)
+
+    def prepare_e2e(self):
+        torch, hyb, fmt = self.torch, self.hyb, self.fmt
+        r_nd, c_nd, _, v_nd = fmt.to_nested_numpy(with_values=True)
+        ell_rows, row_off, slot_off, h_rows, h_cols, h_vals, h_zero = hyb.HybFormat.host_layout(
+            fmt.bucket_widths, r_nd, c_nd, v_nd, self.M, (self.r0, self.r1))
+        del r_nd, c_nd, v_nd
+        pin = lambda a: torch.from_numpy(a).pin_memory().numpy()
+        self.h = tuple(pin(a) for a in (h_rows, h_cols, h_vals, h_zero))
+        self.Bp = pin(self.B_host)
+        self.Cp = torch.empty((self.r1 - self.r0, self.N), dtype=torch.float32).pin_memory().numpy()
+        self.host_fmt = hyb.HybFormat((self.M, self.K), (self.r0, self.r1), fmt.bucket_widths, ell_rows, row_off,
+                                      slot_off, None, None, None, None, self.h[3])
+        self.ws = torch.empty(hyb.host_workspace_bytes(self.host_fmt, self.N), dtype=torch.uint8, device=self.dev)
+        h2d = sum(a.nbytes for a in self.h) + self.Bp.nbytes
+        return h2d, self.Cp.nbytes, "lf_spmm_hyb_f32_host (pinned host format + B in, C out, per rank)"
+
+    def e2e_step(self):
+        self.hyb.spmm_hyb_host(self.h, self.host_fmt, self.Bp, self.Cp, self.ws)
+
+    def e2e_result(self):
+        return self.Cp
+
+    def cpu_matrix(self):
+        return self.csr.toscipy()
+
+
+class BsrProblem:
+    """8x8 block path (config 5): block rows split evenly over the ranks (every block row holds
+    the same number of blocks), B replicated."""
+
+    def __init__(self, args, rank, world, dev):
+        import torch
+        from liteform_ae_b200 import bsr
+        self.bsr, self.torch, self.dev = bsr, torch, dev
+        desc, _, full_rows, N0 = WORKLOADS[args.workload]
+        self.N = N = args.feat or N0
+        t0 = time.perf_counter()
+        indptr, indices, blocks, shape = synth.banded_blocks(M=args.rows or full_rows)
+        self.M, self.K = shape
+        self.B_host = synth.dense_features(self.K, N, args.seed)
+        self.t_gen = time.perf_counter() - t0
+        self.indptr, self.indices, self.blocks = indptr, indices, blocks
+        self.nnz = int(blocks.size)
+        Mb = self.M // 8
+        self.r0, self.r1 = (Mb * rank) // world, (Mb * (rank + 1)) // world   # block rows
+        self.tdt = {"f32": torch.float32, "bf16": torch.bfloat16, "f16": torch.float16}[args.dtype]
+        self.dtype = args.dtype
+        self.kernel = "bsr8_spmm_f32_kernel" if args.dtype == "f32" else "bsr8_spmm_16bit_kernel"
+        name = {"f32": "float32", "bf16": "bfloat16", "f16": "float16"}[args.dtype]
+        self.a = bsr.DeviceBsr8.from_arrays(indptr, indices, blocks, shape, name, dev)
+        self.B = torch.from_numpy(self.B_host).to(dev).to(self.tdt)
+        self.C = torch.empty(((self.r1 - self.r0) * 8, N), dtype=torch.float32, device=dev)
+        self.launches_per_step = 1
+        eb = 4 if args.dtype == "f32" else 2
+        self.eb = eb
+        self.config = {"workload": f"{args.workload}: {desc}", "format": "bsr 8x8", "rows": self.M, "cols": self.K,
+                       "nnz": self.nnz, "N": N, "input_dtype": args.dtype, "accumulate": "f32",
+                       "sharding": f"block rows, even split, {world} rank(s), B replicated, C left sharded",
+                       "l2": "inputs exceed L2 (A %.0f MB + B %.0f MB per rank); no flush between steps" % (
+                           self.nnz * eb / 1e6 / world, self.B_host.size * eb / 1e6)}
+        self.extra = {"generate_s": self.t_gen}
+
+    def step(self):
+        self.bsr.spmm_bsr8(self.a, self.B, out=self.C, block_row_range=(self.r0, self.r1))
+
+    def bytes_models(self):
+        nb = int(self.indptr[self.r1] - self.indptr[self.r0])
+        rows = (self.r1 - self.r0) * 8
+        touched = int(np.unique(self.indices[self.indptr[self.r0]:self.indptr[self.r1]]).size) * 8
+        comp = nb * 64 * self.eb + 4 * nb + 8 * (self.r1 - self.r0 + 1) + touched * self.N * self.eb + rows * self.N * 4
+        gath = nb * 64 * self.eb + 4 * nb + 8 * (self.r1 - self.r0 + 1) + nb * 8 * self.N * self.eb + rows * self.N * 4
+        return comp, gath
+
+    def prepare_e2e(self):
+        torch = self.torch
+        s, e = int(self.indptr[self.r0]), int(self.indptr[self.r1])
+        conv = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(self.tdt).pin_memory()
+        self.h_ptr = torch.from_numpy((self.indptr[self.r0:self.r1 + 1] - s).astype(np.int64)).pin_memory()
+        self.h_idx = torch.from_numpy(self.indices[s:e].astype(np.int32)).pin_memory()
+        self.h_blk = conv(self.blocks[s:e])
+        self.h_B = conv(self.B_host)
+        self.h_C = torch.empty(((self.r1 - self.r0) * 8, self.N), dtype=torch.float32).pin_memory()
+        self.d_ptr = torch.empty_like(self.h_ptr, device=self.dev)
+        self.d_idx = torch.empty_like(self.h_idx, device=self.dev)
+        self.d_blk = torch.empty_like(self.h_blk, device=self.dev)
+        self.d_B = torch.empty_like(self.h_B, device=self.dev)
+        self.d_C = torch.empty_like(self.h_C, device=self.dev)
+        h2d = sum(t.numel() * t.element_size() for t in (self.h_ptr, self.h_idx, self.h_blk, self.h_B))
+        return h2d, self.h_C.numel() * 4, "spmm_bsr8 on buffers copied from/to pinned host memory every step"
+
+    def e2e_step(self):
+        for d, h in ((self.d_ptr, self.h_ptr), (self.d_idx, self.h_idx), (self.d_blk, self.h_blk), (self.d_B, self.h_B)):
+            d.copy_(h, non_blocking=True)
+        a = self.bsr.DeviceBsr8(self.d_ptr, self.d_idx, self.d_blk, ((self.r1 - self.r0) * 8, self.K))
+        self.bsr.spmm_bsr8(a, self.d_B, out=self.d_C)
+        self.h_C.copy_(self.d_C, non_blocking=True)
+        self.torch.cuda.current_stream().synchronize()
+
+    def e2e_result(self):
+        return self.h_C.numpy()
+
+    def cpu_matrix(self):
+        import scipy.sparse as sp
+        return sp.bsr_matrix((self.blocks, self.indices, self.indptr), shape=(self.M, self.K)).tocsr()
+
+
 def run_ours(args, rank, local_rank, world):
     import torch
     import torch.distributed as dist
 
-    from liteform_ae_b200 import hyb, width_search
-    from liteform_ae_b200.sharding import my_range
-
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
-    desc, gen, full_rows, N0 = WORKLOADS[args.workload]
-    rows = args.rows or full_rows
-    N = args.feat or N0
-    P = args.parts
-
-    t_gen = time.perf_counter()
-    csr = gen(rows)
-    M, K = csr.shape
-    B_host = synth.dense_features(K, N, args.seed)
-    t_gen = time.perf_counter() - t_gen
-
-    d_csr = hyb.DeviceCsr.from_host(csr.indptr, csr.indices, csr.data, csr.shape, dev)
-    torch.cuda.synchronize(dev)
-    t0 = time.perf_counter()
-    stats, hist = hyb.hyb_stats(d_csr, P)
-    widths = width_search.search_from_stats(stats, hist, N, P)
-    torch.cuda.synchronize(dev)
-    t_search = time.perf_counter() - t0
-    cuts = hyb.shard_rows(d_csr, world)
-    r0, r1 = my_range(cuts, rank)
-    t0 = time.perf_counter()
-    fmt = hyb.build_hyb_device(d_csr, widths, row_range=(r0, r1), with_mask=False)
-    torch.cuda.synchronize(dev)
-    t_build = time.perf_counter() - t0
-
-    B = torch.from_numpy(B_host).to(dev)
-    C = torch.empty((r1 - r0, N), dtype=torch.float32, device=dev)
-    launches_per_step = 1 + (1 if (P == 1 and fmt.num_zero_rows > 0) else 0) + (1 if P > 1 else 0)
+    use_bsr = args.format == "bsr8" or (args.format == "auto" and args.workload == "blocks")
+    prob = (BsrProblem if use_bsr else HybProblem)(args, rank, world, dev)
+    N = prob.N
 
     def barrier():
         if world > 1:
@@ -233,13 +364,13 @@ def run_ours(args, rank, local_rank, world):
     sampler = ClockSampler(physical_gpu_index(local_rank))
     sampler.start()
     for _ in range(args.warmup):
-        hyb.spmm_hyb(fmt, B, out=C)
+        prob.step()
     barrier()
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
     t_wall0 = time.perf_counter()
     ev[0].record()
     for i in range(args.steps):
-        hyb.spmm_hyb(fmt, B, out=C)
+        prob.step()
         ev[i + 1].record()
     barrier()
     t_wall1 = time.perf_counter()
@@ -252,91 +383,75 @@ def run_ours(args, rank, local_rank, world):
     total_ms_max = float(t.item())
     clocks = sampler.summary(t_wall0, t_wall1)
 
-    # ---- end to end: host buffers in, host buffer out, through the host-memory C entry point ----
-    e2e = None
+    # ---- end to end: host buffers in, host buffer out, copies inside the timed region ----------
     try:
         if args.no_e2e:
             raise RuntimeError("skipped (--no-e2e)")
-        r_nd, c_nd, _, v_nd = fmt.to_nested_numpy(with_values=True)
-        ell_rows, row_off, slot_off, h_rows, h_cols, h_vals, h_zero = hyb.HybFormat.host_layout(
-            fmt.bucket_widths, r_nd, c_nd, v_nd, M, (r0, r1))
-        del r_nd, c_nd, v_nd
-        pin = lambda a: torch.from_numpy(a).pin_memory().numpy()
-        h_rows, h_cols, h_vals, h_zero, Bp = pin(h_rows), pin(h_cols), pin(h_vals), pin(h_zero), pin(B_host)
-        Cp = torch.empty((r1 - r0, N), dtype=torch.float32).pin_memory().numpy()
-        host_fmt = hyb.HybFormat((M, K), (r0, r1), fmt.bucket_widths, ell_rows, row_off, slot_off,
-                                 None, None, None, None, h_zero)
-        ws = torch.empty(hyb.host_workspace_bytes(host_fmt, N), dtype=torch.uint8, device=dev)
+        h2d, d2h, call = prob.prepare_e2e()
         e2e_steps = max(3, min(args.steps, 20))
         for _ in range(2):
-            hyb.spmm_hyb_host((h_rows, h_cols, h_vals, h_zero), host_fmt, Bp, Cp, ws)
+            prob.e2e_step()
         barrier()
         t0 = time.perf_counter()
         for _ in range(e2e_steps):
-            hyb.spmm_hyb_host((h_rows, h_cols, h_vals, h_zero), host_fmt, Bp, Cp, ws)
+            prob.e2e_step()
         barrier()
         te = torch.tensor([(time.perf_counter() - t0) / e2e_steps], dtype=torch.float64, device=dev)
         if world > 1:
             dist.all_reduce(te, op=dist.ReduceOp.MAX)
-        h2d = h_rows.nbytes + h_cols.nbytes + h_vals.nbytes + h_zero.nbytes + Bp.nbytes
-        d2h = Cp.nbytes
-        e2e = {"value": 2.0 * csr.nnz * N / float(te.item()) / 1e9, "unit": UNIT,
+        e2e = {"value": 2.0 * prob.nnz * N / float(te.item()) / 1e9, "unit": UNIT,
                "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
-               "ms_per_step": float(te.item()) * 1e3, "steps": e2e_steps,
-               "call": "lf_spmm_hyb_f32_host (pinned host format + B in, C out, per rank)"}
-        check = np.abs(Cp - C.cpu().numpy()).max()
-        e2e["max_abs_diff_vs_resident_run"] = float(check)
-        del ws
+               "ms_per_step": float(te.item()) * 1e3, "steps": e2e_steps, "call": call,
+               "max_abs_diff_vs_resident_run": float(np.abs(prob.e2e_result() - prob.C.cpu().numpy()).max())}
     except Exception as exc:  # keep the device-resident numbers, say what went wrong
         e2e = {"value": None, "unit": UNIT, "error": repr(exc)}
 
     if rank != 0:
         return
     peak, peak_kind = measured_peak_gbs()
-    my_nnz = int(csr.indptr[r1] - csr.indptr[r0])
-    touched = int(np.unique(csr.indices[csr.indptr[r0]:csr.indptr[r1]]).size)
     launch_ms = statistics.fmean(step_ms)
-    alg = compulsory_bytes(my_nnz, r1 - r0, touched, N)
+    alg, gath = prob.bytes_models()
     achieved = alg / (launch_ms * 1e-3) / 1e9
+    key = (args.workload, "bsr8" if use_bsr else "hyb", prob.dtype, N, args.parts, world)
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": TRAFFIC_BYTES_PER_LAUNCH.get((args.workload, N, P, world)),
-                "peak_kind": f"of {peak_kind}", "kernel": "spmm_hyb_kernel",
+                "traffic": TRAFFIC_BYTES_PER_LAUNCH.get(key),
+                "peak_kind": f"of {peak_kind}", "kernel": prob.kernel,
                 "algorithmic_bytes_per_launch": int(alg), "launch_ms": launch_ms,
                 "launch_ms_median": statistics.median(step_ms),
-                "gather_model_bytes_per_launch": int(gather_bytes(my_nnz, r1 - r0, N)),
-                "gather_model_gbs": gather_bytes(my_nnz, r1 - r0, N) / (launch_ms * 1e-3) / 1e9}
+                "gather_model_bytes_per_launch": int(gath),
+                "gather_model_gbs": gath / (launch_ms * 1e-3) / 1e9}
+    if roofline["traffic"]:
+        roofline["dram_gbs_from_traffic"] = roofline["traffic"] / (launch_ms * 1e-3) / 1e9
 
     cpu = None
     if world == 1 and not args.no_cpu:
-        A = csr.toscipy()
-        gf, t_pass, used_rows, used_nnz, passes = time_cpu(A, B_host, 1, 12.0, 2)
+        A = prob.cpu_matrix()
+        gf, t_pass, used_rows, used_nnz, passes = time_cpu(A, prob.B_host, 1, 12.0, 2)
         cpu = {"value": gf, "unit": UNIT, "cores": 1, "kind": "port",
-               "sample": f"scipy csr @ dense (float32), first {used_rows} of {M} rows ({used_nnz} nnz), median of {passes} passes, {t_pass:.2f} s per pass"}
+               "sample": f"scipy csr @ dense (float32), first {used_rows} of {prob.M} rows ({used_nnz} nnz), median of {passes} passes, {t_pass:.2f} s per pass"}
         threads = os.cpu_count() or 1
         if threads > 1:
-            gfm, tm, ur, un, ps = time_cpu(A, B_host, threads, 6.0, 2)
+            gfm, tm, ur, un, ps = time_cpu(A, prob.B_host, threads, 6.0, 2)
             cpu["all_cores"] = {"value": gfm, "cores": threads, "sample": f"{ur} rows split over {threads} threads, {tm:.2f} s per pass"}
 
     line = {
-        "metric": METRIC, "value": 2.0 * csr.nnz * N * args.steps / (total_ms_max * 1e-3) / 1e9, "unit": UNIT,
+        "metric": METRIC, "value": 2.0 * prob.nnz * N * args.steps / (total_ms_max * 1e-3) / 1e9, "unit": UNIT,
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms_max / args.steps,
-        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
-        "data": "synthetic (seeded, numpy default_rng)",
-        "config": {"workload": f"{args.workload}: {desc}", "rows": M, "cols": K, "nnz": csr.nnz, "N": N,
-                   "num_parts": P, "bucket_widths": widths, "sharding": f"rows, nnz-balanced, {world} rank(s), B replicated, C left sharded",
-                   "l2": "inputs exceed L2 (B %.0f MB + format %.0f MB per rank); no flush between steps" % (
-                       B_host.nbytes / 1e6, (fmt.cols.numel() * 8 + fmt.rows.numel() * 4) / 1e6)},
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": prob.dtype,
+        "data": "synthetic (seeded, numpy default_rng)", "config": prob.config,
         "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks,
-        "gpu_launches": launches_per_step * args.steps,
-        "format_build_ms": t_build * 1e3, "width_search_ms": t_search * 1e3, "generate_s": t_gen,
-        "padded_slots": fmt.total_slots, "zero_rows": fmt.num_zero_rows,
+        "gpu_launches": prob.launches_per_step * args.steps,
     }
+    line.update(prob.extra)
     print(json.dumps(line), flush=True)
 
 
-# DRAM bytes (read + write) of one spmm_hyb_kernel launch taken from the ncu captures summarised
-# under profiles/; keyed by (workload, N, num_parts, n_gpus).  Absent entries are reported as null.
-TRAFFIC_BYTES_PER_LAUNCH = {}
+# DRAM bytes (read + write) of one launch of the dominant kernel, taken from the ncu captures
+# summarised under profiles/; keyed by (workload, format, dtype, N, num_parts, n_gpus).  Absent
+# entries are reported as null.
+TRAFFIC_BYTES_PER_LAUNCH = {
+    ("powerlaw", "hyb", "f32", 128, 1, 1): 3123957760 + 543622144,
+}
 
 
 def main():
@@ -350,6 +465,9 @@ def main():
     ap.add_argument("--feat", type=int, default=0, help="override the feature width N")
     ap.add_argument("--parts", type=int, default=1, help="number of column partitions")
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--format", default="auto", choices=["auto", "hyb", "bsr8"],
+                    help="auto: 8x8 block kernels for the block workload, composed format otherwise")
+    ap.add_argument("--dtype", default="f32", choices=["f32", "bf16", "f16"], help="input type of the block path")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-memory end-to-end leg (profiling runs)")
     args = ap.parse_args()

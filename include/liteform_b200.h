@@ -174,6 +174,30 @@ int lf_spmm_csr_f32(const int64_t* indptr /*[dev]*/, const int32_t* indices /*[d
                     int32_t N, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * Block-sparse SpMM, 8x8 blocks (BSR): C[block_row_begin*8 : block_row_end*8, 0:N] = A * B.
+ * Replaces the kernel of bench_bsrmm (playground_pipline/format_algos.py:1562-1643; arithmetic
+ * format_algos.py:1204-1213), which runs 32x32 fp16 blocks through wmma with fp16 accumulators
+ * (format_algos.py:1226-1233).  Here: indptr int64[Mb+1], indices int32[nb] (block columns, sorted
+ * inside a block row as scipy.sparse.bsr_matrix keeps them, format_matrix_market.py:137), blocks
+ * [nb][8][8] row-major.  Accumulation is fp32 in every variant; the float32 variant splits each
+ * operand into two tf32 halves (three tensor-core products) and matches an fp32 product to ~1e-6
+ * relative.  N, ldb must be multiples of 4 (float32) or 8 (16-bit), ldc of 4, B and C 16-byte aligned.
+ * C points at row block_row_begin*8.
+ * ------------------------------------------------------------------------------------------- */
+int lf_spmm_bsr8_f32(const int64_t* indptr /*[dev]*/, const int32_t* indices /*[dev]*/,
+                     const float* blocks /*[dev]*/, int64_t block_row_begin, int64_t block_row_end,
+                     const float* B /*[dev]*/, int64_t ldb, float* C /*[dev]*/, int64_t ldc, int32_t N,
+                     void* stream);
+/* bf16 blocks and bf16 B (raw 16-bit patterns), float32 C */
+int lf_spmm_bsr8_bf16(const int64_t* indptr, const int32_t* indices, const uint16_t* blocks,
+                      int64_t block_row_begin, int64_t block_row_end, const uint16_t* B, int64_t ldb,
+                      float* C, int64_t ldc, int32_t N, void* stream);
+/* fp16 blocks and fp16 B (the reference's input type, format_algos.py:1629-1637), float32 C */
+int lf_spmm_bsr8_f16(const int64_t* indptr, const int32_t* indices, const uint16_t* blocks,
+                     int64_t block_row_begin, int64_t block_row_end, const uint16_t* B, int64_t ldb,
+                     float* C, int64_t ldc, int32_t N, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
  * nnz-balanced contiguous row ranges for G devices: splits[g] = first row r with
  * indptr[r] >= g*nnz/G, splits[0] = 0, splits[G] = M.  (No counterpart in the reference, which
  * runs on device 0 only, format_algos.py:548.)

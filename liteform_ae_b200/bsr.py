@@ -1,0 +1,96 @@
+"""Block-sparse (8x8 BSR) matrices in device memory and their SpMM.
+
+The reference converts the graph with SciPy (``MTX.tobsr_with_padding``,
+playground_pipline/format_matrix_market.py:116-138, block size 32, fp16) and times a generated
+wmma kernel (``bench_bsrmm``, playground_pipline/format_algos.py:1562-1643).  Here the format
+stays SciPy's (``indptr``, sorted ``indices``, dense ``data[nb, R, C]``), re-blocked to 8x8 on
+the host when it comes in coarser, and the product runs on ``lf_spmm_bsr8_{f32,bf16,f16}``.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional, Tuple
+
+import numpy as np
+
+from . import _cabi
+from ._cabi import check, t_ptr
+from .timing import profile_ms
+
+
+def _torch():
+    import torch
+    if not torch.cuda.is_available():
+        raise RuntimeError("liteform_ae_b200 needs a CUDA device (there is no CPU path)")
+    return torch
+
+
+@dataclass
+class DeviceBsr8:
+    indptr: "object"        # torch int64 [Mb + 1]
+    indices: "object"       # torch int32 [nb]
+    blocks: "object"        # torch float32 / bfloat16 / float16 [nb, 8, 8]
+    shape: Tuple[int, int]
+
+    @property
+    def num_blocks(self) -> int:
+        return int(self.indices.numel())
+
+    @staticmethod
+    def from_arrays(indptr, indices, blocks, shape, dtype="float32", device="cuda") -> "DeviceBsr8":
+        torch = _torch()
+        assert blocks.ndim == 3 and blocks.shape[1:] == (8, 8), "blocks must be [nb, 8, 8]"
+        assert shape[0] % 8 == 0 and shape[1] % 8 == 0, "matrix dimensions must be multiples of 8"
+        tdt = {"float32": torch.float32, "bfloat16": torch.bfloat16, "float16": torch.float16}[str(dtype)]
+        b = torch.from_numpy(np.ascontiguousarray(blocks, dtype=np.float32)).to(device).to(tdt).contiguous()
+        return DeviceBsr8(torch.from_numpy(np.ascontiguousarray(indptr, dtype=np.int64)).to(device),
+                          torch.from_numpy(np.ascontiguousarray(indices, dtype=np.int32)).to(device),
+                          b, (int(shape[0]), int(shape[1])))
+
+    @staticmethod
+    def from_scipy(bsr_mat, dtype: Optional[str] = None, device="cuda") -> "DeviceBsr8":
+        """Accepts a ``scipy.sparse.bsr_matrix`` with square blocks whose size is a multiple of 8
+        (re-blocked to 8x8, all-zero sub-blocks dropped) on a shape that is a multiple of 8."""
+        import scipy.sparse as sp
+        m = sp.bsr_matrix(bsr_mat)
+        if dtype is None:
+            dtype = "float16" if m.dtype == np.float16 else "float32"
+        if m.blocksize != (8, 8):
+            assert m.blocksize[0] % 8 == 0 and m.blocksize[1] % 8 == 0, "block size must be a multiple of 8"
+            m = sp.bsr_matrix(m.astype(np.float32).tocsr(), blocksize=(8, 8))
+        m.sort_indices()
+        return DeviceBsr8.from_arrays(m.indptr, m.indices, m.data, m.shape, dtype, device)
+
+
+def spmm_bsr8(a: DeviceBsr8, B, out=None, block_row_range=None):
+    """C = A @ B for an 8x8-block matrix; B's dtype must match the blocks', C is float32."""
+    torch = _torch()
+    lib = _cabi.load()
+    assert B.is_cuda and B.dim() == 2 and B.stride(1) == 1 and B.shape[0] == a.shape[1]
+    assert B.dtype == a.blocks.dtype, "B and the blocks must have the same dtype"
+    r0, r1 = (0, a.shape[0] // 8) if block_row_range is None else block_row_range
+    N = int(B.shape[1])
+    if out is None:
+        out = torch.empty(((r1 - r0) * 8, N), dtype=torch.float32, device=B.device)
+    assert out.dtype == torch.float32 and out.shape == ((r1 - r0) * 8, N) and out.stride(1) == 1
+    fn = {torch.float32: lib.lf_spmm_bsr8_f32, torch.bfloat16: lib.lf_spmm_bsr8_bf16,
+          torch.float16: lib.lf_spmm_bsr8_f16}[a.blocks.dtype]
+    with torch.cuda.device(B.device):
+        check(fn(t_ptr(a.indptr), t_ptr(a.indices), t_ptr(a.blocks), r0, r1, B.data_ptr(), B.stride(0),
+                 out.data_ptr(), out.stride(0), N, torch.cuda.current_stream().cuda_stream))
+    return out
+
+
+def bench_bsrmm(bsr_mat, x, block_size, device="cuda", warmup=10, repeat=100) -> float:
+    """Drop-in for the reference's ``bench_bsrmm(bsr_mat, x, block_size)``: uploads the matrix and
+    x, runs the block SpMM and returns its mean time in milliseconds (format_algos.py:1562-1643).
+    fp16 inputs (what the reference passes) run with fp32 accumulation."""
+    torch = _torch()
+    assert bsr_mat.blocksize == (block_size, block_size), "block_size does not match the matrix"
+    a = DeviceBsr8.from_scipy(bsr_mat, device=device)
+    xt = x if isinstance(x, torch.Tensor) else torch.as_tensor(np.asarray(x))
+    xt = xt.to(device=device, dtype=a.blocks.dtype).contiguous()
+    out = spmm_bsr8(a, xt)
+    dur = profile_ms(lambda: spmm_bsr8(a, xt, out=out), warmup=warmup, repeat=repeat)
+    print("bsrmm exe time: {:.6f} ms".format(dur))
+    return dur
