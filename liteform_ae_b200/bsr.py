@@ -52,14 +52,17 @@ class DeviceBsr8:
         """Accepts a ``scipy.sparse.bsr_matrix`` with square blocks whose size is a multiple of 8
         (re-blocked to 8x8, all-zero sub-blocks dropped) on a shape that is a multiple of 8."""
         import scipy.sparse as sp
-        m = sp.bsr_matrix(bsr_mat)
+        m = bsr_mat
         if dtype is None:
-            dtype = "float16" if m.dtype == np.float16 else "float32"
-        if m.blocksize != (8, 8):
-            assert m.blocksize[0] % 8 == 0 and m.blocksize[1] % 8 == 0, "block size must be a multiple of 8"
-            m = sp.bsr_matrix(m.astype(np.float32).tocsr(), blocksize=(8, 8))
-        m.sort_indices()
-        return DeviceBsr8.from_arrays(m.indptr, m.indices, m.data, m.shape, dtype, device)
+            dtype = "float16" if m.data.dtype == np.float16 else "float32"
+        R, Cb = m.blocksize
+        assert R % 8 == 0 and Cb % 8 == 0, "block size must be a multiple of 8"
+        # rebuild in float32 from the raw arrays (SciPy itself has no float16 support)
+        m32 = sp.bsr_matrix((m.data.astype(np.float32), m.indices, m.indptr), shape=m.shape, blocksize=(R, Cb))
+        if (R, Cb) != (8, 8):
+            m32 = sp.bsr_matrix(m32.tocsr(), blocksize=(8, 8))
+        m32.sort_indices()
+        return DeviceBsr8.from_arrays(m32.indptr, m32.indices, m32.data, m32.shape, dtype, device)
 
 
 def spmm_bsr8(a: DeviceBsr8, B, out=None, block_row_range=None):

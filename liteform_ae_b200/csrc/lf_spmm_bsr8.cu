@@ -65,9 +65,17 @@ __device__ __forceinline__ void mma_16bit(float (&d)[4], const uint32_t (&a)[4],
 //   MMA tile j of unit q: m = g   <-> feature F + 64q + 4g + j
 //                         m = g+8 <-> feature F + 64q + 32 + 4g + j
 //   n <-> row of the block; a lane ends with C[row 2t / 2t+1][4 consecutive features] as float4.
+// The loop over the blocks of the row is software-pipelined: the B rows and A values of block
+// b+1 are requested before the MMAs of block b are issued (two register buffers, ping-pong).
 // ---------------------------------------------------------------------------------------------
 template <int T>
-__global__ void __launch_bounds__(kThreadsBsr)
+struct FragF32 {
+  float4 x0[T], x1[T], y0[T], y1[T];
+  float2 av;
+};
+
+template <int T, int MINB>
+__global__ void __launch_bounds__(kThreadsBsr, MINB)
 bsr8_spmm_f32_kernel(const int64_t* __restrict__ indptr, const int32_t* __restrict__ indices,
                      const float* __restrict__ blocks, int64_t block_row_begin, int64_t block_row_end,
                      const float* __restrict__ B, int ldb, float* __restrict__ C, int64_t ldc, int N,
@@ -95,29 +103,37 @@ bsr8_spmm_f32_kernel(const int64_t* __restrict__ indptr, const int32_t* __restri
     hi_ok[q] = F + 64 * q + 32 + 4 * g < N;
   }
 
-  const int64_t bs = indptr[I], be = indptr[I + 1];
-  for (int64_t b = bs; b < be; ++b) {
-    const int J = indices[b];
-    const float2 av = __ldcs(reinterpret_cast<const float2*>(blocks + b * 64 + g * 8 + 2 * t));
-    const uint32_t b0h = to_tf32(av.x), b1h = to_tf32(av.y);
-    const uint32_t b0l = to_tf32(av.x - __uint_as_float(b0h)), b1l = to_tf32(av.y - __uint_as_float(b1h));
-    const float* r0 = B + (int64_t)(J * 8 + 2 * t) * ldb + F + 4 * g;
+  const int64_t bs = indptr[I];
+  const int nblk = (int)(indptr[I + 1] - bs);
+  const float* Bl = B + F + 4 * g + (int64_t)(2 * t) * ldb;
+  const float* Al = blocks + g * 8 + 2 * t;
+  int my_idx = 0;
+
+  auto load = [&](FragF32<T>& f, int b) {
+    if ((b & 31) == 0) my_idx = (b + lane < nblk) ? indices[bs + b + lane] : 0;
+    const int J = __shfl_sync(0xffffffffu, my_idx, b & 31);
+    f.av = __ldcs(reinterpret_cast<const float2*>(Al + (bs + b) * 64));
+    const float* r0 = Bl + (int64_t)J * 8 * ldb;
     const float* r1 = r0 + ldb;
-    float4 x0[T], x1[T], y0[T], y1[T];
 #pragma unroll
     for (int q = 0; q < T; ++q) {
       const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
-      x0[q] = lo_ok[q] ? __ldg(reinterpret_cast<const float4*>(r0 + 64 * q)) : z;
-      y0[q] = lo_ok[q] ? __ldg(reinterpret_cast<const float4*>(r1 + 64 * q)) : z;
-      x1[q] = hi_ok[q] ? __ldg(reinterpret_cast<const float4*>(r0 + 64 * q + 32)) : z;
-      y1[q] = hi_ok[q] ? __ldg(reinterpret_cast<const float4*>(r1 + 64 * q + 32)) : z;
+      f.x0[q] = lo_ok[q] ? __ldg(reinterpret_cast<const float4*>(r0 + 64 * q)) : z;
+      f.y0[q] = lo_ok[q] ? __ldg(reinterpret_cast<const float4*>(r1 + 64 * q)) : z;
+      f.x1[q] = hi_ok[q] ? __ldg(reinterpret_cast<const float4*>(r0 + 64 * q + 32)) : z;
+      f.y1[q] = hi_ok[q] ? __ldg(reinterpret_cast<const float4*>(r1 + 64 * q + 32)) : z;
     }
+  };
+
+  auto compute = [&](const FragF32<T>& f) {
+    const uint32_t b0h = to_tf32(f.av.x), b1h = to_tf32(f.av.y);
+    const uint32_t b0l = to_tf32(f.av.x - __uint_as_float(b0h)), b1l = to_tf32(f.av.y - __uint_as_float(b1h));
 #pragma unroll
     for (int q = 0; q < T; ++q) {
-      const float a_f[4][4] = {{x0[q].x, x1[q].x, y0[q].x, y1[q].x},
-                               {x0[q].y, x1[q].y, y0[q].y, y1[q].y},
-                               {x0[q].z, x1[q].z, y0[q].z, y1[q].z},
-                               {x0[q].w, x1[q].w, y0[q].w, y1[q].w}};
+      const float a_f[4][4] = {{f.x0[q].x, f.x1[q].x, f.y0[q].x, f.y1[q].x},
+                               {f.x0[q].y, f.x1[q].y, f.y0[q].y, f.y1[q].y},
+                               {f.x0[q].z, f.x1[q].z, f.y0[q].z, f.y1[q].z},
+                               {f.x0[q].w, f.x1[q].w, f.y0[q].w, f.y1[q].w}};
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         uint32_t ah[4], al[4];
@@ -130,6 +146,17 @@ bsr8_spmm_f32_kernel(const int64_t* __restrict__ indptr, const int32_t* __restri
         mma_tf32(acc[q][j], ah, b0l, b1l);
         mma_tf32(acc[q][j], ah, b0h, b1h);
       }
+    }
+  };
+
+  FragF32<T> fa, fb;
+  if (nblk > 0) load(fa, 0);
+  for (int b = 0; b < nblk; b += 2) {
+    if (b + 1 < nblk) load(fb, b + 1);
+    compute(fa);
+    if (b + 1 < nblk) {
+      if (b + 2 < nblk) load(fa, b + 2);
+      compute(fb);
     }
   }
 
@@ -149,16 +176,22 @@ bsr8_spmm_f32_kernel(const int64_t* __restrict__ indptr, const int32_t* __restri
 }
 
 // ---------------------------------------------------------------------------------------------
-// 16-bit in (bf16 or fp16) / float32 out.  One warp = one block row x one tile of 128*T features;
+// 16-bit in (bf16 or fp16) / float32 out.  One warp = one block row x one tile of 128 features;
 // two blocks per m16n8k16 MMA.  Index maps:
 //   k-slots 2t, 2t+1   <-> block 0, columns 2t, 2t+1      k-slots 2t+8, 2t+9 <-> block 1, same columns
-//   MMA tile j of unit q: m = g   <-> feature F + 128q + 8g + j
-//                         m = g+8 <-> feature F + 128q + 64 + 8g + j
+//   MMA tile j: m = g   <-> feature F + 8g + j
+//               m = g+8 <-> feature F + 64 + 8g + j
 // A lane loads 8 consecutive 16-bit features (one 128-bit load) from each of its four B rows and
-// interleaves rows pairwise with byte permutes to form the packed k-pairs the MMA wants.
+// interleaves rows pairwise with byte permutes to form the packed k-pairs the MMA wants.  Same
+// two-buffer software pipeline as the float32 kernel, over pairs of blocks.
 // ---------------------------------------------------------------------------------------------
-template <int T, bool BF16>
-__global__ void __launch_bounds__(kThreadsBsr)
+struct Frag16 {
+  uint4 v[4][2];   // [row][half]: rows = (blk0 col 2t), (blk0 col 2t+1), (blk1 col 2t), (blk1 col 2t+1)
+  uint32_t b0, b1;
+};
+
+template <bool BF16, int MINB>
+__global__ void __launch_bounds__(kThreadsBsr, MINB)
 bsr8_spmm_16bit_kernel(const int64_t* __restrict__ indptr, const int32_t* __restrict__ indices,
                        const uint16_t* __restrict__ blocks, int64_t block_row_begin, int64_t block_row_end,
                        const uint16_t* __restrict__ B, int ldb, float* __restrict__ C, int64_t ldc, int N,
@@ -167,79 +200,87 @@ bsr8_spmm_16bit_kernel(const int64_t* __restrict__ indptr, const int32_t* __rest
   const int64_t work = (int64_t)blockIdx.x * kWarps + (threadIdx.x >> 5);
   const int64_t I = block_row_begin + work / tiles;
   if (I >= block_row_end) return;
-  const int F = (int)(work % tiles) * (128 * T);
+  const int F = (int)(work % tiles) * 128;
 
-  float acc[T][8][4];
+  float acc[8][4];
 #pragma unroll
-  for (int q = 0; q < T; ++q)
+  for (int j = 0; j < 8; ++j)
 #pragma unroll
-    for (int j = 0; j < 8; ++j)
-#pragma unroll
-      for (int i = 0; i < 4; ++i) acc[q][j][i] = 0.f;
-  bool lo_ok[T], hi_ok[T];
-#pragma unroll
-  for (int q = 0; q < T; ++q) {
-    lo_ok[q] = F + 128 * q + 8 * g < N;
-    hi_ok[q] = F + 128 * q + 64 + 8 * g < N;
-  }
+    for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
+  const bool lo_ok = F + 8 * g < N, hi_ok = F + 64 + 8 * g < N;
 
-  const int64_t bs = indptr[I], be = indptr[I + 1];
-  for (int64_t b = bs; b < be; b += 2) {
-    const bool two = b + 1 < be;
-    const int J0 = indices[b], J1 = two ? indices[b + 1] : J0;
-    const uint32_t b0 = __ldcs(reinterpret_cast<const uint32_t*>(blocks + b * 64 + g * 8 + 2 * t));
-    const uint32_t b1 = two ? __ldcs(reinterpret_cast<const uint32_t*>(blocks + (b + 1) * 64 + g * 8 + 2 * t)) : 0u;
-    const uint16_t* p0 = B + (int64_t)(J0 * 8 + 2 * t) * ldb + F + 8 * g;   // block 0, column 2t
-    const uint16_t* p2 = B + (int64_t)(J1 * 8 + 2 * t) * ldb + F + 8 * g;   // block 1, column 2t
+  const int64_t bs = indptr[I];
+  const int nblk = (int)(indptr[I + 1] - bs);
+  const int npair = (nblk + 1) >> 1;
+  const uint16_t* Bl = B + F + 8 * g + (int64_t)(2 * t) * ldb;
+  const uint16_t* Al = blocks + g * 8 + 2 * t;
+  int my_idx = 0;
+
+  auto load = [&](Frag16& f, int p) {
+    const int b = 2 * p;
+    if ((b & 31) == 0) my_idx = (b + lane < nblk) ? indices[bs + b + lane] : 0;
+    const bool two = b + 1 < nblk;
+    const int J0 = __shfl_sync(0xffffffffu, my_idx, b & 31);
+    const int J1 = __shfl_sync(0xffffffffu, my_idx, (b + 1) & 31);
+    f.b0 = __ldcs(reinterpret_cast<const uint32_t*>(Al + (bs + b) * 64));
+    f.b1 = two ? __ldcs(reinterpret_cast<const uint32_t*>(Al + (bs + b + 1) * 64)) : 0u;
+    const uint16_t* p0 = Bl + (int64_t)J0 * 8 * ldb;
+    const uint16_t* p2 = Bl + (int64_t)J1 * 8 * ldb;
+    const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+    f.v[0][0] = lo_ok ? __ldg(reinterpret_cast<const uint4*>(p0)) : z;
+    f.v[1][0] = lo_ok ? __ldg(reinterpret_cast<const uint4*>(p0 + ldb)) : z;
+    f.v[2][0] = (lo_ok && two) ? __ldg(reinterpret_cast<const uint4*>(p2)) : z;
+    f.v[3][0] = (lo_ok && two) ? __ldg(reinterpret_cast<const uint4*>(p2 + ldb)) : z;
+    f.v[0][1] = hi_ok ? __ldg(reinterpret_cast<const uint4*>(p0 + 64)) : z;
+    f.v[1][1] = hi_ok ? __ldg(reinterpret_cast<const uint4*>(p0 + ldb + 64)) : z;
+    f.v[2][1] = (hi_ok && two) ? __ldg(reinterpret_cast<const uint4*>(p2 + 64)) : z;
+    f.v[3][1] = (hi_ok && two) ? __ldg(reinterpret_cast<const uint4*>(p2 + ldb + 64)) : z;
+  };
+
+  auto compute = [&](const Frag16& f) {
 #pragma unroll
-    for (int q = 0; q < T; ++q) {
-      const uint4 z = make_uint4(0u, 0u, 0u, 0u);
-      // [row][half]: rows = (blk0 col 2t), (blk0 col 2t+1), (blk1 col 2t), (blk1 col 2t+1)
-      uint4 v[4][2];
-      v[0][0] = lo_ok[q] ? __ldg(reinterpret_cast<const uint4*>(p0 + 128 * q)) : z;
-      v[1][0] = lo_ok[q] ? __ldg(reinterpret_cast<const uint4*>(p0 + ldb + 128 * q)) : z;
-      v[2][0] = (lo_ok[q] && two) ? __ldg(reinterpret_cast<const uint4*>(p2 + 128 * q)) : z;
-      v[3][0] = (lo_ok[q] && two) ? __ldg(reinterpret_cast<const uint4*>(p2 + ldb + 128 * q)) : z;
-      v[0][1] = hi_ok[q] ? __ldg(reinterpret_cast<const uint4*>(p0 + 128 * q + 64)) : z;
-      v[1][1] = hi_ok[q] ? __ldg(reinterpret_cast<const uint4*>(p0 + ldb + 128 * q + 64)) : z;
-      v[2][1] = (hi_ok[q] && two) ? __ldg(reinterpret_cast<const uint4*>(p2 + 128 * q + 64)) : z;
-      v[3][1] = (hi_ok[q] && two) ? __ldg(reinterpret_cast<const uint4*>(p2 + ldb + 128 * q + 64)) : z;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        // feature j of the lane's 8: 32-bit word j/2, half-word j%2 of each 128-bit load
-        const uint32_t sel = (j & 1) ? 0x7632u : 0x5410u;   // (lo,lo) or (hi,hi) halves of two words
-        uint32_t a[4];
-        auto word = [&](const uint4& u) { return j < 2 ? u.x : (j < 4 ? u.y : (j < 6 ? u.z : u.w)); };
-        a[0] = __byte_perm(word(v[0][0]), word(v[1][0]), sel);   // m = g,   k = 2t, 2t+1
-        a[1] = __byte_perm(word(v[0][1]), word(v[1][1]), sel);   // m = g+8, k = 2t, 2t+1
-        a[2] = __byte_perm(word(v[2][0]), word(v[3][0]), sel);   // m = g,   k = 2t+8, 2t+9
-        a[3] = __byte_perm(word(v[2][1]), word(v[3][1]), sel);   // m = g+8, k = 2t+8, 2t+9
-        mma_16bit<BF16>(acc[q][j], a, b0, b1);
-      }
+    for (int j = 0; j < 8; ++j) {
+      // feature j of the lane's 8: 32-bit word j/2, half-word j%2 of each 128-bit load
+      const uint32_t sel = (j & 1) ? 0x7632u : 0x5410u;  // (hi,hi) or (lo,lo) halves of two words
+      auto word = [&](const uint4& u) { return j < 2 ? u.x : (j < 4 ? u.y : (j < 6 ? u.z : u.w)); };
+      uint32_t a[4];
+      a[0] = __byte_perm(word(f.v[0][0]), word(f.v[1][0]), sel);  // m = g,   k = 2t, 2t+1
+      a[1] = __byte_perm(word(f.v[0][1]), word(f.v[1][1]), sel);  // m = g+8, k = 2t, 2t+1
+      a[2] = __byte_perm(word(f.v[2][0]), word(f.v[3][0]), sel);  // m = g,   k = 2t+8, 2t+9
+      a[3] = __byte_perm(word(f.v[2][1]), word(f.v[3][1]), sel);  // m = g+8, k = 2t+8, 2t+9
+      mma_16bit<BF16>(acc[j], a, f.b0, f.b1);
+    }
+  };
+
+  Frag16 fa, fb;
+  if (npair > 0) load(fa, 0);
+  for (int p = 0; p < npair; p += 2) {
+    if (p + 1 < npair) load(fb, p + 1);
+    compute(fa);
+    if (p + 1 < npair) {
+      if (p + 2 < npair) load(fa, p + 2);
+      compute(fb);
     }
   }
 
   float* c0 = C + ((I - block_row_begin) * 8 + 2 * t) * ldc + F + 8 * g;
   float* c1 = c0 + ldc;
 #pragma unroll
-  for (int q = 0; q < T; ++q) {
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {   // features 8g + 4h .. +3
-      if (lo_ok[q]) {
-        __stcs(reinterpret_cast<float4*>(c0 + 128 * q + 4 * h),
-               make_float4(acc[q][4 * h][0], acc[q][4 * h + 1][0], acc[q][4 * h + 2][0], acc[q][4 * h + 3][0]));
-        __stcs(reinterpret_cast<float4*>(c1 + 128 * q + 4 * h),
-               make_float4(acc[q][4 * h][1], acc[q][4 * h + 1][1], acc[q][4 * h + 2][1], acc[q][4 * h + 3][1]));
-      }
-      if (hi_ok[q]) {
-        __stcs(reinterpret_cast<float4*>(c0 + 128 * q + 64 + 4 * h),
-               make_float4(acc[q][4 * h][2], acc[q][4 * h + 1][2], acc[q][4 * h + 2][2], acc[q][4 * h + 3][2]));
-        __stcs(reinterpret_cast<float4*>(c1 + 128 * q + 64 + 4 * h),
-               make_float4(acc[q][4 * h][3], acc[q][4 * h + 1][3], acc[q][4 * h + 2][3], acc[q][4 * h + 3][3]));
-      }
+  for (int h = 0; h < 2; ++h) {  // features 8g + 4h .. +3
+    if (lo_ok) {
+      __stcs(reinterpret_cast<float4*>(c0 + 4 * h), make_float4(acc[4 * h][0], acc[4 * h + 1][0], acc[4 * h + 2][0], acc[4 * h + 3][0]));
+      __stcs(reinterpret_cast<float4*>(c1 + 4 * h), make_float4(acc[4 * h][1], acc[4 * h + 1][1], acc[4 * h + 2][1], acc[4 * h + 3][1]));
+    }
+    if (hi_ok) {
+      __stcs(reinterpret_cast<float4*>(c0 + 64 + 4 * h), make_float4(acc[4 * h][2], acc[4 * h + 1][2], acc[4 * h + 2][2], acc[4 * h + 3][2]));
+      __stcs(reinterpret_cast<float4*>(c1 + 64 + 4 * h), make_float4(acc[4 * h][3], acc[4 * h + 1][3], acc[4 * h + 2][3], acc[4 * h + 3][3]));
     }
   }
 }
+
+// tuning state of the block kernels (lf_set_option)
+int g_bsr_feat_units = 0;   // 0 = automatic, 1 or 2 = features per warp / 64 of the float32 kernel
+int g_bsr_min_blocks = 0;   // 0 = automatic
 
 int check_common(const void* indptr, const void* indices, const void* blocks, int64_t r0, int64_t r1,
                  const void* B, int64_t ldb, const void* C, int64_t ldc, int N, int feat_align, int elem_b) {
@@ -263,6 +304,13 @@ using namespace lf;
 
 extern "C" {
 
+int lf_bsr_set_tuning(int32_t feat_units, int32_t min_blocks) {
+  LF_REQUIRE(feat_units >= 0 && feat_units <= 2 && min_blocks >= 0 && min_blocks <= 3, "bad tuning values");
+  g_bsr_feat_units = feat_units;
+  g_bsr_min_blocks = min_blocks;
+  return LF_OK;
+}
+
 int lf_spmm_bsr8_f32(const int64_t* indptr, const int32_t* indices, const float* blocks,
                      int64_t block_row_begin, int64_t block_row_end, const float* B, int64_t ldb,
                      float* C, int64_t ldc, int32_t N, void* stream) {
@@ -270,18 +318,17 @@ int lf_spmm_bsr8_f32(const int64_t* indptr, const int32_t* indices, const float*
   if (block_row_begin == block_row_end) return LF_OK;
   cudaStream_t st = (cudaStream_t)stream;
   const int64_t rows = block_row_end - block_row_begin;
-  if (N > 64) {
-    const int tiles = (N + 127) / 128;
-    const int64_t grid = ceil_div64(rows * tiles, kWarps);
-    LF_REQUIRE(grid < (1ll << 31), "too many thread blocks");
-    bsr8_spmm_f32_kernel<2><<<(unsigned)grid, kThreadsBsr, 0, st>>>(indptr, indices, blocks, block_row_begin,
-                                                                    block_row_end, B, (int)ldb, C, ldc, N, tiles);
-  } else {
-    const int64_t grid = ceil_div64(rows, kWarps);
-    LF_REQUIRE(grid < (1ll << 31), "too many thread blocks");
-    bsr8_spmm_f32_kernel<1><<<(unsigned)grid, kThreadsBsr, 0, st>>>(indptr, indices, blocks, block_row_begin,
-                                                                    block_row_end, B, (int)ldb, C, ldc, N, 1);
-  }
+  const int T = g_bsr_feat_units ? g_bsr_feat_units : (N > 64 ? 2 : 1);
+  const int minb = g_bsr_min_blocks ? g_bsr_min_blocks : (T == 2 ? 1 : 2);
+  const int tiles = (N + 64 * T - 1) / (64 * T);
+  const int64_t grid = ceil_div64(rows * tiles, kWarps);
+  LF_REQUIRE(grid < (1ll << 31), "too many thread blocks");
+#define LF_BSR(T_, M_)                                                                                          \
+  bsr8_spmm_f32_kernel<T_, M_><<<(unsigned)grid, kThreadsBsr, 0, st>>>(indptr, indices, blocks, block_row_begin, \
+                                                                       block_row_end, B, (int)ldb, C, ldc, N, tiles)
+  if (T == 2) { if (minb == 1) LF_BSR(2, 1); else if (minb == 2) LF_BSR(2, 2); else LF_BSR(2, 3); }
+  else        { if (minb == 1) LF_BSR(1, 1); else if (minb == 2) LF_BSR(1, 2); else LF_BSR(1, 3); }
+#undef LF_BSR
   LF_CUDA_CHECK(cudaGetLastError());
   return LF_OK;
 }
@@ -295,10 +342,13 @@ static int launch_16bit(bool bf16, const int64_t* indptr, const int32_t* indices
   const int tiles = (N + 127) / 128;
   const int64_t grid = ceil_div64((r1 - r0) * tiles, kWarps);
   LF_REQUIRE(grid < (1ll << 31), "too many thread blocks");
-  if (bf16)
-    bsr8_spmm_16bit_kernel<1, true><<<(unsigned)grid, kThreadsBsr, 0, st>>>(indptr, indices, blocks, r0, r1, B, (int)ldb, C, ldc, N, tiles);
-  else
-    bsr8_spmm_16bit_kernel<1, false><<<(unsigned)grid, kThreadsBsr, 0, st>>>(indptr, indices, blocks, r0, r1, B, (int)ldb, C, ldc, N, tiles);
+  const int minb = g_bsr_min_blocks ? g_bsr_min_blocks : 2;
+#define LF_BSR16(B_, M_)                                                                                        \
+  bsr8_spmm_16bit_kernel<B_, M_><<<(unsigned)grid, kThreadsBsr, 0, st>>>(indptr, indices, blocks, r0, r1, B,     \
+                                                                         (int)ldb, C, ldc, N, tiles)
+  if (bf16) { if (minb == 1) LF_BSR16(true, 1); else if (minb == 2) LF_BSR16(true, 2); else LF_BSR16(true, 3); }
+  else      { if (minb == 1) LF_BSR16(false, 1); else if (minb == 2) LF_BSR16(false, 2); else LF_BSR16(false, 3); }
+#undef LF_BSR16
   LF_CUDA_CHECK(cudaGetLastError());
   return LF_OK;
 }

@@ -100,9 +100,15 @@ class MTX:
         return self.coo_mtx.tobsr(blocksize=blocksize, copy=copy)
 
     def tobsr_with_padding(self, shape, blocksize=None):
-        data = np.array(self.coo_mtx.data, dtype=np.dtype("float16"))
+        """BSR copy with fp16 block data on a padded shape (format_matrix_market.py:116-138).
+        Current SciPy refuses to construct float16 sparse matrices, so the matrix is assembled in
+        float32 and its block array is narrowed afterwards."""
+        data = np.array(self.coo_mtx.data, dtype=np.float32)
         ij = [self.coo_mtx.row, self.coo_mtx.col]
-        return sp.bsr_matrix((data, ij), blocksize=blocksize, shape=shape)
+        bsr = sp.bsr_matrix((data, ij), blocksize=blocksize, shape=shape)
+        bsr.sort_indices()
+        bsr.data = bsr.data.astype(np.float16)
+        return bsr
 
     def tocsr(self, copy=False):
         return self.coo_mtx.tocsr(copy=copy)
