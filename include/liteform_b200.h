@@ -189,8 +189,9 @@ int lf_spmm_bsr8_f32(const int64_t* indptr /*[dev]*/, const int32_t* indices /*[
                      const float* B /*[dev]*/, int64_t ldb, float* C /*[dev]*/, int64_t ldc, int32_t N,
                      void* stream);
 /* Tuning of the block kernels (results do not depend on it): features per warp of the float32
- * kernel in units of 64 (0 = automatic, 1, 2) and resident thread blocks per SM (0 = automatic, 1..3). */
-int lf_bsr_set_tuning(int32_t feat_units, int32_t min_blocks);
+ * kernel in units of 64 (0 = automatic, 1, 2), depth of the per-warp copy ring (0 = automatic, 3,
+ * 4) and block rows one warp streams through (0 = automatic, 1..31). */
+int lf_bsr_set_tuning(int32_t feat_units, int32_t stages, int32_t rows_per_warp);
 /* bf16 blocks and bf16 B (raw 16-bit patterns), float32 C */
 int lf_spmm_bsr8_bf16(const int64_t* indptr, const int32_t* indices, const uint16_t* blocks,
                       int64_t block_row_begin, int64_t block_row_end, const uint16_t* B, int64_t ldb,

@@ -15,7 +15,7 @@
 //     m16n8k8 tf32 MMAs (hi*hi + lo*hi + hi*lo) reproduce the fp32 product to ~2^-21 relative.
 //   * 16-bit path (bf16 or fp16 inputs): m16n8k16 over a pair of blocks, fp32 accumulate.
 //
-// Data movement.  One warp owns one block row and one feature tile.  The 8 rows of B that a
+// Data movement.  One warp owns a few consecutive block rows and one feature tile.  The 8 rows of B that a
 // block needs (and the block itself) are copied global -> shared with 16-byte cp.async, one
 // fully coalesced row (or two half rows) per instruction, into a warp-private ring of D stages,
 // so D-1 blocks are in flight per warp without holding registers; the warp then reads its MMA
@@ -41,7 +41,7 @@ constexpr int kWarps = 8;
 constexpr int kThreadsBsr = kWarps * 32;
 
 __device__ __forceinline__ void mma_tf32(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
@@ -50,12 +50,12 @@ __device__ __forceinline__ void mma_tf32(float (&d)[4], const uint32_t (&a)[4], 
 template <bool BF16>
 __device__ __forceinline__ void mma_16bit(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   if (BF16) {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
   } else {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
@@ -96,115 +96,137 @@ struct F32Cfg {
   static constexpr int kSmem = kWarps * D * kStage;
 };
 
+// A warp walks the blocks of R consecutive block rows as one stream, so the copy ring stays full
+// across row boundaries; lane l keeps indptr[I0 + l] and a sliding window of 32 block columns.
 template <int T, int D, int MINB>
 __global__ void __launch_bounds__(kThreadsBsr, MINB)
 bsr8_spmm_f32_kernel(const int64_t* __restrict__ indptr, const int32_t* __restrict__ indices,
                      const float* __restrict__ blocks, int64_t block_row_begin, int64_t block_row_end,
                      const float* __restrict__ B, int ldb, float* __restrict__ C, int64_t ldc, int N,
-                     int tiles) {
+                     int tiles, int rows_per_warp) {
   using Cfg = F32Cfg<T, D>;
   extern __shared__ __align__(128) uint8_t smem_raw[];
   const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3, warp = threadIdx.x >> 5;
   // tile index runs fastest so that the tiles of one block row are resident together and the
   // A blocks they share are fetched from HBM once
   const int64_t work = (int64_t)blockIdx.x * kWarps + warp;
-  const int64_t I = block_row_begin + work / tiles;
-  if (I >= block_row_end) return;
+  const int64_t I0 = block_row_begin + (work / tiles) * rows_per_warp;
+  if (I0 >= block_row_end) return;
+  const int R = (int)min((int64_t)rows_per_warp, block_row_end - I0);
   const int F = (int)(work % tiles) * (64 * T);
   uint8_t* ring = smem_raw + warp * (D * Cfg::kStage);
   const uint32_t ring_u32 = smem_u32(ring);
 
-  float acc[T][4][4];
-#pragma unroll
-  for (int q = 0; q < T; ++q)
-#pragma unroll
-    for (int j = 0; j < 4; ++j)
-#pragma unroll
-      for (int i = 0; i < 4; ++i) acc[q][j][i] = 0.f;
+  const int64_t my_ptr = indptr[I0 + min(lane, R)];              // lane l <= R: start of row l
+  const int64_t stream_end = __shfl_sync(0xffffffffu, my_ptr, R);
+  auto row_start = [&](int r) { return __shfl_sync(0xffffffffu, my_ptr, r); };
 
-  const int64_t bs = indptr[I];
-  const int nblk = (int)(indptr[I + 1] - bs);
   int my_idx = 0;
+  int64_t win = -(int64_t)64;   // first block held in my_idx (none yet)
+  int64_t ib = row_start(0);    // issue cursor (runs D-1 blocks ahead of the consumer)
+  int slot_in = 0;
 
-  // copy block b (8 rows of B, then the block) into ring slot `slot`
-  auto issue = [&](int b, int slot) {
-    if ((b & 31) == 0) my_idx = (b + lane < nblk) ? indices[bs + b + lane] : 0;
-    const int J = __shfl_sync(0xffffffffu, my_idx, b & 31);
-    const uint32_t dst = ring_u32 + slot * Cfg::kStage;
-    const float* src = B + (int64_t)J * 8 * ldb + F;
-    if (T == 2) {
-      const int ok = (F + 4 * lane < N) ? 16 : 0;   // lane = chunk of the row
-#pragma unroll
-      for (int r = 0; r < 8; ++r)
-        cp_async16(dst + r * Cfg::kRowBytes + (((lane & ~7) | ((lane ^ r) & 7)) << 4),
-                   src + (int64_t)r * ldb + (ok ? 4 * lane : 0), ok);
-    } else {
-      const int c = lane & 15, rr = lane >> 4;      // two rows per instruction
-      const int ok = (F + 4 * c < N) ? 16 : 0;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int r = 2 * i + rr;
-        cp_async16(dst + r * Cfg::kRowBytes + (((c & ~7) | ((c ^ r) & 7)) << 4),
-                   src + (int64_t)r * ldb + (ok ? 4 * c : 0), ok);
+  // copy the next block of the stream (if any) into the next ring slot
+  auto issue_next = [&]() {
+    if (ib < stream_end) {
+      const int64_t b = ib;
+      if (b >= win + 32) {
+        win = b;
+        my_idx = (b + lane < stream_end) ? indices[b + lane] : 0;
       }
+      const int J = __shfl_sync(0xffffffffu, my_idx, (int)(b - win));
+      const uint32_t dst = ring_u32 + slot_in * Cfg::kStage;
+      const float* src = B + (int64_t)J * 8 * ldb + F;
+      if (T == 2) {
+        const int ok = (F + 4 * lane < N) ? 16 : 0;   // lane = chunk of the row
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+          cp_async16(dst + r * Cfg::kRowBytes + (((lane & ~7) | ((lane ^ r) & 7)) << 4),
+                     src + (int64_t)r * ldb + (ok ? 4 * lane : 0), ok);
+      } else {
+        const int c = lane & 15, rr = lane >> 4;      // two rows per instruction
+        const int ok = (F + 4 * c < N) ? 16 : 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int r = 2 * i + rr;
+          cp_async16(dst + r * Cfg::kRowBytes + (((c & ~7) | ((c ^ r) & 7)) << 4),
+                     src + (int64_t)r * ldb + (ok ? 4 * c : 0), ok);
+        }
+      }
+      if (lane < 16) cp_async16(dst + 8 * Cfg::kRowBytes + lane * 16, blocks + b * 64 + lane * 4, 16);
+      ib = b + 1;
+      slot_in = slot_in + 1 == D ? 0 : slot_in + 1;
     }
-    if (lane < 16) cp_async16(dst + 8 * Cfg::kRowBytes + lane * 16, blocks + (bs + b) * 64 + lane * 4, 16);
+    cp_async_commit();
   };
 
 #pragma unroll
-  for (int s = 0; s < D - 1; ++s) {
-    if (s < nblk) issue(s, s);
-    cp_async_commit();
-  }
-  for (int b = 0; b < nblk; ++b) {
-    cp_async_wait<D - 2>();
-    __syncwarp();
-    const int nb = b + D - 1;
-    if (nb < nblk) issue(nb, nb % D);   // overwrites the slot consumed in the previous iteration
-    cp_async_commit();
+  for (int s = 0; s < D - 1; ++s) issue_next();
 
-    const uint8_t* st = ring + (b % D) * Cfg::kStage;
-    const float2 av = *reinterpret_cast<const float2*>(st + 8 * Cfg::kRowBytes + (g * 8 + 2 * t) * 4);
-    uint32_t b0h, b0l, b1h, b1l;
-    split_tf32(av.x, b0h, b0l);
-    split_tf32(av.y, b1h, b1l);
-    const uint8_t* row0 = st + (2 * t) * Cfg::kRowBytes;
-    const uint8_t* row1 = row0 + Cfg::kRowBytes;
-    const int sw0 = ((g ^ (2 * t)) & 7) << 4, sw1 = ((g ^ (2 * t + 1)) & 7) << 4;
+  int slot_out = 0;
+  for (int r = 0; r < R; ++r) {
+    float acc[T][4][4];
+#pragma unroll
+    for (int q = 0; q < T; ++q)
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[q][j][i] = 0.f;
+
+    const int64_t be = row_start(r + 1);
+    for (int64_t b = row_start(r); b < be; ++b) {
+      cp_async_wait<D - 2>();
+      __syncwarp();
+      issue_next();   // refills the slot consumed in the previous iteration
+
+      const uint8_t* st = ring + slot_out * Cfg::kStage;
+      slot_out = slot_out + 1 == D ? 0 : slot_out + 1;
+      const float2 av = *reinterpret_cast<const float2*>(st + 8 * Cfg::kRowBytes + (g * 8 + 2 * t) * 4);
+      uint32_t b0h, b0l, b1h, b1l;
+      split_tf32(av.x, b0h, b0l);
+      split_tf32(av.y, b1h, b1l);
+      const uint8_t* row0 = st + (2 * t) * Cfg::kRowBytes;
+      const uint8_t* row1 = row0 + Cfg::kRowBytes;
+      const int sw0 = ((g ^ (2 * t)) & 7) << 4, sw1 = ((g ^ (2 * t + 1)) & 7) << 4;
+#pragma unroll
+      for (int q = 0; q < T; ++q) {
+        const float4 x0 = *reinterpret_cast<const float4*>(row0 + q * 256 + sw0);        // k = t,   m = g
+        const float4 x1 = *reinterpret_cast<const float4*>(row0 + q * 256 + 128 + sw0);  // k = t,   m = g+8
+        const float4 y0 = *reinterpret_cast<const float4*>(row1 + q * 256 + sw1);        // k = t+4, m = g
+        const float4 y1 = *reinterpret_cast<const float4*>(row1 + q * 256 + 128 + sw1);  // k = t+4, m = g+8
+        const float a_f[4][4] = {{x0.x, x1.x, y0.x, y1.x}, {x0.y, x1.y, y0.y, y1.y},
+                                 {x0.z, x1.z, y0.z, y1.z}, {x0.w, x1.w, y0.w, y1.w}};
+        uint32_t ah[4][4], al[4][4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) split_tf32(a_f[j][i], ah[j][i], al[j][i]);
+        // the three products of one tile depend on each other through the accumulator: issue
+        // them tile-interleaved so that consecutive MMAs are independent
+#pragma unroll
+        for (int j = 0; j < 4; ++j) mma_tf32(acc[q][j], al[j], b0h, b1h);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) mma_tf32(acc[q][j], ah[j], b0l, b1l);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) mma_tf32(acc[q][j], ah[j], b0h, b1h);
+      }
+    }
+
+    float* c0 = C + ((I0 + r - block_row_begin) * 8 + 2 * t) * ldc + F + 4 * g;
+    float* c1 = c0 + ldc;
 #pragma unroll
     for (int q = 0; q < T; ++q) {
-      const float4 x0 = *reinterpret_cast<const float4*>(row0 + q * 256 + sw0);        // k = t,   m = g
-      const float4 x1 = *reinterpret_cast<const float4*>(row0 + q * 256 + 128 + sw0);  // k = t,   m = g+8
-      const float4 y0 = *reinterpret_cast<const float4*>(row1 + q * 256 + sw1);        // k = t+4, m = g
-      const float4 y1 = *reinterpret_cast<const float4*>(row1 + q * 256 + 128 + sw1);  // k = t+4, m = g+8
-      const float a_f[4][4] = {{x0.x, x1.x, y0.x, y1.x}, {x0.y, x1.y, y0.y, y1.y},
-                               {x0.z, x1.z, y0.z, y1.z}, {x0.w, x1.w, y0.w, y1.w}};
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        uint32_t ah[4], al[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) split_tf32(a_f[j][i], ah[i], al[i]);
-        mma_tf32(acc[q][j], al, b0h, b1h);
-        mma_tf32(acc[q][j], ah, b0l, b1l);
-        mma_tf32(acc[q][j], ah, b0h, b1h);
+      if (F + 64 * q + 4 * g < N) {
+        __stcs(reinterpret_cast<float4*>(c0 + 64 * q), make_float4(acc[q][0][0], acc[q][1][0], acc[q][2][0], acc[q][3][0]));
+        __stcs(reinterpret_cast<float4*>(c1 + 64 * q), make_float4(acc[q][0][1], acc[q][1][1], acc[q][2][1], acc[q][3][1]));
+      }
+      if (F + 64 * q + 32 + 4 * g < N) {
+        __stcs(reinterpret_cast<float4*>(c0 + 64 * q + 32), make_float4(acc[q][0][2], acc[q][1][2], acc[q][2][2], acc[q][3][2]));
+        __stcs(reinterpret_cast<float4*>(c1 + 64 * q + 32), make_float4(acc[q][0][3], acc[q][1][3], acc[q][2][3], acc[q][3][3]));
       }
     }
   }
   cp_async_wait<0>();
-
-  float* c0 = C + ((I - block_row_begin) * 8 + 2 * t) * ldc + F + 4 * g;
-  float* c1 = c0 + ldc;
-#pragma unroll
-  for (int q = 0; q < T; ++q) {
-    if (F + 64 * q + 4 * g < N) {
-      __stcs(reinterpret_cast<float4*>(c0 + 64 * q), make_float4(acc[q][0][0], acc[q][1][0], acc[q][2][0], acc[q][3][0]));
-      __stcs(reinterpret_cast<float4*>(c1 + 64 * q), make_float4(acc[q][0][1], acc[q][1][1], acc[q][2][1], acc[q][3][1]));
-    }
-    if (F + 64 * q + 32 + 4 * g < N) {
-      __stcs(reinterpret_cast<float4*>(c0 + 64 * q + 32), make_float4(acc[q][0][2], acc[q][1][2], acc[q][2][2], acc[q][3][2]));
-      __stcs(reinterpret_cast<float4*>(c1 + 64 * q + 32), make_float4(acc[q][0][3], acc[q][1][3], acc[q][2][3], acc[q][3][3]));
-    }
-  }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -230,110 +252,129 @@ __global__ void __launch_bounds__(kThreadsBsr, MINB)
 bsr8_spmm_16bit_kernel(const int64_t* __restrict__ indptr, const int32_t* __restrict__ indices,
                        const uint16_t* __restrict__ blocks, int64_t block_row_begin, int64_t block_row_end,
                        const uint16_t* __restrict__ B, int ldb, float* __restrict__ C, int64_t ldc, int N,
-                       int tiles) {
+                       int tiles, int rows_per_warp) {
   using Cfg = H16Cfg<D>;
   extern __shared__ __align__(128) uint8_t smem_raw[];
   const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3, warp = threadIdx.x >> 5;
   const int64_t work = (int64_t)blockIdx.x * kWarps + warp;
-  const int64_t I = block_row_begin + work / tiles;
-  if (I >= block_row_end) return;
+  const int64_t I0 = block_row_begin + (work / tiles) * rows_per_warp;
+  if (I0 >= block_row_end) return;
+  const int R = (int)min((int64_t)rows_per_warp, block_row_end - I0);
   const int F = (int)(work % tiles) * 128;
   uint8_t* ring = smem_raw + warp * (D * Cfg::kStage);
   const uint32_t ring_u32 = smem_u32(ring);
 
-  float acc[8][4];
-#pragma unroll
-  for (int j = 0; j < 8; ++j)
-#pragma unroll
-    for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
+  const int64_t my_ptr = indptr[I0 + min(lane, R)];              // lane l <= R: start of row l
+  const int64_t stream_end = __shfl_sync(0xffffffffu, my_ptr, R);
+  auto row_start = [&](int r) { return __shfl_sync(0xffffffffu, my_ptr, r); };
 
-  const int64_t bs = indptr[I];
-  const int nblk = (int)(indptr[I + 1] - bs);
-  const int npair = (nblk + 1) >> 1;
   int my_idx = 0;
+  int64_t win = -(int64_t)64;
+  // issue cursor: pairs never straddle a row (an odd row ends with a half-empty pair)
+  int ir = 0;
+  int64_t ib = row_start(0), ire = row_start(1);
+  while (ib == ire && ir + 1 < R) { ++ir; ire = row_start(ir + 1); }
+  int slot_in = 0;
 
-  auto issue = [&](int p, int slot) {
-    const int b = 2 * p;
-    if ((b & 31) == 0) my_idx = (b + lane < nblk) ? indices[bs + b + lane] : 0;
-    const bool two = b + 1 < nblk;
-    const int J0 = __shfl_sync(0xffffffffu, my_idx, b & 31);
-    const int J1 = __shfl_sync(0xffffffffu, my_idx, (b + 1) & 31);
-    const uint32_t dst = ring_u32 + slot * Cfg::kStage;
-    const int c = lane & 15, rr = lane >> 4;   // two rows per instruction, 16 chunks of 8 features each
-    const bool in = F + 8 * c < N;
-    const uint16_t* s0 = B + (int64_t)J0 * 8 * ldb + F + (in ? 8 * c : 0);
-    const uint16_t* s1 = B + (int64_t)(two ? J1 : J0) * 8 * ldb + F + (in ? 8 * c : 0);
+  auto issue_next = [&]() {
+    if (ib < stream_end) {
+      const int64_t b = ib;
+      const bool two = b + 1 < ire;
+      if (b + 1 >= win + 32) {
+        win = b;
+        my_idx = (b + lane < stream_end) ? indices[b + lane] : 0;
+      }
+      const int J0 = __shfl_sync(0xffffffffu, my_idx, (int)(b - win));
+      const int J1 = __shfl_sync(0xffffffffu, my_idx, (int)(b + 1 - win));
+      const uint32_t dst = ring_u32 + slot_in * Cfg::kStage;
+      const int c = lane & 15, rr = lane >> 4;   // two rows per instruction, 16 chunks of 8 features each
+      const bool in = F + 8 * c < N;
+      const uint16_t* s0 = B + (int64_t)J0 * 8 * ldb + F + (in ? 8 * c : 0);
+      const uint16_t* s1 = B + (int64_t)(two ? J1 : J0) * 8 * ldb + F + (in ? 8 * c : 0);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int r = 2 * i + rr;
-      const uint32_t off = r * Cfg::kRowBytes + (((c & ~7) | ((c ^ r) & 7)) << 4);
-      cp_async16(dst + off, s0 + (int64_t)r * ldb, in ? 16 : 0);
-      cp_async16(dst + 8 * Cfg::kRowBytes + off, s1 + (int64_t)r * ldb, (in && two) ? 16 : 0);
+      for (int i = 0; i < 4; ++i) {
+        const int r = 2 * i + rr;
+        const uint32_t off = r * Cfg::kRowBytes + (((c & ~7) | ((c ^ r) & 7)) << 4);
+        cp_async16(dst + off, s0 + (int64_t)r * ldb, in ? 16 : 0);
+        cp_async16(dst + 8 * Cfg::kRowBytes + off, s1 + (int64_t)r * ldb, (in && two) ? 16 : 0);
+      }
+      // the two blocks: 2 x 128 bytes = 16 chunks; the second is zero-filled for a half-empty pair
+      if (lane < 16)
+        cp_async16(dst + 16 * Cfg::kRowBytes + lane * 16,
+                   blocks + (b + ((lane >= 8 && two) ? 1 : 0)) * 64 + (lane & 7) * 8, (lane < 8 || two) ? 16 : 0);
+      ib = two ? b + 2 : b + 1;
+      while (ib == ire && ir + 1 < R) { ++ir; ire = row_start(ir + 1); }
+      slot_in = slot_in + 1 == D ? 0 : slot_in + 1;
     }
-    // the two blocks: 2 x 128 bytes = 16 chunks; the second is zero-filled when the row has an odd count
-    if (lane < 16)
-      cp_async16(dst + 16 * Cfg::kRowBytes + lane * 16,
-                 blocks + (bs + b + ((lane >= 8 && two) ? 1 : 0)) * 64 + (lane & 7) * 8, (lane < 8 || two) ? 16 : 0);
+    cp_async_commit();
   };
 
 #pragma unroll
-  for (int s = 0; s < D - 1; ++s) {
-    if (s < npair) issue(s, s);
-    cp_async_commit();
-  }
-  for (int p = 0; p < npair; ++p) {
-    cp_async_wait<D - 2>();
-    __syncwarp();
-    const int np = p + D - 1;
-    if (np < npair) issue(np, np % D);
-    cp_async_commit();
+  for (int s = 0; s < D - 1; ++s) issue_next();
 
-    const uint8_t* st = ring + (p % D) * Cfg::kStage;
-    const uint32_t b0 = *reinterpret_cast<const uint32_t*>(st + 16 * Cfg::kRowBytes + (g * 8 + 2 * t) * 2);
-    const uint32_t b1 = *reinterpret_cast<const uint32_t*>(st + 16 * Cfg::kRowBytes + 128 + (g * 8 + 2 * t) * 2);
-    const int sw0 = ((g ^ (2 * t)) & 7) << 4, sw1 = ((g ^ (2 * t + 1)) & 7) << 4;
-    // [row][half]: rows = (blk0 col 2t), (blk0 col 2t+1), (blk1 col 2t), (blk1 col 2t+1)
-    uint4 v[4][2];
+  int slot_out = 0;
+  for (int r = 0; r < R; ++r) {
+    float acc[8][4];
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      v[0][h] = *reinterpret_cast<const uint4*>(st + (2 * t) * Cfg::kRowBytes + h * 128 + sw0);
-      v[1][h] = *reinterpret_cast<const uint4*>(st + (2 * t + 1) * Cfg::kRowBytes + h * 128 + sw1);
-      v[2][h] = *reinterpret_cast<const uint4*>(st + (8 + 2 * t) * Cfg::kRowBytes + h * 128 + sw0);
-      v[3][h] = *reinterpret_cast<const uint4*>(st + (8 + 2 * t + 1) * Cfg::kRowBytes + h * 128 + sw1);
+    for (int j = 0; j < 8; ++j)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
+
+    const int64_t be = row_start(r + 1);
+    for (int64_t b = row_start(r); b < be; b += 2) {
+      cp_async_wait<D - 2>();
+      __syncwarp();
+      issue_next();
+
+      const uint8_t* st = ring + slot_out * Cfg::kStage;
+      slot_out = slot_out + 1 == D ? 0 : slot_out + 1;
+      const uint32_t b0 = *reinterpret_cast<const uint32_t*>(st + 16 * Cfg::kRowBytes + (g * 8 + 2 * t) * 2);
+      const uint32_t b1 = *reinterpret_cast<const uint32_t*>(st + 16 * Cfg::kRowBytes + 128 + (g * 8 + 2 * t) * 2);
+      const int sw0 = ((g ^ (2 * t)) & 7) << 4, sw1 = ((g ^ (2 * t + 1)) & 7) << 4;
+      // [row][half]: rows = (blk0 col 2t), (blk0 col 2t+1), (blk1 col 2t), (blk1 col 2t+1)
+      uint4 v[4][2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        v[0][h] = *reinterpret_cast<const uint4*>(st + (2 * t) * Cfg::kRowBytes + h * 128 + sw0);
+        v[1][h] = *reinterpret_cast<const uint4*>(st + (2 * t + 1) * Cfg::kRowBytes + h * 128 + sw1);
+        v[2][h] = *reinterpret_cast<const uint4*>(st + (8 + 2 * t) * Cfg::kRowBytes + h * 128 + sw0);
+        v[3][h] = *reinterpret_cast<const uint4*>(st + (8 + 2 * t + 1) * Cfg::kRowBytes + h * 128 + sw1);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        // feature j of the lane's 8: 32-bit word j/2, half-word j%2 of each 128-bit load
+        const uint32_t sel = (j & 1) ? 0x7632u : 0x5410u;  // (hi,hi) or (lo,lo) halves of two words
+        auto word = [&](const uint4& u) { return j < 2 ? u.x : (j < 4 ? u.y : (j < 6 ? u.z : u.w)); };
+        uint32_t a[4];
+        a[0] = __byte_perm(word(v[0][0]), word(v[1][0]), sel);  // m = g,   k = 2t, 2t+1
+        a[1] = __byte_perm(word(v[0][1]), word(v[1][1]), sel);  // m = g+8, k = 2t, 2t+1
+        a[2] = __byte_perm(word(v[2][0]), word(v[3][0]), sel);  // m = g,   k = 2t+8, 2t+9
+        a[3] = __byte_perm(word(v[2][1]), word(v[3][1]), sel);  // m = g+8, k = 2t+8, 2t+9
+        mma_16bit<BF16>(acc[j], a, b0, b1);
+      }
     }
+
+    float* c0 = C + ((I0 + r - block_row_begin) * 8 + 2 * t) * ldc + F + 8 * g;
+    float* c1 = c0 + ldc;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      // feature j of the lane's 8: 32-bit word j/2, half-word j%2 of each 128-bit load
-      const uint32_t sel = (j & 1) ? 0x7632u : 0x5410u;  // (hi,hi) or (lo,lo) halves of two words
-      auto word = [&](const uint4& u) { return j < 2 ? u.x : (j < 4 ? u.y : (j < 6 ? u.z : u.w)); };
-      uint32_t a[4];
-      a[0] = __byte_perm(word(v[0][0]), word(v[1][0]), sel);  // m = g,   k = 2t, 2t+1
-      a[1] = __byte_perm(word(v[0][1]), word(v[1][1]), sel);  // m = g+8, k = 2t, 2t+1
-      a[2] = __byte_perm(word(v[2][0]), word(v[3][0]), sel);  // m = g,   k = 2t+8, 2t+9
-      a[3] = __byte_perm(word(v[2][1]), word(v[3][1]), sel);  // m = g+8, k = 2t+8, 2t+9
-      mma_16bit<BF16>(acc[j], a, b0, b1);
+    for (int h = 0; h < 2; ++h) {  // features 8g + 4h .. +3
+      if (F + 8 * g < N) {
+        __stcs(reinterpret_cast<float4*>(c0 + 4 * h), make_float4(acc[4 * h][0], acc[4 * h + 1][0], acc[4 * h + 2][0], acc[4 * h + 3][0]));
+        __stcs(reinterpret_cast<float4*>(c1 + 4 * h), make_float4(acc[4 * h][1], acc[4 * h + 1][1], acc[4 * h + 2][1], acc[4 * h + 3][1]));
+      }
+      if (F + 64 + 8 * g < N) {
+        __stcs(reinterpret_cast<float4*>(c0 + 64 + 4 * h), make_float4(acc[4 * h][2], acc[4 * h + 1][2], acc[4 * h + 2][2], acc[4 * h + 3][2]));
+        __stcs(reinterpret_cast<float4*>(c1 + 64 + 4 * h), make_float4(acc[4 * h][3], acc[4 * h + 1][3], acc[4 * h + 2][3], acc[4 * h + 3][3]));
+      }
     }
   }
   cp_async_wait<0>();
-
-  float* c0 = C + ((I - block_row_begin) * 8 + 2 * t) * ldc + F + 8 * g;
-  float* c1 = c0 + ldc;
-#pragma unroll
-  for (int h = 0; h < 2; ++h) {  // features 8g + 4h .. +3
-    if (F + 8 * g < N) {
-      __stcs(reinterpret_cast<float4*>(c0 + 4 * h), make_float4(acc[4 * h][0], acc[4 * h + 1][0], acc[4 * h + 2][0], acc[4 * h + 3][0]));
-      __stcs(reinterpret_cast<float4*>(c1 + 4 * h), make_float4(acc[4 * h][1], acc[4 * h + 1][1], acc[4 * h + 2][1], acc[4 * h + 3][1]));
-    }
-    if (F + 64 + 8 * g < N) {
-      __stcs(reinterpret_cast<float4*>(c0 + 64 + 4 * h), make_float4(acc[4 * h][2], acc[4 * h + 1][2], acc[4 * h + 2][2], acc[4 * h + 3][2]));
-      __stcs(reinterpret_cast<float4*>(c1 + 64 + 4 * h), make_float4(acc[4 * h][3], acc[4 * h + 1][3], acc[4 * h + 2][3], acc[4 * h + 3][3]));
-    }
-  }
 }
 
 // tuning state of the block kernels (lf_bsr_set_tuning)
 int g_bsr_feat_units = 0;   // 0 = automatic, 1 or 2 = features per warp / 64 of the float32 kernel
 int g_bsr_stages = 0;       // 0 = automatic, 3 or 4 = depth of the per-warp copy ring
+int g_bsr_rows_per_warp = 0;  // 0 = automatic (4 float32, 8 16-bit); block rows one warp streams through, 1..31
 
 int check_common(const void* indptr, const void* indices, const void* blocks, int64_t r0, int64_t r1,
                  const void* B, int64_t ldb, const void* C, int64_t ldc, int N, int feat_align) {
@@ -362,10 +403,12 @@ using namespace lf;
 
 extern "C" {
 
-int lf_bsr_set_tuning(int32_t feat_units, int32_t stages) {
-  LF_REQUIRE(feat_units >= 0 && feat_units <= 2 && (stages == 0 || stages == 3 || stages == 4), "bad tuning values");
+int lf_bsr_set_tuning(int32_t feat_units, int32_t stages, int32_t rows_per_warp) {
+  LF_REQUIRE(feat_units >= 0 && feat_units <= 2 && (stages == 0 || stages == 3 || stages == 4) &&
+                 rows_per_warp >= 0 && rows_per_warp <= 31, "bad tuning values");
   g_bsr_feat_units = feat_units;
   g_bsr_stages = stages;
+  g_bsr_rows_per_warp = rows_per_warp;
   return LF_OK;
 }
 
@@ -379,14 +422,15 @@ int lf_spmm_bsr8_f32(const int64_t* indptr, const int32_t* indices, const float*
   const int T = g_bsr_feat_units ? g_bsr_feat_units : (N > 64 ? 2 : 1);
   const int D = g_bsr_stages ? g_bsr_stages : (T == 2 ? 3 : 4);
   const int tiles = (N + 64 * T - 1) / (64 * T);
-  const int64_t grid = ceil_div64(rows * tiles, kWarps);
+  const int rpw = g_bsr_rows_per_warp ? g_bsr_rows_per_warp : 4;
+  const int64_t grid = ceil_div64(ceil_div64(rows, rpw) * tiles, kWarps);
   LF_REQUIRE(grid < (1ll << 31), "too many thread blocks");
 #define LF_BSR(T_, D_, M_)                                                                                   \
   do {                                                                                                       \
     auto k = bsr8_spmm_f32_kernel<T_, D_, M_>;                                                               \
     if (int s = set_smem(k, F32Cfg<T_, D_>::kSmem)) return s;                                                \
     k<<<(unsigned)grid, kThreadsBsr, F32Cfg<T_, D_>::kSmem, st>>>(indptr, indices, blocks, block_row_begin,  \
-                                                                  block_row_end, B, (int)ldb, C, ldc, N, tiles); \
+                                                                  block_row_end, B, (int)ldb, C, ldc, N, tiles, rpw); \
   } while (0)
   if (T == 2) { if (D == 3) LF_BSR(2, 3, 2); else LF_BSR(2, 4, 1); }
   else        { if (D == 3) LF_BSR(1, 3, 3); else LF_BSR(1, 4, 3); }
@@ -402,7 +446,8 @@ static int launch_16bit(bool bf16, const int64_t* indptr, const int32_t* indices
   if (r0 == r1) return LF_OK;
   cudaStream_t st = (cudaStream_t)stream;
   const int tiles = (N + 127) / 128;
-  const int64_t grid = ceil_div64((r1 - r0) * tiles, kWarps);
+  const int rpw = g_bsr_rows_per_warp ? g_bsr_rows_per_warp : 8;
+  const int64_t grid = ceil_div64(ceil_div64(r1 - r0, rpw) * tiles, kWarps);
   LF_REQUIRE(grid < (1ll << 31), "too many thread blocks");
   const int D = g_bsr_stages ? g_bsr_stages : 3;
 #define LF_BSR16(B_, D_, M_)                                                                                  \
@@ -410,7 +455,7 @@ static int launch_16bit(bool bf16, const int64_t* indptr, const int32_t* indices
     auto k = bsr8_spmm_16bit_kernel<B_, D_, M_>;                                                              \
     if (int s = set_smem(k, H16Cfg<D_>::kSmem)) return s;                                                     \
     k<<<(unsigned)grid, kThreadsBsr, H16Cfg<D_>::kSmem, st>>>(indptr, indices, blocks, r0, r1, B, (int)ldb, C, \
-                                                              ldc, N, tiles);                                 \
+                                                              ldc, N, tiles, rpw);                            \
   } while (0)
   if (bf16) { if (D == 3) LF_BSR16(true, 3, 2); else LF_BSR16(true, 4, 1); }
   else      { if (D == 3) LF_BSR16(false, 3, 2); else LF_BSR16(false, 4, 1); }
