@@ -80,6 +80,29 @@ int lf_hyb_stats(const int64_t* indptr /*[dev] M+1*/, const int32_t* indices /*[
                  void* workspace /*[dev]*/, size_t workspace_bytes, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * lf_hyb_stats without any workspace argument.  It has no counterpart in the reference; it is
+ * lf_hyb_stats for callers that must not allocate device memory and cannot be handed a scratch
+ * buffer either: a call site inside a serving loop that promised the rest of the process a fixed
+ * memory footprint, or a plugin whose host owns the allocator (a cudaMalloc there would also
+ * synchronise the whole device in the middle of somebody else's work).  The per-column scratch
+ * lives in a static device array inside the library instead, LF_STATIC_STATS_MAX_COLS * 4 bytes
+ * (4 MiB) on every GPU that loads the library, until the process exits.
+ *   - matrices with more than LF_STATIC_STATS_MAX_COLS columns are refused (LF_ERR_UNSUPPORTED);
+ *   - the first call on a device looks up the array's device address (a one-time set-up that is
+ *     not stream work), so make that first call before any stream capture begins;
+ *   - the array is shared by all calls and keeps whatever the last call left in it: each call
+ *     clears the part it uses on `stream` first, and two calls that may overlap on the GPU
+ *     (different streams, or host threads on different streams) race on it -- serialise them;
+ *   - no cudaMalloc, cudaFree or other allocating routine is called; class_stats and
+ *     colmask_hist are the caller's buffers exactly as for lf_hyb_stats.
+ * ------------------------------------------------------------------------------------------- */
+#define LF_STATIC_STATS_MAX_COLS (1 << 20)
+int lf_hyb_stats_static(const int64_t* indptr /*[dev] M+1*/, const int32_t* indices /*[dev] nnz*/,
+                        int64_t num_rows, int64_t num_cols, int32_t num_parts,
+                        int64_t* class_stats /*[dev] P*11*3*/, int64_t* colmask_hist /*[dev] P*2048*/,
+                        void* stream);
+
+/* ---------------------------------------------------------------------------------------------
  * Description of a composed (column-partitioned, bucketed ELL) matrix in device memory.
  * This is the device form of build_hyb_format's return value (format_algos.py:226-237, 385):
  * for partition p and bucket b (global bucket index i = part_bucket_off[p] + b, width widths[i])

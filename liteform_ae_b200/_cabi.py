@@ -25,6 +25,7 @@ LF_SPMM_OVERWRITE = 0
 LF_SPMM_ACCUMULATE = 1
 NUM_WIDTH_CLASSES = 11
 COLMASK_BINS = 2048
+STATIC_STATS_MAX_COLS = 1 << 20
 
 i32p = C.POINTER(C.c_int32)
 i64p = C.POINTER(C.c_int64)
@@ -59,6 +60,7 @@ SIGNATURES = {
     "lf_set_option": (C.c_int, [C.c_int32, C.c_int32]),
     "lf_hyb_stats_workspace_bytes": (C.c_size_t, [C.c_int64, C.c_int64, C.c_int32]),
     "lf_hyb_stats": (C.c_int, [vp, vp, C.c_int64, C.c_int64, C.c_int32, vp, vp, vp, C.c_size_t, vp]),
+    "lf_hyb_stats_static": (C.c_int, [vp, vp, C.c_int64, C.c_int64, C.c_int32, vp, vp, vp]),
     "lf_hyb_build_workspace_bytes": (C.c_size_t, [C.c_int64, C.c_int64, C.c_int32, C.c_int32]),
     "lf_hyb_fill_scratch_bytes": (C.c_size_t, [C.c_int64]),
     "lf_hyb_plan": (C.c_int, [vp, vp, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int32, vp, vp,

@@ -7,6 +7,8 @@
 //
 // None of the kernels below waits on another thread block: offsets across blocks come from a
 // separate scan launch, never from a look-back spin.
+#include <mutex>
+
 #include "lf_common.cuh"
 
 namespace lf {
@@ -417,6 +419,53 @@ int lf_hyb_stats(const int64_t* indptr, const int32_t* indices, int64_t num_rows
     LF_CUDA_CHECK(cudaGetLastError());
   }
   return LF_OK;
+}
+
+// ---- allocation-free statistics -------------------------------------------------------------
+// Scratch of lf_hyb_stats_static: the per-column class-mask array, resident in every device
+// that loads this library until the process exits.
+#define LF_STATIC_STATS_MAX_COLS_IMPL (1 << 20)
+static __device__ __align__(256) uint32_t g_static_colmask[LF_STATIC_STATS_MAX_COLS_IMPL];
+static_assert(LF_STATIC_STATS_MAX_COLS_IMPL == LF_STATIC_STATS_MAX_COLS, "header and implementation disagree");
+
+// In host code `g_static_colmask` is only a handle of the symbol, not an address a kernel can
+// use; the device address is looked up once per device (with that device current) and kept.
+static uint32_t* static_colmask_address(int* status) {
+  constexpr int kMaxDevices = 64;
+  static uint32_t* addr[kMaxDevices] = {nullptr};
+  static std::mutex lock;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    *status = fail(LF_ERR_CUDA, "cudaGetDevice failed or device ordinal %d unsupported: %s", dev, cudaGetErrorString(e));
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> guard(lock);
+  if (!addr[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_static_colmask);
+    if (e != cudaSuccess || !p) {
+      *status = fail(LF_ERR_CUDA, "cudaGetSymbolAddress(static scratch) failed on device %d: %s", dev, cudaGetErrorString(e));
+      return nullptr;
+    }
+    addr[dev] = (uint32_t*)p;
+  }
+  *status = LF_OK;
+  return addr[dev];
+}
+
+int lf_hyb_stats_static(const int64_t* indptr, const int32_t* indices, int64_t num_rows, int64_t num_cols,
+                        int32_t num_parts, int64_t* class_stats, int64_t* colmask_hist, void* stream) {
+  if (num_cols > LF_STATIC_STATS_MAX_COLS)
+    return fail(LF_ERR_UNSUPPORTED,
+                "lf_hyb_stats_static handles at most %d columns (got %lld); use lf_hyb_stats with a caller-owned workspace",
+                LF_STATIC_STATS_MAX_COLS, (long long)num_cols);
+  int status = LF_OK;
+  uint32_t* scratch = static_colmask_address(&status);
+  if (!scratch) return status;
+  // same launches as lf_hyb_stats, which clears the part of the scratch it is about to use
+  return lf_hyb_stats(indptr, indices, num_rows, num_cols, num_parts, class_stats, colmask_hist, scratch,
+                      sizeof(uint32_t) * (size_t)LF_STATIC_STATS_MAX_COLS, stream);
 }
 
 size_t lf_hyb_build_workspace_bytes(int64_t row_begin, int64_t row_end, int32_t num_parts,
