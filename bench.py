@@ -450,7 +450,11 @@ def run_ours(args, rank, local_rank, world):
 # summarised under profiles/; keyed by (workload, format, dtype, N, num_parts, n_gpus).  Absent
 # entries are reported as null.
 TRAFFIC_BYTES_PER_LAUNCH = {
-    ("powerlaw", "hyb", "f32", 128, 1, 1): 3123957760 + 543622144,
+    # profiles/spmm_hyb_powerlaw_n128.md (full-size capture)
+    ("powerlaw", "hyb", "f32", 128, 1, 1): 3124605000 + 543989248,
+    # profiles/spmm_bsr8_blocks_n128.md (captured at 2^20 rows, scaled x2 to the 2^21-row matrix)
+    ("blocks", "bsr8", "f32", 128, 1, 1): 2 * (918607360 + 508638720),
+    ("blocks", "bsr8", "bf16", 128, 1, 1): 2 * (494361600 + 492801280),
 }
 
 
