@@ -53,7 +53,7 @@ const char* lf_last_error(void);
 
 /* Process-wide tuning knobs of the SpMM launch (no counterpart in the reference, whose launch
  * shape is fixed by its code generator, format_algos.py:503-539).  Results do not depend on them. */
-#define LF_OPT_SPMM_SLOTS_PER_GROUP 1  /* ELL slots one thread group walks (default 256)          */
+#define LF_OPT_SPMM_SLOTS_PER_GROUP 1  /* ELL slots one thread group walks (0 = automatic: 256, less for small launches) */
 #define LF_OPT_SPMM_CACHE_POLICY 2     /* 0 plain; 1 stream slots and C (default); 2 also B rows evict-last */
 #define LF_OPT_SPMM_MIN_BLOCKS 3       /* resident thread blocks per SM the kernel is compiled for: 2..4 (default 3) */
 int lf_set_option(int32_t option, int32_t value);

@@ -314,13 +314,29 @@ FeatCfg pick_cfg(const void* B, int64_t ldb, const void* C, int64_t ldc, int N) 
 int g_slots_per_group = 0;
 int g_cache_policy = -1;
 
+// 0 = automatic: 256 slots per group, halved (down to 32) while the launch would have fewer than
+// eight waves of thread blocks, so that small shards do not lose a third of the time in the tail.
 int slots_per_group() {
-  if (!g_slots_per_group) {
+  static bool env_read = false;
+  if (!env_read) {
+    env_read = true;
     const char* e = getenv("LF_SPMM_SLOTS_PER_GROUP");
-    int v = e ? atoi(e) : 0;
-    g_slots_per_group = (v >= 8 && v <= (1 << 20)) ? v : 256;
+    const int v = e ? atoi(e) : 0;
+    if (!g_slots_per_group && v >= 8 && v <= (1 << 20)) g_slots_per_group = v;
   }
   return g_slots_per_group;
+}
+
+int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (!cached[dev]) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
 }
 
 int g_min_blocks = 0;
@@ -402,7 +418,7 @@ extern "C" {
 int lf_set_option(int32_t option, int32_t value) {
   switch (option) {
     case LF_OPT_SPMM_SLOTS_PER_GROUP:
-      LF_REQUIRE(value >= 8 && value <= (1 << 20), "slots per group %d out of range", value);
+      LF_REQUIRE(value == 0 || (value >= 8 && value <= (1 << 20)), "slots per group %d out of range", value);
       g_slots_per_group = value;
       return LF_OK;
     case LF_OPT_SPMM_CACHE_POLICY:
@@ -450,7 +466,19 @@ int lf_spmm_hyb_f32(const lf_hyb* A, const float* B, int64_t ldb, float* C, int6
 
   // one launch per LF_MAX_BUCKETS_PER_LAUNCH non-empty buckets (one launch in every practical case)
   const int gpc = kThreads / cfg.G;
-  const int spg = slots_per_group();
+  int spg = slots_per_group();
+  if (!spg) {
+    const int64_t want_tiles = (int64_t)sm_count() * min_blocks() * 8;
+    for (spg = 256; spg > 32; spg >>= 1) {
+      int64_t t = 0;
+      for (int k = 0; k < A->num_buckets; ++k) {
+        const int w = A->widths[k];
+        const int rpg = spg / w > 0 ? spg / w : 1;
+        t += ceil_div64(A->ell_rows[k], (int64_t)rpg * gpc);
+      }
+      if (t >= want_tiles) break;
+    }
+  }
   int i = 0;
   while (i < A->num_buckets) {
     static thread_local SpmmTable<LF_MAX_BUCKETS_PER_LAUNCH> big;
