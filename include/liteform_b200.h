@@ -133,6 +133,9 @@ typedef struct lf_hyb {
   const uint8_t* mask;              /* [dev] slot_off[num_buckets] or NULL                 */
   const int32_t* zero_rows;         /* [dev] num_zero_rows or NULL                         */
   int64_t num_zero_rows;
+  const uint32_t* hot_bits;         /* [dev] slot_off[num_buckets]/32 words or NULL: bit k of word j is
+                                       set when slot 32*j + k gathers a frequently used row of B; only
+                                       read under cache policy 2, a pure performance hint             */
 } lf_hyb;
 
 /* ---------------------------------------------------------------------------------------------

@@ -42,7 +42,7 @@ class LfHyb(C.Structure):
         ("num_parts", C.c_int32), ("num_buckets", C.c_int32),
         ("part_bucket_off", vp), ("widths", vp), ("ell_rows", vp), ("row_off", vp), ("slot_off", vp),
         ("rows", vp), ("cols", vp), ("vals", vp), ("mask", vp), ("zero_rows", vp),
-        ("num_zero_rows", C.c_int64),
+        ("num_zero_rows", C.c_int64), ("hot_bits", vp),
     ]
 
 

@@ -53,6 +53,11 @@ __device__ __forceinline__ uint64_t l2_policy_evict_last() {
   asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
   return p;
 }
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
 
 template <int VEC> struct Chunk;
 template <> struct Chunk<4> {
@@ -96,7 +101,8 @@ __device__ __forceinline__ void walk_slots(const int32_t* __restrict__ rows, con
                                            const float* __restrict__ vals, int wlog, int64_t e0, int64_t e1,
                                            int64_t ell_rows, bool all_open, const float* __restrict__ B,
                                            int ldb, float* __restrict__ C, int64_t ldc, int N,
-                                           int64_t row_base, int lane, unsigned gmask, int2* cv, int* rd) {
+                                           int64_t row_base, int lane, unsigned gmask, int2* cv, int* rd,
+                                           const uint32_t* __restrict__ hot) {
   constexpr int U = V == 1 ? 8 : (V == 2 ? 4 : 2);  // gathers in flight per lane (x V chunks)
   static_assert(G % U == 0 && 8 % U == 0, "unroll must divide the group size and the batch");
   const int first_row = rows[e0], last_row = rows[e1 - 1];
@@ -113,8 +119,11 @@ __device__ __forceinline__ void walk_slots(const int32_t* __restrict__ rows, con
     acc[v].zero();
   }
   int cur = first_row;
-  uint64_t keep = 0;
-  if (POL == 2) keep = l2_policy_evict_last();
+  uint64_t keep = 0, drop = 0;
+  if (POL == 2) {
+    keep = l2_policy_evict_last();
+    drop = hot ? l2_policy_evict_first() : keep;
+  }
 
   auto flush = [&](int row) {
     const bool open = all_open || (row == first_row && head_open) || (row == last_row && tail_open);
@@ -139,6 +148,8 @@ __device__ __forceinline__ void walk_slots(const int32_t* __restrict__ rows, con
     const int my_col = POL >= 1 ? __ldcs(cols + cidx) : cols[cidx];
     const float my_val = in ? (POL >= 1 ? __ldcs(vals + cidx) : vals[cidx]) : 0.f;
     const int my_rid = rows[cidx >> wlog];
+    uint32_t hot_word = 0xffffffffu;   // bit k: slot s + k gathers a frequently used row of B
+    if (POL == 2 && hot) hot_word = __ldg(hot + (s >> 5)) >> (int)(s & 31);
     __syncwarp(gmask);  // the previous strip has been consumed by every lane of the group
     cv[lane] = make_int2(my_col, __float_as_int(my_val));
     rd[lane] = my_rid;
@@ -155,7 +166,8 @@ __device__ __forceinline__ void walk_slots(const int32_t* __restrict__ rows, con
 #pragma unroll
         for (int v = 0; v < V; ++v) {
           if (val[u] != 0.f && active[v]) {
-            if (POL == 2) b[u][v].load_keep(src + v * G * VEC, keep); else b[u][v].load(src + v * G * VEC);
+            if (POL == 2) b[u][v].load_keep(src + v * G * VEC, ((hot_word >> (t + u)) & 1u) ? keep : drop);
+            else b[u][v].load(src + v * G * VEC);
           } else {
             b[u][v].zero();
           }
@@ -185,7 +197,7 @@ __global__ void __launch_bounds__(kThreads, MINB)
 spmm_hyb_kernel(const __grid_constant__ SpmmTable<MAXB> tbl, const int32_t* __restrict__ rows_arena,
                 const int32_t* __restrict__ cols_arena, const float* __restrict__ vals_arena,
                 const float* __restrict__ B, int ldb, float* __restrict__ C, int64_t ldc, int N,
-                int64_t row_base) {
+                int64_t row_base, const uint32_t* __restrict__ hot_arena) {
   constexpr int GPC = kThreads / G;  // groups per thread block
   __shared__ int2 s_cv[kThreads];
   __shared__ int s_rd[kThreads];
@@ -209,9 +221,10 @@ spmm_hyb_kernel(const __grid_constant__ SpmmTable<MAXB> tbl, const int32_t* __re
   const bool all_open = d.force_atomic != 0;
   int2* cv = s_cv + g * G;
   int* rd = s_rd + g * G;
+  const uint32_t* hot = hot_arena ? hot_arena + (d.slot_off >> 5) : nullptr;
 #define LF_WALK(WC_)                                                                                     \
   walk_slots<G, V, VEC, WC_, POL>(rows, cols, vals, wlog, e0, e1, d.ell_rows, all_open, B, ldb, C, ldc, \
-                                  N, row_base, lane, gmask, cv, rd)
+                                  N, row_base, lane, gmask, cv, rd, hot)
   switch (wlog) {
     case 0: LF_WALK(1); break;
     case 1: LF_WALK(2); break;
@@ -364,7 +377,7 @@ int launch_hyb_pol(const SpmmTable<MAXB>& tbl, int64_t tiles, const lf_hyb* A, c
   dim3 grid((unsigned)tiles, (unsigned)((N + cfg.pass - 1) / cfg.pass));
 #define LF_LAUNCH(G_, V_, VEC_)                                                                          \
   spmm_hyb_kernel<G_, V_, VEC_, MAXB, POL, MINB><<<grid, kThreads, 0, st>>>(tbl, A->rows, A->cols, A->vals, \
-                                                                           B, (int)ldb, C, ldc, N, A->row_begin)
+                                                                           B, (int)ldb, C, ldc, N, A->row_begin, A->hot_bits)
   if (cfg.VEC == 4) {
     if (cfg.G == 8) LF_LAUNCH(8, 1, 4);
     else if (cfg.G == 16) LF_LAUNCH(16, 1, 4);
@@ -563,6 +576,7 @@ int lf_spmm_hyb_f32_host(const lf_hyb* A, const float* B, float* C, int32_t N, i
   dev.cols = (const int32_t*)(ws + off[1]);
   dev.vals = (const float*)(ws + off[2]);
   dev.mask = nullptr;
+  dev.hot_bits = nullptr;
   dev.zero_rows = (const int32_t*)(ws + off[3]);
   if (int s = lf_spmm_hyb_f32(&dev, (const float*)(ws + off[4]), N, (float*)(ws + off[5]), N, N, flags, st)) return s;
   if (c_bytes) LF_CUDA_CHECK(cudaMemcpyAsync(C, ws + off[5], c_bytes, cudaMemcpyDeviceToHost, st));

@@ -92,6 +92,7 @@ class HybFormat:
         self.row_off = np.ascontiguousarray(row_off, dtype=np.int64)
         self.slot_off = np.ascontiguousarray(slot_off, dtype=np.int64)
         self.rows, self.cols, self.vals, self.mask, self.zero_rows = rows, cols, vals, mask, zero_rows
+        self.hot_bits = None     # optional uint32 device tensor, one bit per slot (see struct lf_hyb)
 
     # -- C view ---------------------------------------------------------------------------
     def c_struct(self, host_arrays=None) -> LfHyb:
@@ -117,6 +118,7 @@ class HybFormat:
             s.rows, s.cols, s.vals, s.mask = np_ptr(r), np_ptr(c), np_ptr(v), 0
             s.zero_rows = np_ptr(z) if self.num_zero_rows else 0
         s.num_zero_rows = self.num_zero_rows
+        s.hot_bits = t_ptr(self.hot_bits) if (host_arrays is None and self.hot_bits is not None) else 0
         return s
 
     @property

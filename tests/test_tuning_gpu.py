@@ -1,0 +1,68 @@
+"""Tuning knobs select differently compiled kernels; none of them may change the result."""
+import itertools
+
+import numpy as np
+import pytest
+
+from oracle import hyb_oracle as ho
+from liteform_ae_b200 import _cabi, bsr, hyb, synth
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture
+def restore_defaults():
+    yield
+    lib = _cabi.load()
+    lib.lf_set_option(_cabi.LF_OPT_SPMM_CACHE_POLICY, 1)
+    lib.lf_set_option(_cabi.LF_OPT_SPMM_MIN_BLOCKS, 3)
+    lib.lf_set_option(_cabi.LF_OPT_SPMM_SLOTS_PER_GROUP, 0)
+    lib.lf_bsr_set_tuning(0, 0, 0)
+
+
+def test_every_spmm_variant_gives_the_same_product(cuda_device, restore_defaults):
+    import torch
+    lib = _cabi.load()
+    csr = synth.skewed_rows(M=4096, seed=5, heavy_rows=6, heavy_len=3000)
+    d = hyb.DeviceCsr.from_host(csr.indptr, csr.indices, csr.data, csr.shape, cuda_device)
+    fmt = hyb.build_hyb_device(d, [[1, 2, 4, 8, 16]], with_mask=False)
+    # per-slot hint bits for policy 2: mark every other slot; hints must never change values
+    words = (int(fmt.slot_off[-1]) + 31) // 32
+    hot = torch.full((words,), 0x55555555, dtype=torch.int32, device=cuda_device)
+    for N in (32, 128, 512):
+        B = synth.dense_features(4096, N, 2)
+        Bd = torch.from_numpy(B).to(cuda_device)
+        want = ho.spmm_scipy_csr(csr.indptr, csr.indices, csr.data.astype(np.float64), csr.shape, B.astype(np.float64))
+        for pol, minb, slots in itertools.product((0, 1, 2), (2, 3, 4), (0, 8, 64, 4096)):
+            assert lib.lf_set_option(_cabi.LF_OPT_SPMM_CACHE_POLICY, pol) == 0
+            assert lib.lf_set_option(_cabi.LF_OPT_SPMM_MIN_BLOCKS, minb) == 0
+            assert lib.lf_set_option(_cabi.LF_OPT_SPMM_SLOTS_PER_GROUP, slots) == 0
+            for bits in ((None, hot) if pol == 2 else (None,)):
+                fmt.hot_bits = bits
+                C = hyb.spmm_hyb(fmt, Bd).cpu().numpy()
+                np.testing.assert_allclose(C, want, rtol=1e-5, atol=1e-4, err_msg=f"{N} {pol} {minb} {slots}")
+        fmt.hot_bits = None
+    assert lib.lf_set_option(_cabi.LF_OPT_SPMM_MIN_BLOCKS, 7) == _cabi.LF_ERR_INVALID_ARGUMENT
+    assert lib.lf_set_option(99, 1) == _cabi.LF_ERR_INVALID_ARGUMENT
+
+
+def test_every_block_kernel_variant_gives_the_same_product(cuda_device, restore_defaults):
+    import scipy.sparse as sp
+    import torch
+    lib = _cabi.load()
+    indptr, indices, blocks, shape = synth.banded_blocks(M=2048, seed=3, per_block_row=7, half_band=50)
+    A = sp.bsr_matrix((blocks.astype(np.float64), indices, indptr), shape=shape)
+    a32 = bsr.DeviceBsr8.from_arrays(indptr, indices, blocks, shape, "float32", cuda_device)
+    a16 = bsr.DeviceBsr8.from_arrays(indptr, indices, blocks, shape, "bfloat16", cuda_device)
+    A16 = sp.bsr_matrix((a16.blocks.float().cpu().numpy().astype(np.float64), indices, indptr), shape=shape)
+    for N in (64, 136, 256):
+        B = synth.dense_features(shape[1], N, 4)
+        Bd = torch.from_numpy(B).to(cuda_device)
+        B16 = Bd.to(torch.bfloat16)
+        want = A @ B.astype(np.float64)
+        want16 = A16 @ B16.float().cpu().numpy().astype(np.float64)
+        for units, stages, rpw in itertools.product((0, 1, 2), (0, 3, 4), (0, 1, 5, 31)):
+            assert lib.lf_bsr_set_tuning(units, stages, rpw) == 0
+            np.testing.assert_allclose(bsr.spmm_bsr8(a32, Bd).cpu().numpy(), want, rtol=1e-5, atol=1e-4)
+            np.testing.assert_allclose(bsr.spmm_bsr8(a16, B16).cpu().numpy(), want16, rtol=1e-5, atol=1e-4)
+    assert lib.lf_bsr_set_tuning(3, 0, 0) == _cabi.LF_ERR_INVALID_ARGUMENT
