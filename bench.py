@@ -265,6 +265,42 @@ class HybProblem:
     def cpu_matrix(self):
         return self.csr.toscipy()
 
+    def per_bucket(self, repeat):
+        """Time every bucket on its own (a one-bucket view of the same arenas).  Bytes per bucket:
+        compulsory = slots' index+value of real entries, row ids, touched B rows once, C rows once;
+        gather = every real entry fetches its own B row."""
+        torch, hyb, fmt, N = self.torch, self.hyb, self.fmt, self.N
+        cols = fmt.cols.cpu().numpy()
+        vals = fmt.vals.cpu().numpy()
+        rows = fmt.rows.cpu().numpy()
+        out = []
+        for i in range(len(fmt.widths)):
+            R, w = int(fmt.ell_rows[i]), int(fmt.widths[i])
+            if R == 0:
+                continue
+            so, ro = int(fmt.slot_off[i]), int(fmt.row_off[i])
+            sub = hyb.HybFormat(fmt.shape, (fmt.row_begin, fmt.row_end), [[w]], [R], [ro, int(fmt.row_off[i + 1])],
+                                [so, int(fmt.slot_off[i + 1])], fmt.rows, fmt.cols, fmt.vals, None, None)
+            # accumulate: no clearing launch, every flush is an atomic only where rows are shared
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(repeat + 1)]
+            for _ in range(3):
+                hyb.spmm_hyb(sub, self.B, out=self.C)
+            ev[0].record()
+            for k in range(repeat):
+                hyb.spmm_hyb(sub, self.B, out=self.C)
+                ev[k + 1].record()
+            torch.cuda.synchronize(self.dev)
+            ms = statistics.median(ev[k].elapsed_time(ev[k + 1]) for k in range(repeat))
+            real = vals[so:so + R * w] != 0
+            nnz_b = int(real.sum())
+            touched = int(np.unique(cols[so:so + R * w][real]).size)
+            nrows = int(np.unique(rows[ro:ro + R]).size)
+            comp = nnz_b * 8 + 4 * R + touched * N * 4 + nrows * N * 4
+            gath = nnz_b * 8 + 4 * R + nnz_b * N * 4 + nrows * N * 4
+            out.append({"width": w, "ell_rows": R, "nnz": nnz_b, "ms": ms, "gflops": 2.0 * nnz_b * N / ms / 1e6,
+                        "compulsory_gbs": comp / ms / 1e6, "gather_model_gbs": gath / ms / 1e6})
+        return out
+
 
 class BsrProblem:
     """8x8 block path (config 5): block rows split evenly over the ranks (every block row holds
@@ -443,6 +479,8 @@ def run_ours(args, rank, local_rank, world):
         "gpu_launches": prob.launches_per_step * args.steps,
     }
     line.update(prob.extra)
+    if args.per_bucket and hasattr(prob, "per_bucket"):
+        line["per_bucket"] = prob.per_bucket(20)
     print(json.dumps(line), flush=True)
 
 
@@ -472,6 +510,7 @@ def main():
     ap.add_argument("--format", default="auto", choices=["auto", "hyb", "bsr8"],
                     help="auto: 8x8 block kernels for the block workload, composed format otherwise")
     ap.add_argument("--dtype", default="f32", choices=["f32", "bf16", "f16"], help="input type of the block path")
+    ap.add_argument("--per-bucket", action="store_true", help="also time every ELL bucket on its own")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-memory end-to-end leg (profiling runs)")
     args = ap.parse_args()
