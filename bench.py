@@ -490,6 +490,9 @@ def run_ours(args, rank, local_rank, world):
 TRAFFIC_BYTES_PER_LAUNCH = {
     # profiles/spmm_hyb_powerlaw_n128.md (full-size capture)
     ("powerlaw", "hyb", "f32", 128, 1, 1): 3124605000 + 543989248,
+    # profiles/spmm_hyb_uniform_n64_skew_n256.md (full-size captures)
+    ("uniform", "hyb", "f32", 64, 1, 1): 33724907264 + 1074169856,
+    ("skew", "hyb", "f32", 256, 1, 1): 21397719552 + 1109027072,
     # profiles/spmm_bsr8_blocks_n128.md (captured at 2^20 rows, scaled x2 to the 2^21-row matrix)
     ("blocks", "bsr8", "f32", 128, 1, 1): 2 * (918607360 + 508638720),
     ("blocks", "bsr8", "bf16", 128, 1, 1): 2 * (494361600 + 492801280),

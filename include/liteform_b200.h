@@ -228,6 +228,16 @@ int lf_spmm_bsr8_f16(const int64_t* indptr, const int32_t* indices, const uint16
                      float* C, int64_t ldc, int32_t N, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * Row-length statistics behind MTX.matrix_features (playground_pipline/format_matrix_market.py:
+ * 153-202, a Python loop over all rows in the reference).  One record of four uint64 per block of
+ * 256 rows: sum, sum of squares, minimum, maximum of the row lengths of rows [row_begin, row_end).
+ * partials holds lf_row_stats_blocks() * 4 values; the caller folds the exact integers.
+ * ------------------------------------------------------------------------------------------- */
+int64_t lf_row_stats_blocks(int64_t row_begin, int64_t row_end);
+int lf_row_stats(const int64_t* indptr /*[dev]*/, int64_t row_begin, int64_t row_end,
+                 uint64_t* partials /*[dev]*/, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
  * nnz-balanced contiguous row ranges for G devices: splits[g] = first row r with
  * indptr[r] >= g*nnz/G, splits[0] = 0, splits[G] = M.  (No counterpart in the reference, which
  * runs on device 0 only, format_algos.py:548.)

@@ -74,6 +74,8 @@ SIGNATURES = {
     "lf_spmm_bsr8_f32": (C.c_int, [vp, vp, vp, C.c_int64, C.c_int64, vp, C.c_int64, vp, C.c_int64, C.c_int32, vp]),
     "lf_spmm_bsr8_bf16": (C.c_int, [vp, vp, vp, C.c_int64, C.c_int64, vp, C.c_int64, vp, C.c_int64, C.c_int32, vp]),
     "lf_spmm_bsr8_f16": (C.c_int, [vp, vp, vp, C.c_int64, C.c_int64, vp, C.c_int64, vp, C.c_int64, C.c_int32, vp]),
+    "lf_row_stats_blocks": (C.c_int64, [C.c_int64, C.c_int64]),
+    "lf_row_stats": (C.c_int, [vp, C.c_int64, C.c_int64, vp, vp]),
     "lf_shard_rows": (C.c_int, [vp, C.c_int64, C.c_int32, vp, vp]),
 }
 

@@ -333,6 +333,40 @@ __global__ void shard_rows_kernel(const int64_t* __restrict__ indptr, int64_t nu
   splits[g] = lo;
 }
 
+// Row-length statistics for MTX.matrix_features (format_matrix_market.py:153-202): per block of
+// 256 rows the sum, the sum of squares, the minimum and the maximum of the row lengths.  The
+// partials stay exact integers; the caller folds them (in arbitrary precision) into mean / std.
+__global__ void __launch_bounds__(kRowsPerBlock)
+row_stats_kernel(const int64_t* __restrict__ indptr, int64_t row_begin, int64_t row_end,
+                 unsigned long long* __restrict__ partials) {
+  __shared__ unsigned long long s_sum[kRowsPerBlock / 32], s_sq[kRowsPerBlock / 32];
+  __shared__ unsigned long long s_min[kRowsPerBlock / 32], s_max[kRowsPerBlock / 32];
+  const int64_t r = row_begin + (int64_t)blockIdx.x * kRowsPerBlock + threadIdx.x;
+  const bool live = r < row_end;
+  const unsigned long long len = live ? (unsigned long long)(indptr[r + 1] - indptr[r]) : 0ull;
+  unsigned long long sum = len, sq = len * len, mn = live ? len : ~0ull, mx = len;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    sq += __shfl_xor_sync(0xffffffffu, sq, o);
+    const unsigned long long a = __shfl_xor_sync(0xffffffffu, mn, o), b = __shfl_xor_sync(0xffffffffu, mx, o);
+    mn = a < mn ? a : mn;
+    mx = b > mx ? b : mx;
+  }
+  const int warp = threadIdx.x >> 5;
+  if ((threadIdx.x & 31) == 0) { s_sum[warp] = sum; s_sq[warp] = sq; s_min[warp] = mn; s_max[warp] = mx; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < kRowsPerBlock / 32; ++w) {
+      sum += s_sum[w]; sq += s_sq[w];
+      mn = s_min[w] < mn ? s_min[w] : mn;
+      mx = s_max[w] > mx ? s_max[w] : mx;
+    }
+    unsigned long long* out = partials + (size_t)blockIdx.x * 4;
+    out[0] = sum; out[1] = sq; out[2] = mn; out[3] = mx;
+  }
+}
+
 // ---- workspace carving ---------------------------------------------------------------------
 struct BuildWs {
   int32_t* pbo; int32_t* widths; int64_t* row_off; int64_t* slot_off; int64_t* ell_rows;
@@ -466,6 +500,21 @@ int lf_hyb_stats_static(const int64_t* indptr, const int32_t* indices, int64_t n
   // same launches as lf_hyb_stats, which clears the part of the scratch it is about to use
   return lf_hyb_stats(indptr, indices, num_rows, num_cols, num_parts, class_stats, colmask_hist, scratch,
                       sizeof(uint32_t) * (size_t)LF_STATIC_STATS_MAX_COLS, stream);
+}
+
+int64_t lf_row_stats_blocks(int64_t row_begin, int64_t row_end) {
+  return row_end > row_begin ? ceil_div64(row_end - row_begin, kRowsPerBlock) : 0;
+}
+
+int lf_row_stats(const int64_t* indptr, int64_t row_begin, int64_t row_end, uint64_t* partials, void* stream) {
+  LF_REQUIRE(indptr && partials && 0 <= row_begin && row_begin <= row_end, "bad arguments");
+  const int64_t blocks = lf_row_stats_blocks(row_begin, row_end);
+  if (blocks == 0) return LF_OK;
+  LF_REQUIRE(blocks < (1ll << 31), "row range too large");
+  row_stats_kernel<<<(unsigned)blocks, kRowsPerBlock, 0, (cudaStream_t)stream>>>(
+      indptr, row_begin, row_end, (unsigned long long*)partials);
+  LF_CUDA_CHECK(cudaGetLastError());
+  return LF_OK;
 }
 
 size_t lf_hyb_build_workspace_bytes(int64_t row_begin, int64_t row_end, int32_t num_parts,

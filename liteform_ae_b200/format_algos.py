@@ -25,7 +25,7 @@ from .format_matrix_market import MTX
 from .timing import profile_ms
 
 __all__ = ["build_hyb_format", "bench_hyb_with_config", "search_bucket_config", "CostModelSettings",
-           "bench_bsrmm", "bench_naive", "build_hyb_format_device", "spmm"]
+           "bench_bsrmm", "bench_naive", "build_hyb_format_device", "spmm", "suggest_num_parts"]
 
 
 class CostModelSettings:
@@ -49,6 +49,31 @@ def search_bucket_config(g: MTX, num_parts: int, cost_model_config: CostModelSet
     stats, hist = _hyb.hyb_stats(csr, int(num_parts))
     return _ws.search_from_stats(stats, hist, int(cost_model_config.feat_size),
                                  int(cost_model_config.num_parts))
+
+
+def suggest_num_parts(g: MTX, feat_size: int, candidates=(1, 2, 4, 8, 16, 32), device="cuda"):
+    """Number of column partitions with the smallest modelled memory traffic.
+
+    NOT a reference-pinned function: the reference takes ``num_parts`` from a RandomForest whose model
+    file is not part of its repository (proc05.spmm.end-to-end.py:82-97, 142-148).  This chooser
+    evaluates the reference's own cost model (format_algos.py:1035-1166) at its best widths for every
+    candidate and sums it over the partitions; candidates that leave a partition with a single
+    nonzero are skipped.  Returns ``(num_parts, {candidate: cost})``."""
+    csr = g.csr_device(device)
+    costs = {}
+    for P in candidates:
+        if P > g.num_dst_nodes():
+            continue
+        stats, hist = _hyb.hyb_stats(csr, int(P))
+        per_part = []
+        try:
+            _ws.search_from_stats(stats, hist, int(feat_size), int(P), cost_out=per_part)
+        except ValueError:
+            continue
+        costs[int(P)] = float(sum(per_part))
+    if not costs:
+        raise ValueError("no candidate number of partitions is usable")
+    return min(costs, key=costs.get), costs
 
 
 def build_hyb_format_device(g: MTX, bucket_widths: Sequence[Sequence[int]], row_range=None,

@@ -136,6 +136,26 @@ class MTX:
             "std_dev_nnz_density_per_row": np.std(nnz_per_row / num_cols),
         }
 
+    def matrix_features_device(self, device="cuda"):
+        """Same dictionary as ``matrix_features`` with the per-row pass done on the device
+        (``lf_row_stats``).  Sums are exact integers, so the means and extrema are identical to the
+        host version and the standard deviations agree to rounding (the reference sums squared
+        deviations in floating point; here the variance is formed from exact integer moments)."""
+        import math
+        from fractions import Fraction
+        from .hyb import row_length_stats
+        num_rows, num_cols = self.coo_mtx.shape
+        n, total, squares, lo, hi = row_length_stats(self.csr_device(device))
+        avg = total / n
+        var = Fraction(n * squares - total * total, n * n)
+        std = math.sqrt(var)
+        return {
+            "name": self.name, "num_rows": num_rows, "num_cols": num_cols, "nnz": self.coo_mtx.nnz,
+            "avg_nnz_per_row": avg, "min_nnz_per_row": lo, "max_nnz_per_row": hi, "std_dev_nnz_per_row": std,
+            "avg_nnz_density_per_row": avg / num_cols, "min_nnz_density_per_row": lo / num_cols,
+            "max_nnz_density_per_row": hi / num_cols, "std_dev_nnz_density_per_row": std / num_cols,
+        }
+
     def __str__(self):
         return str(self.coo_mtx)
 

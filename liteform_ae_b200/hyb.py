@@ -314,3 +314,20 @@ def shard_rows(csr: DeviceCsr, num_shards: int) -> List[int]:
     with torch.cuda.device(out.device):
         check(lib.lf_shard_rows(t_ptr(csr.indptr), csr.shape[0], num_shards, t_ptr(out), _stream_ptr(torch)))
     return [int(x) for x in out.cpu().tolist()]
+
+
+def row_length_stats(csr: DeviceCsr, row_range=None):
+    """``lf_row_stats`` folded on the host: exact ``(count, sum, sum_of_squares, min, max)`` of the row
+    lengths as Python integers."""
+    torch = _torch()
+    lib = _cabi.load()
+    r0, r1 = (0, csr.shape[0]) if row_range is None else row_range
+    nblk = int(lib.lf_row_stats_blocks(r0, r1))
+    if nblk == 0:
+        return 0, 0, 0, 0, 0
+    part = torch.empty(nblk * 4, dtype=torch.int64, device=csr.indptr.device)
+    with torch.cuda.device(part.device):
+        check(lib.lf_row_stats(t_ptr(csr.indptr), r0, r1, t_ptr(part), _stream_ptr(torch)))
+    p = part.cpu().numpy().view(np.uint64).reshape(nblk, 4)
+    return (r1 - r0, sum(int(x) for x in p[:, 0]), sum(int(x) for x in p[:, 1]),
+            int(p[:, 2].min()), int(p[:, 3].max()))

@@ -98,7 +98,8 @@ def _fix_single_row_buckets(pool: Dict[int, _Bucket]) -> None:
         _move(pool, 1, target)
 
 
-def _choose(pool: Dict[int, _Bucket], ncols: _ColumnCounter, feat_size: int, num_parts: int) -> List[int]:
+def _choose(pool: Dict[int, _Bucket], ncols: _ColumnCounter, feat_size: int, num_parts: int,
+            cost_out: list = None) -> List[int]:
     best_cost = _cost(pool, ncols, feat_size, num_parts)
     best = sorted(pool.keys())
     cur = max(pool.keys())
@@ -109,12 +110,15 @@ def _choose(pool: Dict[int, _Bucket], ncols: _ColumnCounter, feat_size: int, num
         if c < best_cost:
             best, best_cost = sorted(pool.keys()), c
         cur, nxt = nxt, nxt // 2
+    if cost_out is not None:
+        cost_out.append(best_cost)
     return best
 
 
 def search_from_stats(class_stats: np.ndarray, colmask_hist: np.ndarray, feat_size: int,
-                      num_parts: int) -> List[List[int]]:
-    """``class_stats``: int64[P, 11, 3] = (num_rows, nnz, #rows); ``colmask_hist``: int64[P, 2048]."""
+                      num_parts: int, cost_out: list = None) -> List[List[int]]:
+    """``class_stats``: int64[P, 11, 3] = (num_rows, nnz, #rows); ``colmask_hist``: int64[P, 2048].
+    ``cost_out`` (a list) receives the winning cost of every non-empty partition."""
     class_stats = np.asarray(class_stats, dtype=np.int64).reshape(num_parts, NUM_CLASSES, 3)
     colmask_hist = np.asarray(colmask_hist, dtype=np.int64).reshape(num_parts, BINS)
     pools: List[Dict[int, _Bucket]] = []
@@ -131,7 +135,7 @@ def search_from_stats(class_stats: np.ndarray, colmask_hist: np.ndarray, feat_si
         _fix_single_row_buckets(pool)
     out: List[List[int]] = []
     for p, pool in enumerate(pools):
-        out.append(_choose(pool, _ColumnCounter(colmask_hist[p]), feat_size, num_parts) if pool else [])
+        out.append(_choose(pool, _ColumnCounter(colmask_hist[p]), feat_size, num_parts, cost_out) if pool else [])
     return out
 
 
