@@ -451,7 +451,9 @@ int lf_spmm_hyb_f32(const lf_hyb* A, const float* B, int64_t ldb, float* C, int6
                     int32_t flags, void* stream) {
   if (int s = check_hyb(A)) return s;
   LF_REQUIRE(N >= 1, "N must be >= 1");
-  LF_REQUIRE(B && C && ldb >= N && ldc >= N && ldb < (1ll << 31), "bad dense operands");
+  LF_REQUIRE(ldb >= N && ldc >= N && ldb < (1ll << 31), "bad leading dimensions");
+  if (A->row_end == A->row_begin) return LF_OK;   // empty shard: nothing to write, C may be NULL
+  LF_REQUIRE(B && C, "bad dense operands");
   LF_REQUIRE(flags == LF_SPMM_OVERWRITE || flags == LF_SPMM_ACCUMULATE, "unknown flags %d", flags);
   const int64_t total_rows = A->row_off[A->num_buckets];
   LF_REQUIRE(total_rows == 0 || (A->rows && A->cols && A->vals), "format device arrays missing");
@@ -587,9 +589,10 @@ int lf_spmm_hyb_f32_host(const lf_hyb* A, const float* B, float* C, int32_t N, i
 int lf_spmm_csr_f32(const int64_t* indptr, const int32_t* indices, const float* data, int64_t row_begin,
                     int64_t row_end, const float* B, int64_t ldb, float* C, int64_t ldc, int32_t N,
                     void* stream) {
-  LF_REQUIRE(indptr && B && C && N >= 1 && ldb >= N && ldc >= N, "bad arguments");
+  LF_REQUIRE(N >= 1 && ldb >= N && ldc >= N, "bad arguments");
   LF_REQUIRE(0 <= row_begin && row_begin <= row_end, "bad row range");
   if (row_begin == row_end) return LF_OK;
+  LF_REQUIRE(indptr && B && C, "null pointer argument");
   cudaStream_t st = (cudaStream_t)stream;
   const FeatCfg cfg = pick_cfg(B, ldb, C, ldc, N);
   const int gpc = kThreads / cfg.G;

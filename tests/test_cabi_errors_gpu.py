@@ -32,6 +32,7 @@ def test_status_codes_and_messages(cuda_device):
     Cout = torch.zeros((512, 32), device=cuda_device)
     s = fmt.c_struct()
     assert lib.lf_spmm_hyb_f32(C.byref(s), B.data_ptr(), 16, Cout.data_ptr(), 32, 32, 0, 0) == _cabi.LF_ERR_INVALID_ARGUMENT
+    assert b"leading" in lib.lf_last_error()
     assert lib.lf_spmm_hyb_f32(C.byref(s), B.data_ptr(), 32, Cout.data_ptr(), 32, 32, 9, 0) == _cabi.LF_ERR_INVALID_ARGUMENT
     assert lib.lf_spmm_hyb_f32(C.byref(s), 0, 32, Cout.data_ptr(), 32, 32, 0, 0) == _cabi.LF_ERR_INVALID_ARGUMENT
     assert lib.lf_spmm_hyb_f32(None, B.data_ptr(), 32, Cout.data_ptr(), 32, 32, 0, 0) == _cabi.LF_ERR_INVALID_ARGUMENT

@@ -139,18 +139,25 @@ def test_row_shards(cuda_device):
     np.testing.assert_allclose(np.concatenate(out), _ref(csr, B), rtol=RTOL, atol=ATOL)
 
 
-def test_host_memory_entry_point(cuda_device):
+@pytest.mark.parametrize("N,pinned", [(32, False), (64, True), (100, True)])
+def test_host_memory_entry_point(cuda_device, N, pinned):
     import torch
-    csr, d, fmt, B, Bd = _setup("zipf_16384_s0", 1, 32, cuda_device)
+    csr, d, fmt, B, Bd = _setup("zipf_16384_s0", 1, N, cuda_device)
     r, c, m, v = fmt.to_nested_numpy(with_values=True)
     ell_rows, row_off, slot_off, rows, cols, vals, zero_rows = hyb.HybFormat.host_layout(
         fmt.bucket_widths, r, c, v, csr.shape[0])
     host_fmt = hyb.HybFormat(csr.shape, (0, csr.shape[0]), fmt.bucket_widths, ell_rows, row_off, slot_off,
                              None, None, None, None, zero_rows)
-    ws = torch.empty(hyb.host_workspace_bytes(host_fmt, 32), dtype=torch.uint8, device=cuda_device)
-    Ch = np.empty((csr.shape[0], 32), dtype=np.float32)
-    hyb.spmm_hyb_host((rows, cols, vals, zero_rows), host_fmt, B, Ch, ws)
-    np.testing.assert_allclose(Ch, _ref(csr, B), rtol=RTOL, atol=ATOL)
+    ws = torch.empty(hyb.host_workspace_bytes(host_fmt, N), dtype=torch.uint8, device=cuda_device)
+    if pinned:
+        Bh = torch.from_numpy(B).pin_memory().numpy()
+        Ch = torch.full((csr.shape[0], N), float("nan")).pin_memory().numpy()
+    else:
+        Bh, Ch = B, np.full((csr.shape[0], N), np.nan, dtype=np.float32)
+    for _ in range(2):
+        hyb.spmm_hyb_host((rows, cols, vals, zero_rows), host_fmt, Bh, Ch, ws)
+        np.testing.assert_allclose(Ch, _ref(csr, B), rtol=RTOL, atol=ATOL)
+        Ch[:] = np.nan
 
 
 def test_full_size_linearity_and_checksum(cuda_device):
