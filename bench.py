@@ -265,6 +265,42 @@ class HybProblem:
     def cpu_matrix(self):
         return self.csr.toscipy()
 
+    def time_gather(self, mode, rank, world, steps, barrier):
+        """Product followed by / fused with the all-gather of C; checks the gathered C on rank 0
+        against a sample of rows computed on the host."""
+        import torch
+        from liteform_ae_b200.sharding import ShardedSpmm
+        torch_, hyb = self.torch, self.hyb
+        sh = ShardedSpmm.__new__(ShardedSpmm)
+        sh.rank, sh.world, sh.fmt = rank, world, self.fmt
+        d_ptr = torch_.from_numpy(self.csr.indptr).to(self.dev)
+        sh.cuts = hyb.shard_rows(hyb.DeviceCsr(d_ptr, None, None, self.csr.shape), world)
+        if mode == "fused":
+            sh.prepare_fused_gather(self.N)
+            run = lambda: sh.spmm_gather_fused(self.B)
+        else:
+            run = lambda: sh.gather(hyb.spmm_hyb(self.fmt, self.B, out=self.C))
+        for _ in range(3):
+            full = run()
+        barrier()
+        ev0, ev1 = torch_.cuda.Event(enable_timing=True), torch_.cuda.Event(enable_timing=True)
+        ev0.record()
+        for _ in range(steps):
+            full = run()
+        ev1.record()
+        barrier()
+        t = torch_.tensor([ev0.elapsed_time(ev1) / steps], dtype=torch_.float64, device=self.dev)
+        if world > 1:
+            import torch.distributed as dist
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        pick = np.unique(np.random.default_rng(5).integers(0, self.M, 4000))
+        sub = self.csr.toscipy()[pick]
+        want = np.asarray(sub @ self.B_host.astype(np.float64))
+        got = full[torch_.from_numpy(pick).to(self.dev)].cpu().numpy()
+        return {"mode": mode, "ms_per_step": float(t.item()), "gflops": 2.0 * self.nnz * self.N / float(t.item()) / 1e6,
+                "gathered_bytes_per_rank": int(self.M * self.N * 4),
+                "max_abs_err_sampled_rows": float(np.abs(got - want).max())}
+
     def per_bucket(self, repeat):
         """Time every bucket on its own (a one-bucket view of the same arenas).  Bytes per bucket:
         compulsory = slots' index+value of real entries, row ids, touched B rows once, C rows once;
@@ -442,6 +478,14 @@ def run_ours(args, rank, local_rank, world):
     except Exception as exc:  # keep the device-resident numbers, say what went wrong
         e2e = {"value": None, "unit": UNIT, "error": repr(exc)}
 
+    # ---- optional: the whole C on every rank (NCCL all-gather after the product, or fused) -----
+    gather = None
+    if args.gather != "none" and world > 1 and isinstance(prob, HybProblem):
+        try:
+            gather = prob.time_gather(args.gather, rank, world, max(3, min(args.steps, 30)), barrier)
+        except Exception as exc:
+            gather = {"mode": args.gather, "error": repr(exc)}
+
     if rank != 0:
         return
     peak, peak_kind = measured_peak_gbs()
@@ -479,6 +523,8 @@ def run_ours(args, rank, local_rank, world):
         "gpu_launches": prob.launches_per_step * args.steps,
     }
     line.update(prob.extra)
+    if gather is not None:
+        line["gather"] = gather
     if args.per_bucket and hasattr(prob, "per_bucket"):
         line["per_bucket"] = prob.per_bucket(20)
     print(json.dumps(line), flush=True)
@@ -514,6 +560,8 @@ def main():
                     help="auto: 8x8 block kernels for the block workload, composed format otherwise")
     ap.add_argument("--dtype", default="f32", choices=["f32", "bf16", "f16"], help="input type of the block path")
     ap.add_argument("--per-bucket", action="store_true", help="also time every ELL bucket on its own")
+    ap.add_argument("--gather", default="none", choices=["none", "nccl", "fused"],
+                    help="multi-GPU only: also time product + full C on every rank (NCCL all-gather or fused epilogue)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-memory end-to-end leg (profiling runs)")
     args = ap.parse_args()

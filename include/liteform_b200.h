@@ -179,6 +179,19 @@ int lf_spmm_hyb_f32(const lf_hyb* A, const float* B /*[dev] K x N*/, int64_t ldb
                     float* C /*[dev] (row_end-row_begin) x N*/, int64_t ldc, int32_t N,
                     int32_t flags, void* stream);
 
+/* The same product fused with the all-gather of C (no counterpart in the reference, which runs on
+ * one device, format_algos.py:548): every output row of this shard is written by the kernel's
+ * epilogue into num_dests FULL-size C matrices at once -- C_full[k] points at row 0 of a
+ * num_rows x N matrix on GPU k of the group, this GPU's own buffer included, reachable from this
+ * GPU through peer mappings (plain peer stores and peer vector atomics over NVLink; no
+ * multicast).  Each rank calls it for its own row shard; after a barrier over the group every
+ * buffer holds the whole product, without a separate collective and without re-reading C.
+ * Always overwrites.  N, ldb, ldc multiples of 4, all operands 16-byte aligned. */
+#define LF_MAX_DESTS 8
+int lf_spmm_hyb_f32_bcast(const lf_hyb* A, const float* B /*[dev] K x N*/, int64_t ldb,
+                          float* const* C_full /*[host] num_dests device pointers*/, int32_t num_dests,
+                          int64_t ldc, int32_t N, void* stream);
+
 /* Same product with every operand in HOST memory: the arrays of build_hyb_format as NumPy holds
  * them after the int32/float32 casts of format_algos.py:568-577, B and C row-major.  The call
  * copies the format and B into `device_workspace`, runs lf_spmm_hyb_f32 and copies C back, all on

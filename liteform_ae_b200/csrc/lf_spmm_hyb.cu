@@ -42,6 +42,14 @@ struct SpmmTable {
   BucketDesc b[MAXB];
 };
 
+// Destinations of a broadcasting launch: full-size C matrices (row 0 first), one per GPU of the
+// group, addressed through peer mappings; the shard's rows are written into every one of them.
+struct DestList {
+  float* p[LF_MAX_DESTS];
+  int32_t n;
+  int32_t pad_;
+};
+
 __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
@@ -96,13 +104,13 @@ template <> struct Chunk<1> {
 //        (evict-first) accesses; 2 = as 1, and B rows are loaded with an L2 evict-last policy.
 // The group stages G (column, value) pairs and row ids in shared memory with one coalesced load
 // each, then broadcasts a pair per gather with a single 64-bit shared load.
-template <int G, int V, int VEC, int WC, int POL>
+template <int G, int V, int VEC, int WC, int POL, bool MD>
 __device__ __forceinline__ void walk_slots(const int32_t* __restrict__ rows, const int32_t* __restrict__ cols,
                                            const float* __restrict__ vals, int wlog, int64_t e0, int64_t e1,
                                            int64_t ell_rows, bool all_open, const float* __restrict__ B,
                                            int ldb, float* __restrict__ C, int64_t ldc, int N,
                                            int64_t row_base, int lane, unsigned gmask, int2* cv, int* rd,
-                                           const uint32_t* __restrict__ hot) {
+                                           const uint32_t* __restrict__ hot, const DestList& dl) {
   constexpr int U = V == 1 ? 8 : (V == 2 ? 4 : 2);  // gathers in flight per lane (x V chunks)
   static_assert(G % U == 0 && 8 % U == 0, "unroll must divide the group size and the batch");
   const int first_row = rows[e0], last_row = rows[e1 - 1];
@@ -127,7 +135,22 @@ __device__ __forceinline__ void walk_slots(const int32_t* __restrict__ rows, con
 
   auto flush = [&](int row) {
     const bool open = all_open || (row == first_row && head_open) || (row == last_row && tail_open);
-    float* dst = C + (int64_t)(row - row_base) * ldc + f0;
+    const int64_t off = (int64_t)(row - row_base) * ldc + f0;
+    if (MD) {   // the same row goes to every destination (peer stores / peer atomics over NVLink)
+      for (int k = 0; k < dl.n; ++k) {
+        float* dst = dl.p[k] + off;
+#pragma unroll
+        for (int v = 0; v < V; ++v) {
+          if (active[v]) {
+            if (open) acc[v].red(dst + v * G * VEC); else acc[v].store(dst + v * G * VEC);
+          }
+        }
+      }
+#pragma unroll
+      for (int v = 0; v < V; ++v) acc[v].zero();
+      return;
+    }
+    float* dst = C + off;
 #pragma unroll
     for (int v = 0; v < V; ++v) {
       if (active[v]) {
@@ -192,12 +215,12 @@ __device__ __forceinline__ void walk_slots(const int32_t* __restrict__ rows, con
 
 // All buckets of all partitions in one launch: a thread block looks up its bucket in the table
 // passed as kernel parameter and each of its groups takes a contiguous run of that bucket's ELL rows.
-template <int G, int V, int VEC, int MAXB, int POL, int MINB>
+template <int G, int V, int VEC, int MAXB, int POL, int MINB, bool MD>
 __global__ void __launch_bounds__(kThreads, MINB)
 spmm_hyb_kernel(const __grid_constant__ SpmmTable<MAXB> tbl, const int32_t* __restrict__ rows_arena,
                 const int32_t* __restrict__ cols_arena, const float* __restrict__ vals_arena,
                 const float* __restrict__ B, int ldb, float* __restrict__ C, int64_t ldc, int N,
-                int64_t row_base, const uint32_t* __restrict__ hot_arena) {
+                int64_t row_base, const uint32_t* __restrict__ hot_arena, const __grid_constant__ DestList dests) {
   constexpr int GPC = kThreads / G;  // groups per thread block
   __shared__ int2 s_cv[kThreads];
   __shared__ int s_rd[kThreads];
@@ -223,8 +246,8 @@ spmm_hyb_kernel(const __grid_constant__ SpmmTable<MAXB> tbl, const int32_t* __re
   int* rd = s_rd + g * G;
   const uint32_t* hot = hot_arena ? hot_arena + (d.slot_off >> 5) : nullptr;
 #define LF_WALK(WC_)                                                                                     \
-  walk_slots<G, V, VEC, WC_, POL>(rows, cols, vals, wlog, e0, e1, d.ell_rows, all_open, B, ldb, C, ldc, \
-                                  N, row_base, lane, gmask, cv, rd, hot)
+  walk_slots<G, V, VEC, WC_, POL, MD>(rows, cols, vals, wlog, e0, e1, d.ell_rows, all_open, B, ldb, C, ldc, \
+                                  N, row_base, lane, gmask, cv, rd, hot, dests)
   switch (wlog) {
     case 0: LF_WALK(1); break;
     case 1: LF_WALK(2); break;
@@ -249,6 +272,21 @@ zero_rows_kernel(const int32_t* __restrict__ zero_rows, int64_t n, float* __rest
     } else {
       for (int f = lane; f < N; f += 32) dst[f] = 0.f;
     }
+  }
+}
+
+// Same for a broadcasting launch: the rows are cleared in every destination.
+__global__ void __launch_bounds__(kThreads)
+zero_rows_multi_kernel(const int32_t* __restrict__ zero_rows, int64_t n, const __grid_constant__ DestList dests,
+                       int64_t ldc, int N) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (int64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
+  const int64_t n_warps = (int64_t)gridDim.x * (kThreads / 32);
+  for (int64_t i = warp; i < n; i += n_warps) {
+    const int64_t off = (int64_t)zero_rows[i] * ldc;
+    for (int k = 0; k < dests.n; ++k)
+      for (int f = lane * 4; f < N; f += 128)
+        *reinterpret_cast<float4*>(dests.p[k] + off + f) = make_float4(0.f, 0.f, 0.f, 0.f);
   }
 }
 
@@ -371,13 +409,14 @@ int cache_policy() {
   return g_cache_policy;
 }
 
-template <int MAXB, int POL, int MINB>
+template <int MAXB, int POL, int MINB, bool MD>
 int launch_hyb_pol(const SpmmTable<MAXB>& tbl, int64_t tiles, const lf_hyb* A, const float* B, int64_t ldb,
-                   float* C, int64_t ldc, int N, FeatCfg cfg, cudaStream_t st) {
+                   float* C, int64_t ldc, int N, FeatCfg cfg, cudaStream_t st, const DestList& dests) {
+  const int64_t row_base = MD ? 0 : A->row_begin;
   dim3 grid((unsigned)tiles, (unsigned)((N + cfg.pass - 1) / cfg.pass));
 #define LF_LAUNCH(G_, V_, VEC_)                                                                          \
-  spmm_hyb_kernel<G_, V_, VEC_, MAXB, POL, MINB><<<grid, kThreads, 0, st>>>(tbl, A->rows, A->cols, A->vals, \
-                                                                           B, (int)ldb, C, ldc, N, A->row_begin, A->hot_bits)
+  spmm_hyb_kernel<G_, V_, VEC_, MAXB, POL, MINB, MD><<<grid, kThreads, 0, st>>>(                              \
+      tbl, A->rows, A->cols, A->vals, B, (int)ldb, C, ldc, N, row_base, A->hot_bits, dests)
   if (cfg.VEC == 4) {
     if (cfg.G == 8) LF_LAUNCH(8, 1, 4);
     else if (cfg.G == 16) LF_LAUNCH(16, 1, 4);
@@ -396,9 +435,11 @@ int launch_hyb_pol(const SpmmTable<MAXB>& tbl, int64_t tiles, const lf_hyb* A, c
 
 template <int MAXB>
 int launch_hyb(const SpmmTable<MAXB>& tbl, int64_t tiles, const lf_hyb* A, const float* B, int64_t ldb,
-               float* C, int64_t ldc, int N, FeatCfg cfg, cudaStream_t st) {
+               float* C, int64_t ldc, int N, FeatCfg cfg, cudaStream_t st, const DestList& dests) {
+  if (dests.n > 0)   // broadcasting launch: one compiled variant
+    return launch_hyb_pol<MAXB, 1, 3, true>(tbl, tiles, A, B, ldb, C, ldc, N, cfg, st, dests);
   const int pol = cache_policy(), minb = min_blocks();
-#define LF_CASE(P_, M_) if (pol == P_ && minb == M_) return launch_hyb_pol<MAXB, P_, M_>(tbl, tiles, A, B, ldb, C, ldc, N, cfg, st)
+#define LF_CASE(P_, M_) if (pol == P_ && minb == M_) return launch_hyb_pol<MAXB, P_, M_, false>(tbl, tiles, A, B, ldb, C, ldc, N, cfg, st, dests)
   LF_CASE(0, 2); LF_CASE(0, 3); LF_CASE(0, 4);
   LF_CASE(1, 2); LF_CASE(1, 3); LF_CASE(1, 4);
   LF_CASE(2, 2); LF_CASE(2, 3); LF_CASE(2, 4);
@@ -447,8 +488,33 @@ int lf_set_option(int32_t option, int32_t value) {
   }
 }
 
+static int spmm_hyb_impl(const lf_hyb* A, const float* B, int64_t ldb, float* C, int64_t ldc, int32_t N,
+                         int32_t flags, void* stream, const DestList& dests);
+
 int lf_spmm_hyb_f32(const lf_hyb* A, const float* B, int64_t ldb, float* C, int64_t ldc, int32_t N,
                     int32_t flags, void* stream) {
+  DestList none;
+  none.n = 0;
+  none.pad_ = 0;
+  return spmm_hyb_impl(A, B, ldb, C, ldc, N, flags, stream, none);
+}
+
+int lf_spmm_hyb_f32_bcast(const lf_hyb* A, const float* B, int64_t ldb, float* const* C_full, int32_t num_dests,
+                          int64_t ldc, int32_t N, void* stream) {
+  LF_REQUIRE(C_full && num_dests >= 1 && num_dests <= LF_MAX_DESTS, "1..%d destinations are supported", LF_MAX_DESTS);
+  DestList d;
+  d.n = num_dests;
+  d.pad_ = 0;
+  for (int k = 0; k < LF_MAX_DESTS; ++k) d.p[k] = k < num_dests ? C_full[k] : nullptr;
+  for (int k = 0; k < num_dests; ++k)
+    LF_REQUIRE(d.p[k] && (uintptr_t)d.p[k] % 16 == 0, "destination %d is null or not 16-byte aligned", k);
+  LF_REQUIRE(N % 4 == 0 && ldc % 4 == 0 && ldb % 4 == 0 && (uintptr_t)B % 16 == 0,
+             "the broadcasting SpMM needs N, ldb, ldc multiples of 4 and 16-byte aligned operands");
+  return spmm_hyb_impl(A, B, ldb, d.p[0], ldc, N, LF_SPMM_OVERWRITE, stream, d);
+}
+
+static int spmm_hyb_impl(const lf_hyb* A, const float* B, int64_t ldb, float* C, int64_t ldc, int32_t N,
+                         int32_t flags, void* stream, const DestList& dests) {
   if (int s = check_hyb(A)) return s;
   LF_REQUIRE(N >= 1, "N must be >= 1");
   LF_REQUIRE(ldb >= N && ldc >= N && ldb < (1ll << 31), "bad leading dimensions");
@@ -464,7 +530,19 @@ int lf_spmm_hyb_f32(const lf_hyb* A, const float* B, int64_t ldb, float* C, int6
   const bool accumulate = flags == LF_SPMM_ACCUMULATE;
   const bool all_atomic = accumulate || A->num_parts > 1;
 
-  if (!accumulate) {
+  if (dests.n > 0) {
+    if (A->num_parts > 1) {
+      for (int k = 0; k < dests.n; ++k)
+        LF_CUDA_CHECK(cudaMemset2DAsync(dests.p[k] + A->row_begin * ldc, sizeof(float) * ldc, 0, sizeof(float) * N,
+                                        shard_rows, st));
+    } else if (A->num_zero_rows > 0) {
+      LF_REQUIRE(A->zero_rows, "zero_rows missing");
+      const int64_t want = ceil_div64(A->num_zero_rows, kThreads / 32);
+      const int grid = (int)(want > 148 * 16 ? 148 * 16 : want);
+      zero_rows_multi_kernel<<<grid, kThreads, 0, st>>>(A->zero_rows, A->num_zero_rows, dests, ldc, N);
+      LF_CUDA_CHECK(cudaGetLastError());
+    }
+  } else if (!accumulate) {
     if (A->num_parts > 1) {
       LF_CUDA_CHECK(cudaMemset2DAsync(C, sizeof(float) * ldc, 0, sizeof(float) * N, shard_rows, st));
     } else if (A->num_zero_rows > 0) {
@@ -523,10 +601,10 @@ int lf_spmm_hyb_f32(const lf_hyb* A, const float* B, int64_t ldb, float* C, int6
     int s;
     if (n <= 16) {
       small.n = n; small.pad_ = 0;
-      s = launch_hyb<16>(small, tiles, A, B, ldb, C, ldc, N, cfg, st);
+      s = launch_hyb<16>(small, tiles, A, B, ldb, C, ldc, N, cfg, st, dests);
     } else {
       big.n = n; big.pad_ = 0;
-      s = launch_hyb<LF_MAX_BUCKETS_PER_LAUNCH>(big, tiles, A, B, ldb, C, ldc, N, cfg, st);
+      s = launch_hyb<LF_MAX_BUCKETS_PER_LAUNCH>(big, tiles, A, B, ldb, C, ldc, N, cfg, st, dests);
     }
     if (s) return s;
   }

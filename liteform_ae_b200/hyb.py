@@ -331,3 +331,16 @@ def row_length_stats(csr: DeviceCsr, row_range=None):
     p = part.cpu().numpy().view(np.uint64).reshape(nblk, 4)
     return (r1 - r0, sum(int(x) for x in p[:, 0]), sum(int(x) for x in p[:, 1]),
             int(p[:, 2].min()), int(p[:, 3].max()))
+
+
+def spmm_hyb_bcast(fmt: HybFormat, B, dest_ptrs: Sequence[int], ldc: int):
+    """``lf_spmm_hyb_f32_bcast``: write this shard's rows of C = A @ B into every full-size C whose
+    device address is listed in ``dest_ptrs`` (own buffer and peers' symmetric-memory buffers)."""
+    torch = _torch()
+    lib = _cabi.load()
+    assert B.is_cuda and B.dtype == torch.float32 and B.stride(1) == 1 and B.shape[0] == fmt.shape[1]
+    arr = (C.c_void_p * len(dest_ptrs))(*[int(p) for p in dest_ptrs])
+    with torch.cuda.device(B.device):
+        s = fmt.c_struct()
+        check(lib.lf_spmm_hyb_f32_bcast(C.byref(s), B.data_ptr(), B.stride(0), arr, len(dest_ptrs), int(ldc),
+                                        int(B.shape[1]), _stream_ptr(torch)))

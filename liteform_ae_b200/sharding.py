@@ -72,3 +72,28 @@ class ShardedSpmm:
 
     def gather(self, C_local, group=None):
         return all_gather_rows(C_local, self.cuts, group)
+
+    # ---- fused product + all-gather -----------------------------------------------------------
+    def prepare_fused_gather(self, N: int, group=None):
+        """Allocate the full-size C in symmetric memory (``torch.distributed._symmetric_memory``) and
+        exchange the peers' buffer addresses.  Collective: every rank of the group must call it."""
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+        group = dist.group.WORLD if group is None else group
+        dev = self.fmt.device
+        self.C_full = symm.empty((self.fmt.shape[0], int(N)), dtype=torch.float32, device=dev)
+        self._symm = symm.rendezvous(self.C_full, group)
+        self._dest_ptrs = [int(p) for p in self._symm.buffer_ptrs]
+        assert len(self._dest_ptrs) == self.world
+        return self.C_full
+
+    def spmm_gather_fused(self, B):
+        """C = A @ B with the whole product on every rank: the kernel's epilogue stores each row of
+        this rank's shard into every rank's full-size C (peer stores over NVLink).  Barriers on the
+        symmetric-memory handle order it against the previous readers and the next ones."""
+        from . import hyb
+        self._symm.barrier()                      # nobody still reads the previous product
+        hyb.spmm_hyb_bcast(self.fmt, B, self._dest_ptrs, self.C_full.stride(0))
+        self._symm.barrier()                      # every rank's rows have landed everywhere
+        return self.C_full
