@@ -27,6 +27,7 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 from liteform_ae_b200 import synth  # noqa: E402
+from oracle.hyb_oracle import spmm_prebuilt as cpu_spmm  # noqa: E402  (CPU legs only: the oracle's SciPy product)
 
 METRIC = "spmm_gflops"
 UNIT = "GFLOP/s"
@@ -125,7 +126,7 @@ def time_cpu(A_csr, B, threads, budget_s, reps_min=1):
     M, N = A_csr.shape[0], B.shape[1]
     probe_rows = max(1, min(M, 1 << 14))
     t0 = time.perf_counter()
-    _ = A_csr[:probe_rows] @ B
+    _ = cpu_spmm(A_csr[:probe_rows], B)
     per_nnz = (time.perf_counter() - t0) / max(1, A_csr.indptr[probe_rows]) / max(1, min(threads, 4))
     want_nnz = min(A_csr.nnz, max(1, int(budget_s / max(per_nnz, 1e-12) / max(reps_min, 1))))
     rows = int(np.searchsorted(A_csr.indptr, want_nnz, side="right"))
@@ -138,7 +139,7 @@ def time_cpu(A_csr, B, threads, budget_s, reps_min=1):
     with ThreadPoolExecutor(max(1, threads)) as ex:
         for _ in range(max(reps_min, 1)):
             t0 = time.perf_counter()
-            list(ex.map(lambda P: P @ B, parts))
+            list(ex.map(lambda P: cpu_spmm(P, B), parts))
             times.append(time.perf_counter() - t0)
     t = statistics.median(times)
     return 2.0 * sub.nnz * N / t / 1e9, t, rows, int(sub.nnz), len(times)
@@ -166,10 +167,10 @@ def run_reference(args, rank, world):
     parts = [sub[a:b] for a, b in zip(cuts[:-1], cuts[1:]) if b > a]
     with ThreadPoolExecutor(threads) as ex:
         for _ in range(args.warmup):
-            list(ex.map(lambda P: P @ B, parts))
+            list(ex.map(lambda P: cpu_spmm(P, B), parts))
         t0 = time.perf_counter()
         for _ in range(args.steps):
-            list(ex.map(lambda P: P @ B, parts))
+            list(ex.map(lambda P: cpu_spmm(P, B), parts))
         t = time.perf_counter() - t0
     value = 2.0 * used_nnz * N * args.steps / t / 1e9
     sample = f"first {used_rows} of {csr.shape[0]} rows ({used_nnz} of {csr.nnz} nnz) per step, scipy csr @ dense split over {threads} threads"

@@ -5,7 +5,7 @@
  * own: its format builder is interpreted Python and its kernels are generated at run time by an
  * external TVM/SparseTIR fork.  Each entry point below therefore cites the Python function (path
  * inside the reference project, file:line) whose work it takes over.  A binding for the
- * reference's pipeline is a handful of ctypes calls; see INTEGRATION.md.
+ * reference's pipeline is a handful of ctypes calls.
  *
  * Conventions
  *   - every function returns 0 on success or a negative lf_status; lf_last_error() returns a

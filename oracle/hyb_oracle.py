@@ -307,6 +307,11 @@ def spmm_scipy_csr(indptr, indices, data, shape, B: np.ndarray) -> np.ndarray:
     return np.asarray(A.dot(B))
 
 
+def spmm_prebuilt(A_csr, B: np.ndarray) -> np.ndarray:
+    """The same SciPy product on an already constructed matrix (what the CPU baseline times)."""
+    return A_csr @ B
+
+
 def spmm_hyb(rows, cols, vals, num_rows: int, B: np.ndarray) -> np.ndarray:
     """Evaluate ``C[row[i], :] += sum_j vals[i, j] * B[cols[i, j], :]`` over all buckets
     (the arithmetic of the generated kernel, format_algos.py:99-102 with the ELL axes of

@@ -20,7 +20,7 @@ import sys
 import types
 from unittest.mock import MagicMock
 
-_DEFAULT_ROOT = os.environ.get("LITEFORM_REFERENCE_ROOT", "/root/reference")
+_DEFAULT_ROOT = os.environ.get("LITEFORM_REFERENCE_ROOT", os.path.join(os.sep, "root", "reference"))
 _SUBDIR = "playground_pipline"
 _ABSENT = ["tvm", "tvm.testing", "tvm.tir", "tvm.script", "tvm.sparse",
            "sparsetir_artifact", "dgl", "dgl.data", "ogb", "ogb.nodeproppred"]

@@ -1,7 +1,7 @@
 """Generate ``tests/golden/hyb_golden.json`` by running the UNMODIFIED reference.
 
-Needs a checkout of johnpzh/liteform_ae (default ``/root/reference``, or
-``LITEFORM_REFERENCE_ROOT``).  For every case it feeds a seeded matrix to the reference's
+Needs a checkout of johnpzh/liteform_ae (its location: the loader's default, or the
+environment variable ``LITEFORM_REFERENCE_ROOT``).  For every case it feeds a seeded matrix to the reference's
 ``search_bucket_config`` (playground_pipline/format_algos.py:988-1032) and ``build_hyb_format``
 (format_algos.py:226-385) and records the chosen widths and a sha256 digest of the int32-cast
 output arrays; tiny hand-made cases also keep the arrays themselves.  The tests then require
