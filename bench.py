@@ -221,9 +221,16 @@ class HybProblem:
         self.t_build = time.perf_counter() - t0
         del d_csr
         self.B = torch.from_numpy(self.B_host).to(dev)
+        self.eb = 4
+        self.dtype = "f32"
+        if args.dtype == "bf16":       # B in bf16, values / accumulation / C in float32
+            self.B = self.B.to(torch.bfloat16)
+            self.eb = 2
+            self.dtype = "bf16"
+        elif args.dtype != "f32":
+            raise SystemExit("the composed-format path takes --dtype f32 or bf16")
         self.C = torch.empty((self.r1 - self.r0, N), dtype=torch.float32, device=dev)
         self.launches_per_step = 1 + (1 if (P == 1 and self.fmt.num_zero_rows > 0) else 0) + (1 if P > 1 else 0)
-        self.dtype = "f32"
         self.config = {"workload": f"{args.workload}: {desc}", "format": "hyb (composed ELL)", "rows": self.M,
                        "cols": self.K, "nnz": self.nnz, "N": N, "num_parts": P, "bucket_widths": self.widths,
                        "sharding": f"rows, nnz-balanced, {world} rank(s), B replicated, C left sharded",
@@ -239,10 +246,16 @@ class HybProblem:
         csr, r0, r1 = self.csr, self.r0, self.r1
         my_nnz = int(csr.indptr[r1] - csr.indptr[r0])
         touched = int(np.unique(csr.indices[csr.indptr[r0]:csr.indptr[r1]]).size)
-        return compulsory_bytes(my_nnz, r1 - r0, touched, self.N), gather_bytes(my_nnz, r1 - r0, self.N)
+        comp, gath = compulsory_bytes(my_nnz, r1 - r0, touched, self.N), gather_bytes(my_nnz, r1 - r0, self.N)
+        if self.eb == 2:               # B rows are half as wide
+            comp -= touched * self.N * 2
+            gath -= my_nnz * self.N * 2
+        return comp, gath
 
     def prepare_e2e(self):
         torch, hyb, fmt = self.torch, self.hyb, self.fmt
+        if self.eb != 4:
+            raise RuntimeError("the host-memory entry point is float32 only")
         r_nd, c_nd, _, v_nd = fmt.to_nested_numpy(with_values=True)
         ell_rows, row_off, slot_off, h_rows, h_cols, h_vals, h_zero = hyb.HybFormat.host_layout(
             fmt.bucket_widths, r_nd, c_nd, v_nd, self.M, (self.r0, self.r1))

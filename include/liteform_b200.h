@@ -179,6 +179,13 @@ int lf_spmm_hyb_f32(const lf_hyb* A, const float* B /*[dev] K x N*/, int64_t ldb
                     float* C /*[dev] (row_end-row_begin) x N*/, int64_t ldc, int32_t N,
                     int32_t flags, void* stream);
 
+/* The same product with B in bf16 (raw 16-bit patterns), values and accumulation in float32, C in
+ * float32: halves the bytes of every gather.  N and ldb multiples of 8, ldc of 4, B and C 16-byte
+ * aligned (LF_ERR_UNSUPPORTED otherwise).  Matches the float64 product of the rounded B to 1e-5 and
+ * the unrounded one to 1e-2 relative. */
+int lf_spmm_hyb_bf16(const lf_hyb* A, const uint16_t* B /*[dev] K x N bf16*/, int64_t ldb,
+                     float* C /*[dev]*/, int64_t ldc, int32_t N, int32_t flags, void* stream);
+
 /* The same product fused with the all-gather of C (no counterpart in the reference, which runs on
  * one device, format_algos.py:548): every output row of this shard is written by the kernel's
  * epilogue into num_dests FULL-size C matrices at once -- C_full[k] points at row 0 of a

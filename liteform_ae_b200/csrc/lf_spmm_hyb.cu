@@ -96,6 +96,51 @@ template <> struct Chunk<1> {
   __device__ __forceinline__ void red(float* p) const { atomicAdd(p, v); }
 };
 
+// VEC = 8 stands for "B holds bf16": a lane gathers 8 consecutive 16-bit features with one
+// 128-bit load and accumulates them in 8 floats (fp32 accumulation, fp32 C).
+template <> struct Chunk<8> {
+  float a[8];
+  __device__ __forceinline__ void zero() {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) a[i] = 0.f;
+  }
+  __device__ __forceinline__ void store(float* p) const {
+    *reinterpret_cast<float4*>(p) = make_float4(a[0], a[1], a[2], a[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(a[4], a[5], a[6], a[7]);
+  }
+  __device__ __forceinline__ void store_stream(float* p) const {
+    __stcs(reinterpret_cast<float4*>(p), make_float4(a[0], a[1], a[2], a[3]));
+    __stcs(reinterpret_cast<float4*>(p + 4), make_float4(a[4], a[5], a[6], a[7]));
+  }
+  __device__ __forceinline__ void red(float* p) const {
+    red_add_v4(p, a[0], a[1], a[2], a[3]);
+    red_add_v4(p + 4, a[4], a[5], a[6], a[7]);
+  }
+};
+struct RawBf16x8 {
+  uint4 v;
+  __device__ __forceinline__ void zero() { v = make_uint4(0u, 0u, 0u, 0u); }
+  __device__ __forceinline__ void load(const uint16_t* p) { v = __ldg(reinterpret_cast<const uint4*>(p)); }
+  __device__ __forceinline__ void load_keep(const uint16_t* p, uint64_t pol) {
+    asm volatile("ld.global.nc.L2::cache_hint.v4.u32 {%0, %1, %2, %3}, [%4], %5;"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p), "l"(pol));
+  }
+};
+// element type of B and the register image of one gathered chunk, per VEC
+template <int VEC> struct BTraits { using elem = float; using raw = Chunk<VEC>; };
+template <> struct BTraits<8> { using elem = uint16_t; using raw = RawBf16x8; };
+
+__device__ __forceinline__ void chunk_fma(Chunk<4>& acc, float a, const Chunk<4>& x) { acc.fma(a, x); }
+__device__ __forceinline__ void chunk_fma(Chunk<1>& acc, float a, const Chunk<1>& x) { acc.fma(a, x); }
+__device__ __forceinline__ void chunk_fma(Chunk<8>& acc, float a, const RawBf16x8& x) {
+  const uint32_t w[4] = {x.v.x, x.v.y, x.v.z, x.v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {   // a bf16 is the upper half of the float with the same value
+    acc.a[2 * i] = fmaf(a, __uint_as_float(w[i] << 16), acc.a[2 * i]);
+    acc.a[2 * i + 1] = fmaf(a, __uint_as_float(w[i] & 0xffff0000u), acc.a[2 * i + 1]);
+  }
+}
+
 // One thread group walks the slots [s0, s1) of whole ELL rows of one bucket.
 //   G lanes per group, V chunks of VEC floats per lane: one pass covers G*V*VEC features.
 //   WC = min(bucket width, 8): ELL rows start every WC slots at the earliest, so the row id has to
@@ -107,8 +152,8 @@ template <> struct Chunk<1> {
 template <int G, int V, int VEC, int WC, int POL, bool MD>
 __device__ __forceinline__ void walk_slots(const int32_t* __restrict__ rows, const int32_t* __restrict__ cols,
                                            const float* __restrict__ vals, int wlog, int64_t e0, int64_t e1,
-                                           int64_t ell_rows, bool all_open, const float* __restrict__ B,
-                                           int ldb, float* __restrict__ C, int64_t ldc, int N,
+                                           int64_t ell_rows, bool all_open,
+                                           const typename BTraits<VEC>::elem* __restrict__ B, int ldb, float* __restrict__ C, int64_t ldc, int N,
                                            int64_t row_base, int lane, unsigned gmask, int2* cv, int* rd,
                                            const uint32_t* __restrict__ hot, const DestList& dl) {
   constexpr int U = V == 1 ? 8 : (V == 2 ? 4 : 2);  // gathers in flight per lane (x V chunks)
@@ -162,7 +207,7 @@ __device__ __forceinline__ void walk_slots(const int32_t* __restrict__ rows, con
     }
   };
 
-  const float* __restrict__ Bf = B + f0;
+  const typename BTraits<VEC>::elem* __restrict__ Bf = B + f0;
   const int64_t s0 = e0 << wlog, s1 = e1 << wlog;
   for (int64_t s = s0; s < s1; s += G) {
     const int64_t idx = s + lane;
@@ -180,12 +225,12 @@ __device__ __forceinline__ void walk_slots(const int32_t* __restrict__ rows, con
     const int nstrip = (int)min((int64_t)G, s1 - s);
     for (int t = 0; t < nstrip; t += U) {
       float val[U];
-      Chunk<VEC> b[U][V];
+      typename BTraits<VEC>::raw b[U][V];
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         const int2 p = cv[t + u];
         val[u] = __int_as_float(p.y);
-        const float* src = Bf + (int64_t)p.x * ldb;
+        const typename BTraits<VEC>::elem* src = Bf + (int64_t)p.x * ldb;
 #pragma unroll
         for (int v = 0; v < V; ++v) {
           if (val[u] != 0.f && active[v]) {
@@ -206,7 +251,7 @@ __device__ __forceinline__ void walk_slots(const int32_t* __restrict__ rows, con
           }
         }
 #pragma unroll
-        for (int v = 0; v < V; ++v) acc[v].fma(val[u], b[u][v]);
+        for (int v = 0; v < V; ++v) chunk_fma(acc[v], val[u], b[u][v]);
       }
     }
   }
@@ -219,8 +264,9 @@ template <int G, int V, int VEC, int MAXB, int POL, int MINB, bool MD>
 __global__ void __launch_bounds__(kThreads, MINB)
 spmm_hyb_kernel(const __grid_constant__ SpmmTable<MAXB> tbl, const int32_t* __restrict__ rows_arena,
                 const int32_t* __restrict__ cols_arena, const float* __restrict__ vals_arena,
-                const float* __restrict__ B, int ldb, float* __restrict__ C, int64_t ldc, int N,
-                int64_t row_base, const uint32_t* __restrict__ hot_arena, const __grid_constant__ DestList dests) {
+                const typename BTraits<VEC>::elem* __restrict__ B, int ldb, float* __restrict__ C, int64_t ldc,
+                int N, int64_t row_base, const uint32_t* __restrict__ hot_arena,
+                const __grid_constant__ DestList dests) {
   constexpr int GPC = kThreads / G;  // groups per thread block
   __shared__ int2 s_cv[kThreads];
   __shared__ int s_rd[kThreads];
@@ -361,6 +407,18 @@ FeatCfg pick_cfg(const void* B, int64_t ldb, const void* C, int64_t ldc, int N) 
   return c;
 }
 
+// bf16 B: 8 features per lane and chunk; needs N, ldb multiples of 8 and 16-byte aligned bases
+FeatCfg pick_cfg_bf16(int N) {
+  FeatCfg c;
+  c.VEC = 8;
+  if (N <= 64) { c.G = 8; c.V = 1; }
+  else if (N <= 128) { c.G = 16; c.V = 1; }
+  else if (N <= 256) { c.G = 32; c.V = 1; }
+  else { c.G = 32; c.V = 2; }
+  c.pass = c.G * c.V * c.VEC;
+  return c;
+}
+
 // Process-wide tuning knobs (lf_set_option); the environment gives the initial values.
 int g_slots_per_group = 0;
 int g_cache_policy = -1;
@@ -409,6 +467,22 @@ int cache_policy() {
   return g_cache_policy;
 }
 
+template <int MAXB>
+int launch_hyb_bf16(const SpmmTable<MAXB>& tbl, int64_t tiles, const lf_hyb* A, const uint16_t* B, int64_t ldb,
+                    float* C, int64_t ldc, int N, FeatCfg cfg, cudaStream_t st, const DestList& dests) {
+  dim3 grid((unsigned)tiles, (unsigned)((N + cfg.pass - 1) / cfg.pass));
+#define LF_LAUNCH(G_, V_)                                                                        \
+  spmm_hyb_kernel<G_, V_, 8, MAXB, 1, 3, false><<<grid, kThreads, 0, st>>>(                      \
+      tbl, A->rows, A->cols, A->vals, B, (int)ldb, C, ldc, N, A->row_begin, A->hot_bits, dests)
+  if (cfg.G == 8) LF_LAUNCH(8, 1);
+  else if (cfg.G == 16) LF_LAUNCH(16, 1);
+  else if (cfg.V == 1) LF_LAUNCH(32, 1);
+  else LF_LAUNCH(32, 2);
+#undef LF_LAUNCH
+  LF_CUDA_CHECK(cudaGetLastError());
+  return LF_OK;
+}
+
 template <int MAXB, int POL, int MINB, bool MD>
 int launch_hyb_pol(const SpmmTable<MAXB>& tbl, int64_t tiles, const lf_hyb* A, const float* B, int64_t ldb,
                    float* C, int64_t ldc, int N, FeatCfg cfg, cudaStream_t st, const DestList& dests) {
@@ -434,8 +508,11 @@ int launch_hyb_pol(const SpmmTable<MAXB>& tbl, int64_t tiles, const lf_hyb* A, c
 }
 
 template <int MAXB>
-int launch_hyb(const SpmmTable<MAXB>& tbl, int64_t tiles, const lf_hyb* A, const float* B, int64_t ldb,
+int launch_hyb(const SpmmTable<MAXB>& tbl, int64_t tiles, const lf_hyb* A, const void* Bv, int64_t ldb,
                float* C, int64_t ldc, int N, FeatCfg cfg, cudaStream_t st, const DestList& dests) {
+  if (cfg.VEC == 8)   // bf16 B: one compiled variant per feature layout
+    return launch_hyb_bf16<MAXB>(tbl, tiles, A, (const uint16_t*)Bv, ldb, C, ldc, N, cfg, st, dests);
+  const float* B = (const float*)Bv;
   if (dests.n > 0)   // broadcasting launch: one compiled variant
     return launch_hyb_pol<MAXB, 1, 3, true>(tbl, tiles, A, B, ldb, C, ldc, N, cfg, st, dests);
   const int pol = cache_policy(), minb = min_blocks();
@@ -488,15 +565,25 @@ int lf_set_option(int32_t option, int32_t value) {
   }
 }
 
-static int spmm_hyb_impl(const lf_hyb* A, const float* B, int64_t ldb, float* C, int64_t ldc, int32_t N,
-                         int32_t flags, void* stream, const DestList& dests);
+static int spmm_hyb_impl(const lf_hyb* A, const void* B, bool b_is_bf16, int64_t ldb, float* C, int64_t ldc,
+                         int32_t N, int32_t flags, void* stream, const DestList& dests);
 
 int lf_spmm_hyb_f32(const lf_hyb* A, const float* B, int64_t ldb, float* C, int64_t ldc, int32_t N,
                     int32_t flags, void* stream) {
   DestList none;
   none.n = 0;
   none.pad_ = 0;
-  return spmm_hyb_impl(A, B, ldb, C, ldc, N, flags, stream, none);
+  return spmm_hyb_impl(A, B, false, ldb, C, ldc, N, flags, stream, none);
+}
+
+int lf_spmm_hyb_bf16(const lf_hyb* A, const uint16_t* B, int64_t ldb, float* C, int64_t ldc, int32_t N,
+                     int32_t flags, void* stream) {
+  DestList none;
+  none.n = 0;
+  none.pad_ = 0;
+  if (N % 8 != 0 || ldb % 8 != 0 || ldc % 4 != 0 || (uintptr_t)B % 16 != 0 || (uintptr_t)C % 16 != 0)
+    return fail(LF_ERR_UNSUPPORTED, "the bf16 SpMM needs N and ldb multiples of 8, ldc a multiple of 4 and 16-byte aligned B and C");
+  return spmm_hyb_impl(A, B, true, ldb, C, ldc, N, flags, stream, none);
 }
 
 int lf_spmm_hyb_f32_bcast(const lf_hyb* A, const float* B, int64_t ldb, float* const* C_full, int32_t num_dests,
@@ -510,11 +597,11 @@ int lf_spmm_hyb_f32_bcast(const lf_hyb* A, const float* B, int64_t ldb, float* c
     LF_REQUIRE(d.p[k] && (uintptr_t)d.p[k] % 16 == 0, "destination %d is null or not 16-byte aligned", k);
   LF_REQUIRE(N % 4 == 0 && ldc % 4 == 0 && ldb % 4 == 0 && (uintptr_t)B % 16 == 0,
              "the broadcasting SpMM needs N, ldb, ldc multiples of 4 and 16-byte aligned operands");
-  return spmm_hyb_impl(A, B, ldb, d.p[0], ldc, N, LF_SPMM_OVERWRITE, stream, d);
+  return spmm_hyb_impl(A, B, false, ldb, d.p[0], ldc, N, LF_SPMM_OVERWRITE, stream, d);
 }
 
-static int spmm_hyb_impl(const lf_hyb* A, const float* B, int64_t ldb, float* C, int64_t ldc, int32_t N,
-                         int32_t flags, void* stream, const DestList& dests) {
+static int spmm_hyb_impl(const lf_hyb* A, const void* B, bool b_is_bf16, int64_t ldb, float* C, int64_t ldc,
+                         int32_t N, int32_t flags, void* stream, const DestList& dests) {
   if (int s = check_hyb(A)) return s;
   LF_REQUIRE(N >= 1, "N must be >= 1");
   LF_REQUIRE(ldb >= N && ldc >= N && ldb < (1ll << 31), "bad leading dimensions");
@@ -526,7 +613,7 @@ static int spmm_hyb_impl(const lf_hyb* A, const float* B, int64_t ldb, float* C,
   cudaStream_t st = (cudaStream_t)stream;
   const int64_t shard_rows = A->row_end - A->row_begin;
   if (shard_rows == 0) return LF_OK;
-  const FeatCfg cfg = pick_cfg(B, ldb, C, ldc, N);
+  const FeatCfg cfg = b_is_bf16 ? pick_cfg_bf16(N) : pick_cfg(B, ldb, C, ldc, N);
   const bool accumulate = flags == LF_SPMM_ACCUMULATE;
   const bool all_atomic = accumulate || A->num_parts > 1;
 
@@ -549,7 +636,7 @@ static int spmm_hyb_impl(const lf_hyb* A, const float* B, int64_t ldb, float* C,
       LF_REQUIRE(A->zero_rows, "zero_rows missing");
       const int64_t want = ceil_div64(A->num_zero_rows, kThreads / 32);
       const int grid = (int)(want > 148 * 16 ? 148 * 16 : want);
-      if (cfg.VEC == 4)
+      if (cfg.VEC != 1)
         zero_rows_kernel<4><<<grid, kThreads, 0, st>>>(A->zero_rows, A->num_zero_rows, C, ldc, N, A->row_begin);
       else
         zero_rows_kernel<1><<<grid, kThreads, 0, st>>>(A->zero_rows, A->num_zero_rows, C, ldc, N, A->row_begin);

@@ -250,10 +250,11 @@ def build_hyb_device(csr: DeviceCsr, bucket_widths: Sequence[Sequence[int]],
 
 
 def spmm_hyb(fmt: HybFormat, B, out=None, accumulate: bool = False):
-    """``lf_spmm_hyb_f32``: returns ``C[row_begin:row_end]`` (float32, on the format's device)."""
+    """``lf_spmm_hyb_f32`` (or ``lf_spmm_hyb_bf16`` when B is bfloat16): returns
+    ``C[row_begin:row_end]`` (float32, on the format's device)."""
     torch = _torch()
     lib = _cabi.load()
-    assert B.is_cuda and B.dtype == torch.float32 and B.dim() == 2 and B.stride(1) == 1
+    assert B.is_cuda and B.dtype in (torch.float32, torch.bfloat16) and B.dim() == 2 and B.stride(1) == 1
     assert B.shape[0] == fmt.shape[1], "B must have one row per matrix column"
     N = int(B.shape[1])
     n_rows = fmt.row_end - fmt.row_begin
@@ -264,7 +265,8 @@ def spmm_hyb(fmt: HybFormat, B, out=None, accumulate: bool = False):
     assert out.shape == (n_rows, N) and out.stride(1) == 1 and out.dtype == torch.float32
     with torch.cuda.device(B.device):
         s = fmt.c_struct()
-        check(lib.lf_spmm_hyb_f32(C.byref(s), B.data_ptr(), B.stride(0), out.data_ptr(), out.stride(0), N,
+        fn = lib.lf_spmm_hyb_f32 if B.dtype == torch.float32 else lib.lf_spmm_hyb_bf16
+        check(fn(C.byref(s), B.data_ptr(), B.stride(0), out.data_ptr(), out.stride(0), N,
                                   _cabi.LF_SPMM_ACCUMULATE if accumulate else _cabi.LF_SPMM_OVERWRITE,
                                   _stream_ptr(torch)))
     return out

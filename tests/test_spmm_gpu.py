@@ -208,3 +208,21 @@ def test_broadcasting_spmm_two_destinations_on_one_gpu(cuda_device):
         want = _ref(csr, B)
         for t in full:
             np.testing.assert_allclose(t.cpu().numpy(), want, rtol=RTOL, atol=ATOL)
+
+
+@pytest.mark.parametrize("N", [8, 64, 128, 256, 512, 1000])
+def test_bf16_features_fp32_accumulate(cuda_device, N):
+    """B in bf16, values and accumulation in float32: rel 1e-2 against the float64 product of the
+    unrounded B, and 1e-5 against the product of the rounded B (isolates the accumulation)."""
+    import torch
+    for name, P in (("skew_8192_s3", 1), ("powerlaw_8192_s1", 3)):
+        csr, d, fmt, B, Bd = _setup(name, P, N, cuda_device)
+        B16 = Bd.to(torch.bfloat16)
+        C = hyb.spmm_hyb(fmt, B16).cpu().numpy()
+        want = _ref(csr, B)
+        assert np.abs(C - want).max() <= 1e-2 * np.abs(want).max()
+        rounded = ho.spmm_scipy_csr(csr.indptr, csr.indices, csr.data.astype(np.float64), csr.shape,
+                                    B16.float().cpu().numpy().astype(np.float64))
+        np.testing.assert_allclose(C, rounded, rtol=RTOL, atol=ATOL)
+    with pytest.raises(Exception, match="multiples of 8"):
+        hyb.spmm_hyb(fmt, torch.zeros((csr.shape[1], 12), dtype=torch.bfloat16, device=cuda_device))
