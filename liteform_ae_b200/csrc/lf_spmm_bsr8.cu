@@ -103,17 +103,21 @@ __global__ void __launch_bounds__(kThreadsBsr, MINB)
 bsr8_spmm_f32_kernel(const int64_t* __restrict__ indptr, const int32_t* __restrict__ indices,
                      const float* __restrict__ blocks, int64_t block_row_begin, int64_t block_row_end,
                      const float* __restrict__ B, int ldb, float* __restrict__ C, int64_t ldc, int N,
-                     int tiles, int rows_per_warp) {
+                     int tiles, int rows_per_warp, int64_t tile_major_groups) {
   using Cfg = F32Cfg<T, D>;
   extern __shared__ __align__(128) uint8_t smem_raw[];
   const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3, warp = threadIdx.x >> 5;
-  // tile index runs fastest so that the tiles of one block row are resident together and the
-  // A blocks they share are fetched from HBM once
+  // Default order: tile index fastest, so the tiles of one block row are resident together and
+  // the A blocks they share come from HBM once.  With many tiles the B rows all of them gather
+  // (band x N) outgrow the L2; then (tile_major_groups > 0) all row groups of tile 0 run first,
+  // then tile 1, ...: B is read from HBM once per tile and A once per tile.
   const int64_t work = (int64_t)blockIdx.x * kWarps + warp;
-  const int64_t I0 = block_row_begin + (work / tiles) * rows_per_warp;
-  if (I0 >= block_row_end) return;
+  const int64_t grp = tile_major_groups > 0 ? work % tile_major_groups : work / tiles;
+  const int tile = (int)(tile_major_groups > 0 ? work / tile_major_groups : work % tiles);
+  const int64_t I0 = block_row_begin + grp * rows_per_warp;
+  if (I0 >= block_row_end || tile >= tiles) return;
   const int R = (int)min((int64_t)rows_per_warp, block_row_end - I0);
-  const int F = (int)(work % tiles) * (64 * T);
+  const int F = tile * (64 * T);
   uint8_t* ring = smem_raw + warp * (D * Cfg::kStage);
   const uint32_t ring_u32 = smem_u32(ring);
 
@@ -374,6 +378,7 @@ bsr8_spmm_16bit_kernel(const int64_t* __restrict__ indptr, const int32_t* __rest
 // tuning state of the block kernels (lf_bsr_set_tuning)
 int g_bsr_feat_units = 0;   // 0 = automatic, 1 or 2 = features per warp / 64 of the float32 kernel
 int g_bsr_stages = 0;       // 0 = automatic, 3 or 4 = depth of the per-warp copy ring
+int g_bsr_tile_major = -1;  // -1 = automatic (float32, more than three feature tiles), 0 = never, 1 = always
 int g_bsr_rows_per_warp = 0;  // 0 = automatic (4 float32, 8 16-bit); block rows one warp streams through, 1..31
 
 int check_common(const void* indptr, const void* indices, const void* blocks, int64_t r0, int64_t r1,
@@ -409,6 +414,8 @@ int lf_bsr_set_tuning(int32_t feat_units, int32_t stages, int32_t rows_per_warp)
   g_bsr_feat_units = feat_units;
   g_bsr_stages = stages;
   g_bsr_rows_per_warp = rows_per_warp;
+  const char* e = getenv("LF_BSR_TILE_MAJOR");
+  if (e) g_bsr_tile_major = atoi(e) > 0 ? 1 : (atoi(e) == 0 ? 0 : -1);
   return LF_OK;
 }
 
@@ -423,14 +430,18 @@ int lf_spmm_bsr8_f32(const int64_t* indptr, const int32_t* indices, const float*
   const int D = g_bsr_stages ? g_bsr_stages : (T == 2 ? 3 : 4);
   const int tiles = (N + 64 * T - 1) / (64 * T);
   const int rpw = g_bsr_rows_per_warp ? g_bsr_rows_per_warp : 4;
-  const int64_t grid = ceil_div64(ceil_div64(rows, rpw) * tiles, kWarps);
+  const int64_t groups = ceil_div64(rows, rpw);
+  const int64_t grid = ceil_div64(groups * tiles, kWarps);
+  // measured on the banded benchmark matrix: no difference up to three tiles (N <= 384), 10 %
+  // faster with four (N = 512), where the B rows of all tiles together no longer fit the L2
+  const int64_t tile_major = (g_bsr_tile_major < 0 ? tiles > 3 : g_bsr_tile_major > 0) ? groups : 0;
   LF_REQUIRE(grid < (1ll << 31), "too many thread blocks");
 #define LF_BSR(T_, D_, M_)                                                                                   \
   do {                                                                                                       \
     auto k = bsr8_spmm_f32_kernel<T_, D_, M_>;                                                               \
     if (int s = set_smem(k, F32Cfg<T_, D_>::kSmem)) return s;                                                \
     k<<<(unsigned)grid, kThreadsBsr, F32Cfg<T_, D_>::kSmem, st>>>(indptr, indices, blocks, block_row_begin,  \
-                                                                  block_row_end, B, (int)ldb, C, ldc, N, tiles, rpw); \
+                                                                  block_row_end, B, (int)ldb, C, ldc, N, tiles, rpw, tile_major); \
   } while (0)
   if (T == 2) { if (D == 3) LF_BSR(2, 3, 2); else LF_BSR(2, 4, 1); }
   else        { if (D == 3) LF_BSR(1, 3, 3); else LF_BSR(1, 4, 3); }
