@@ -14,9 +14,14 @@
 //   * G lanes (8, 16 or 32) form a group; lane l of the group owns features [f0 + 4*l, +4) of V
 //     consecutive G*4-wide feature chunks, so one B-row gather is a 128-bit load per lane and a
 //     fully coalesced 128..512 B segment per group;
-//   * the group reads the (col, val) slots of its ELL rows G at a time, coalesced, and broadcasts
-//     them with shuffles; U gathers are issued back to back before any FMA consumes them;
-//   * padded slots (val == 0) issue no gather.
+//   * the group reads the (col, val) slots and row ids of its ELL rows G at a time, coalesced,
+//     parks them in shared memory and broadcasts one pair per gather with a 64-bit shared load;
+//     U gathers are issued back to back before any FMA consumes them;
+//   * the kernel is specialised on min(width, 8): a row id is compared only where an ELL row can
+//     start, so buckets of width >= 8 pay one check per 8 gathers;
+//   * padded slots (val == 0) issue no gather;
+//   * variants of the same code: B in bf16 (8 features per lane), and a broadcasting epilogue that
+//     stores every row into several full-size C matrices (the GPUs of a group) at once.
 #include "lf_common.cuh"
 
 namespace lf {

@@ -15,7 +15,7 @@ format in device memory, ``spmm`` returns C.
 """
 from __future__ import annotations
 
-from typing import List, Optional, Sequence
+from typing import List, Sequence
 
 import numpy as np
 

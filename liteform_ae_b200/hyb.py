@@ -242,7 +242,6 @@ def build_hyb_device(csr: DeviceCsr, bucket_widths: Sequence[Sequence[int]],
         sc_bytes = lib.lf_hyb_fill_scratch_bytes(n_rows_total)
         scratch = torch.empty(sc_bytes, dtype=torch.uint8, device=dev)
         layout = fmt.c_struct()
-        # zero_rows pointer must be set even when the torch tensor is empty-but-allocated
         check(lib.lf_hyb_fill(t_ptr(csr.indptr), t_ptr(csr.indices), t_ptr(csr.data), C.byref(layout),
                               t_ptr(ws), ws_bytes, t_ptr(scratch), sc_bytes, stream))
         torch.cuda.current_stream().synchronize()   # ws / scratch are released on return

@@ -29,8 +29,7 @@ from __future__ import annotations
 
 import bisect
 import hashlib
-import math
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Dict, List, Sequence, Tuple
 
 import numpy as np

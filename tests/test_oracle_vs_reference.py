@@ -1,7 +1,6 @@
 """Run the unmodified reference next to the oracle (only where a reference checkout exists)."""
 import warnings
 
-import numpy as np
 import pytest
 
 from oracle import hyb_oracle as ho
