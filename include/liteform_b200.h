@@ -212,10 +212,14 @@ int lf_spmm_hyb_f32_host(const lf_hyb* A_host /* rows/cols/vals/zero_rows are [h
 /* ---------------------------------------------------------------------------------------------
  * CSR SpMM, C = A * B.  Replaces the kernel of bench_naive (playground_pipline/
  * format_algos.py:1660-1755); also the fallback the reference pipeline takes when the block
- * format fails (proc05.spmm.end-to-end.py:237-249).
+ * format fails (proc05.spmm.end-to-end.py:237-249).  Work is split by stored entries, not by
+ * rows: a long row is shared by many thread groups (vector atomics into rows that a preparation
+ * launch cleared) and short rows are packed together, so no format has to be built first.
  * ------------------------------------------------------------------------------------------- */
 int lf_spmm_csr_f32(const int64_t* indptr /*[dev]*/, const int32_t* indices /*[dev]*/,
                     const float* data /*[dev] or NULL: all ones*/, int64_t row_begin, int64_t row_end,
+                    int64_t nnz /* exact number of entries of rows [row_begin,row_end), or -1: the call
+                                   reads it back and synchronises the stream */,
                     const float* B /*[dev]*/, int64_t ldb, float* C /*[dev]*/, int64_t ldc,
                     int32_t N, void* stream);
 

@@ -71,7 +71,7 @@ SIGNATURES = {
     "lf_spmm_hyb_f32_bcast": (C.c_int, [C.POINTER(LfHyb), vp, C.c_int64, vp, C.c_int32, C.c_int64, C.c_int32, vp]),
     "lf_spmm_hyb_f32_host_workspace_bytes": (C.c_size_t, [C.POINTER(LfHyb), C.c_int32]),
     "lf_spmm_hyb_f32_host": (C.c_int, [C.POINTER(LfHyb), vp, vp, C.c_int32, C.c_int32, vp, C.c_size_t, vp]),
-    "lf_spmm_csr_f32": (C.c_int, [vp, vp, vp, C.c_int64, C.c_int64, vp, C.c_int64, vp, C.c_int64, C.c_int32, vp]),
+    "lf_spmm_csr_f32": (C.c_int, [vp, vp, vp, C.c_int64, C.c_int64, C.c_int64, vp, C.c_int64, vp, C.c_int64, C.c_int32, vp]),
     "lf_bsr_set_tuning": (C.c_int, [C.c_int32, C.c_int32, C.c_int32]),
     "lf_spmm_bsr8_f32": (C.c_int, [vp, vp, vp, C.c_int64, C.c_int64, vp, C.c_int64, vp, C.c_int64, C.c_int32, vp]),
     "lf_spmm_bsr8_bf16": (C.c_int, [vp, vp, vp, C.c_int64, C.c_int64, vp, C.c_int64, vp, C.c_int64, C.c_int32, vp]),

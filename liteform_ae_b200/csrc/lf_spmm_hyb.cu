@@ -341,53 +341,149 @@ zero_rows_multi_kernel(const int32_t* __restrict__ zero_rows, int64_t n, const _
   }
 }
 
-// CSR row-per-group SpMM (the "naive" kernel of the reference, format_algos.py:1660-1686).
+// ---------------------------------------------------------------------------------------------
+// CSR SpMM (the kernel behind bench_naive, format_algos.py:1660-1755), balanced over entries
+// instead of rows: every thread group takes `spg` consecutive stored entries, whatever rows they
+// belong to, so a 100 000-entry row is shared by hundreds of groups and short rows are packed
+// together.  A row that lies inside one group's range is written with a plain store; a row cut
+// by a range boundary is accumulated with vector atomics after csr_prepare_kernel cleared it.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+csr_prepare_kernel(const int64_t* __restrict__ indptr, int64_t row_begin, int64_t row_end, int64_t spg,
+                   float* __restrict__ C, int64_t ldc, int N) {
+  const int64_t rows = row_end - row_begin;
+  const int64_t base = indptr[row_begin];
+  const int64_t total = indptr[row_end] - base;
+  const int64_t groups = (total + spg - 1) / spg;
+  const int64_t n = rows > groups ? rows : groups;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    int64_t zero_row = -1;
+    if (i < rows && indptr[row_begin + i] == indptr[row_begin + i + 1]) zero_row = i;   // empty row
+    if (zero_row >= 0) {
+      float* dst = C + zero_row * ldc;
+      for (int f = 0; f < N; ++f) dst[f] = 0.f;
+    }
+    if (i >= 1 && i < groups) {   // the row that contains the first entry of group i, if it started earlier
+      const int64_t x = base + i * spg;
+      int64_t lo = row_begin, hi = row_end;   // indptr[lo] <= x, answer in [lo, hi)
+      while (hi - lo > 1) {
+        const int64_t mid = (lo + hi) >> 1;
+        if (indptr[mid] <= x) lo = mid; else hi = mid;
+      }
+      if (indptr[lo] < x) {
+        float* dst = C + (lo - row_begin) * ldc;
+        for (int f = 0; f < N; ++f) dst[f] = 0.f;
+      }
+    }
+  }
+}
+
 template <int G, int V, int VEC>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 3)
 spmm_csr_kernel(const int64_t* __restrict__ indptr, const int32_t* __restrict__ indices,
                 const float* __restrict__ data, int64_t row_begin, int64_t row_end,
-                const float* __restrict__ B, int64_t ldb, float* __restrict__ C, int64_t ldc, int N) {
+                const float* __restrict__ B, int ldb, float* __restrict__ C, int64_t ldc, int N, int spg) {
   constexpr int GPC = kThreads / G;
   constexpr int U = V == 1 ? 8 : (V == 2 ? 4 : 2);
+  __shared__ int2 s_cv[kThreads];
+  __shared__ int64_t s_bd[kThreads];
   const int g = threadIdx.x / G, lane = threadIdx.x % G;
-  const unsigned gmask = G == 32 ? 0xffffffffu : (((1u << G) - 1u) << ((threadIdx.x & 31) / G * G));
-  const int64_t r = row_begin + (int64_t)blockIdx.x * GPC + g;
-  if (r >= row_end) return;
+  const int shift = (threadIdx.x & 31) / G * G;
+  const unsigned gmask = G == 32 ? 0xffffffffu : (((1u << G) - 1u) << shift);
+  const int64_t base = indptr[row_begin];
+  const int64_t total = indptr[row_end] - base;
+  const int64_t s0 = ((int64_t)blockIdx.x * GPC + g) * (int64_t)spg;
+  if (s0 >= total) return;
+  const int64_t s1 = min(s0 + spg, total);
+  int2* cv = s_cv + g * G;
+  int64_t* bd = s_bd + g * G;
+
+  // (G+1)-ary search, one probe per lane: the row that holds entry s0
+  int64_t lo = row_begin, hi = row_end;   // indptr[lo] - base <= s0, answer in [lo, hi)
+  while (hi - lo > 1) {
+    const int64_t span = hi - lo;
+    int64_t q = lo + ((int64_t)(lane + 1) * span) / (G + 1);
+    if (q <= lo) q = lo + 1;
+    const bool le = indptr[q] - base <= s0;
+    const int cnt = __popc((__ballot_sync(gmask, le) & gmask) >> shift);   // probes are monotone
+    const int64_t qlo = __shfl_sync(gmask, q, cnt > 0 ? cnt - 1 : 0, G);
+    const int64_t qhi = __shfl_sync(gmask, q, cnt < G ? cnt : G - 1, G);
+    if (cnt > 0) lo = qlo;
+    if (cnt < G) hi = qhi;
+  }
+  int64_t cur = lo;
+  const int64_t first_row = cur;
+  const bool head_open = indptr[cur] - base < s0;
+
+  // boundaries of the next G rows, refilled when used up
+  int kb = 0;
+  auto refill = [&]() {
+    __syncwarp(gmask);
+    const int64_t r = cur + 1 + lane;
+    bd[lane] = indptr[r < row_end ? r : row_end] - base;
+    __syncwarp(gmask);
+    kb = 0;
+  };
+  refill();
+  int64_t nb = bd[0];   // first entry of the next row
+
   const int f0 = blockIdx.y * (G * V * VEC) + lane * VEC;
   bool active[V];
   Chunk<VEC> acc[V];
 #pragma unroll
   for (int v = 0; v < V; ++v) { active[v] = f0 + v * G * VEC < N; acc[v].zero(); }
-  const int64_t s0 = indptr[r], s1 = indptr[r + 1];
+
+  auto flush = [&](int64_t row, bool open) {
+    float* dst = C + (row - row_begin) * ldc + f0;
+#pragma unroll
+    for (int v = 0; v < V; ++v) {
+      if (active[v]) {
+        if (open) acc[v].red(dst + v * G * VEC); else acc[v].store_stream(dst + v * G * VEC);
+      }
+      acc[v].zero();
+    }
+  };
+
+  const float* __restrict__ Bf = B + f0;
   for (int64_t s = s0; s < s1; s += G) {
     const int64_t idx = s + lane;
     const bool in = idx < s1;
-    const int my_col = in ? indices[idx] : 0;
-    const float my_val = in ? (data ? data[idx] : 1.f) : 0.f;
+    const int my_col = in ? __ldcs(indices + base + idx) : 0;
+    const float my_val = in ? (data ? __ldcs(data + base + idx) : 1.f) : 0.f;
+    __syncwarp(gmask);
+    cv[lane] = make_int2(my_col, __float_as_int(my_val));
+    __syncwarp(gmask);
     const int nstrip = (int)min((int64_t)G, s1 - s);
     for (int t = 0; t < nstrip; t += U) {
       float val[U];
       Chunk<VEC> b[U][V];
 #pragma unroll
       for (int u = 0; u < U; ++u) {
-        const int c = __shfl_sync(gmask, my_col, t + u, G);
-        val[u] = __shfl_sync(gmask, my_val, t + u, G);
-        const float* src = B + (int64_t)c * ldb + f0;
+        const int2 p = cv[t + u];
+        val[u] = __int_as_float(p.y);
+        const float* src = Bf + (int64_t)p.x * ldb;
 #pragma unroll
         for (int v = 0; v < V; ++v) {
           if (val[u] != 0.f && active[v]) b[u][v].load(src + v * G * VEC); else b[u][v].zero();
         }
       }
 #pragma unroll
-      for (int u = 0; u < U; ++u)
+      for (int u = 0; u < U; ++u) {
+        const int64_t pos = s + t + u;
+        if (pos < s1) {
+          while (pos == nb) {   // the current row ended here (and empty rows may follow)
+            flush(cur, cur == first_row && head_open);
+            ++cur;
+            if (++kb == G) refill();
+            nb = bd[kb];
+          }
 #pragma unroll
-        for (int v = 0; v < V; ++v) acc[v].fma(val[u], b[u][v]);
+          for (int v = 0; v < V; ++v) acc[v].fma(val[u], b[u][v]);
+        }
+      }
     }
   }
-  float* dst = C + (r - row_begin) * ldc + f0;
-#pragma unroll
-  for (int v = 0; v < V; ++v)
-    if (active[v]) acc[v].store(dst + v * G * VEC);
+  flush(cur, (cur == first_row && head_open) || s1 < nb);
 }
 
 struct FeatCfg { int G, V, VEC, pass; };
@@ -757,20 +853,39 @@ int lf_spmm_hyb_f32_host(const lf_hyb* A, const float* B, float* C, int32_t N, i
 }
 
 int lf_spmm_csr_f32(const int64_t* indptr, const int32_t* indices, const float* data, int64_t row_begin,
-                    int64_t row_end, const float* B, int64_t ldb, float* C, int64_t ldc, int32_t N,
+                    int64_t row_end, int64_t nnz, const float* B, int64_t ldb, float* C, int64_t ldc, int32_t N,
                     void* stream) {
-  LF_REQUIRE(N >= 1 && ldb >= N && ldc >= N, "bad arguments");
+  LF_REQUIRE(N >= 1 && ldb >= N && ldc >= N && ldb < (1ll << 31), "bad arguments");
   LF_REQUIRE(0 <= row_begin && row_begin <= row_end, "bad row range");
   if (row_begin == row_end) return LF_OK;
   LF_REQUIRE(indptr && B && C, "null pointer argument");
   cudaStream_t st = (cudaStream_t)stream;
+  if (nnz < 0) {   // the launch shape depends on the number of entries: read it back
+    int64_t ends[2] = {0, 0};
+    LF_CUDA_CHECK(cudaMemcpyAsync(&ends[0], indptr + row_begin, sizeof(int64_t), cudaMemcpyDeviceToHost, st));
+    LF_CUDA_CHECK(cudaMemcpyAsync(&ends[1], indptr + row_end, sizeof(int64_t), cudaMemcpyDeviceToHost, st));
+    LF_CUDA_CHECK(cudaStreamSynchronize(st));
+    nnz = ends[1] - ends[0];
+  }
+  LF_REQUIRE(nnz == 0 || indices, "indices missing");
   const FeatCfg cfg = pick_cfg(B, ldb, C, ldc, N);
   const int gpc = kThreads / cfg.G;
-  const int64_t blocks = ceil_div64(row_end - row_begin, gpc);
-  LF_REQUIRE(blocks < (1ll << 31), "row range too large");
+  int spg = 256;   // entries per group; smaller for small matrices so that the grid has several waves
+  while (spg > 32 && ceil_div64(nnz, (int64_t)spg * gpc) < (int64_t)sm_count() * 3 * 8) spg >>= 1;
+  {
+    const int64_t rows = row_end - row_begin, groups = ceil_div64(nnz, spg);
+    const int64_t n = rows > groups ? rows : groups;
+    const int64_t want = ceil_div64(n, 256);
+    csr_prepare_kernel<<<(unsigned)(want > 148 * 32 ? 148 * 32 : want), 256, 0, st>>>(indptr, row_begin, row_end, spg, C, ldc, N);
+    LF_CUDA_CHECK(cudaGetLastError());
+  }
+  if (nnz == 0) return LF_OK;
+  const int64_t blocks = ceil_div64(nnz, (int64_t)spg * gpc);
+  LF_REQUIRE(blocks < (1ll << 31), "too many thread blocks");
   dim3 grid((unsigned)blocks, (unsigned)((N + cfg.pass - 1) / cfg.pass));
-#define LF_LAUNCH(G_, V_, VEC_) \
-  spmm_csr_kernel<G_, V_, VEC_><<<grid, kThreads, 0, st>>>(indptr, indices, data, row_begin, row_end, B, ldb, C, ldc, N)
+#define LF_LAUNCH(G_, V_, VEC_)                                                                              \
+  spmm_csr_kernel<G_, V_, VEC_><<<grid, kThreads, 0, st>>>(indptr, indices, data, row_begin, row_end, B, (int)ldb, \
+                                                           C, ldc, N, spg)
   if (cfg.VEC == 4) {
     if (cfg.G == 8) LF_LAUNCH(8, 1, 4);
     else if (cfg.G == 16) LF_LAUNCH(16, 1, 4);

@@ -281,7 +281,8 @@ def spmm_csr(csr: DeviceCsr, B, out=None, row_range=None):
     if out is None:
         out = torch.empty((r1 - r0, N), dtype=torch.float32, device=B.device)
     with torch.cuda.device(B.device):
-        check(lib.lf_spmm_csr_f32(t_ptr(csr.indptr), t_ptr(csr.indices), t_ptr(csr.data), r0, r1,
+        nnz = csr.nnz if (r0, r1) == (0, csr.shape[0]) else -1
+        check(lib.lf_spmm_csr_f32(t_ptr(csr.indptr), t_ptr(csr.indices), t_ptr(csr.data), r0, r1, nnz,
                                   B.data_ptr(), B.stride(0), out.data_ptr(), out.stride(0), N,
                                   _stream_ptr(torch)))
     return out

@@ -226,3 +226,28 @@ def test_bf16_features_fp32_accumulate(cuda_device, N):
         np.testing.assert_allclose(C, rounded, rtol=RTOL, atol=ATOL)
     with pytest.raises(Exception, match="multiples of 8"):
         hyb.spmm_hyb(fmt, torch.zeros((csr.shape[1], 12), dtype=torch.bfloat16, device=cuda_device))
+
+
+@pytest.mark.parametrize("N", [32, 64, 128, 200, 512])
+def test_csr_spmm_balanced_over_entries(cuda_device, N):
+    """Long rows shared by many groups, empty rows (leading, trailing, in between), row ranges."""
+    import torch
+    csr = synth.skewed_rows(M=4096, seed=11, heavy_rows=5, heavy_len=3000)
+    lens = np.diff(csr.indptr).copy()
+    for r in (0, 1, 2, 77, 78, 4094, 4095):       # carve empty rows
+        lens[r] = 0
+    keep = np.repeat(lens > 0, np.diff(csr.indptr))
+    indptr = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)
+    csr2 = synth.Csr(indptr, csr.indices[keep], csr.data[keep], csr.shape)
+    d = hyb.DeviceCsr.from_host(csr2.indptr, csr2.indices, csr2.data, csr2.shape, cuda_device)
+    B = synth.dense_features(4096, N, 5)
+    Bd = torch.from_numpy(B).to(cuda_device)
+    want = _ref(csr2, B)
+    C = torch.full((4096, N), float("nan"), device=cuda_device)
+    hyb.spmm_csr(d, Bd, out=C)
+    np.testing.assert_allclose(C.cpu().numpy(), want, rtol=RTOL, atol=ATOL)
+    part = hyb.spmm_csr(d, Bd, row_range=(70, 3000)).cpu().numpy()
+    np.testing.assert_allclose(part, want[70:3000], rtol=RTOL, atol=ATOL)
+    ones = hyb.DeviceCsr(d.indptr, d.indices, None, d.shape)      # data = NULL: all ones
+    pattern = synth.Csr(csr2.indptr, csr2.indices, np.ones(csr2.nnz, dtype=np.float32), csr2.shape)
+    np.testing.assert_allclose(hyb.spmm_csr(ones, Bd).cpu().numpy(), _ref(pattern, B), rtol=RTOL, atol=ATOL)
