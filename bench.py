@@ -179,7 +179,8 @@ def run_reference(args, rank, world):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": t / args.steps * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic (seeded)",
-        "config": {"workload": f"{args.workload}: {desc}", "rows": csr.shape[0], "nnz": csr.nnz, "N": N},
+        "config": {"workload": f"{args.workload}: {desc}", "format": "scipy csr on the host", "rows": csr.shape[0],
+                   "cols": csr.shape[1], "nnz": csr.nnz, "N": N},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -207,18 +208,19 @@ class HybProblem:
         self.t_gen = time.perf_counter() - t0
         self.nnz = csr.nnz
         d_csr = hyb.DeviceCsr.from_host(csr.indptr, csr.indices, csr.data, csr.shape, dev)
-        torch.cuda.synchronize(dev)
-        t0 = time.perf_counter()
-        stats, hist = hyb.hyb_stats(d_csr, P)
-        self.widths = width_search.search_from_stats(stats, hist, N, P)
-        torch.cuda.synchronize(dev)
-        self.t_search = time.perf_counter() - t0
         cuts = hyb.shard_rows(d_csr, world)
         self.r0, self.r1 = my_range(cuts, rank)
-        t0 = time.perf_counter()
-        self.fmt = hyb.build_hyb_device(d_csr, self.widths, row_range=(self.r0, self.r1), with_mask=False)
-        torch.cuda.synchronize(dev)
-        self.t_build = time.perf_counter() - t0
+        for attempt in range(2):   # the first pass pays context and module load; report the second
+            torch.cuda.synchronize(dev)
+            t0 = time.perf_counter()
+            stats, hist = hyb.hyb_stats(d_csr, P)
+            self.widths = width_search.search_from_stats(stats, hist, N, P)
+            torch.cuda.synchronize(dev)
+            self.t_search = time.perf_counter() - t0
+            t0 = time.perf_counter()
+            self.fmt = hyb.build_hyb_device(d_csr, self.widths, row_range=(self.r0, self.r1), with_mask=False)
+            torch.cuda.synchronize(dev)
+            self.t_build = time.perf_counter() - t0
         del d_csr
         self.B = torch.from_numpy(self.B_host).to(dev)
         self.eb = 4
