@@ -389,6 +389,37 @@ class BsrProblem:
                        "l2": "inputs exceed L2 (A %.0f MB + B %.0f MB per rank); no flush between steps" % (
                            self.nnz * eb / 1e6 / world, self.B_host.size * eb / 1e6)}
         self.extra = {"generate_s": self.t_gen}
+        if not args.no_build_timing:
+            self.extra.update(self.time_device_builder(name))
+
+    def time_device_builder(self, dtype_name):
+        """CSR -> 8x8 blocks on the device (lf_bsr8_plan + lf_bsr8_fill), timed on the element CSR form
+        of this matrix.  The CSR arrays are laid out on the device from the block arrays (every block
+        row of the synthetic matrix holds the same number of blocks, so this is a reshape)."""
+        torch = self.torch
+        from liteform_ae_b200 import hyb
+        per = np.diff(self.indptr)
+        if per.size == 0 or not (per == per[0]).all():
+            return {}
+        k, Mb = int(per[0]), self.M // 8
+        cols = (self.a.indices.view(Mb, 1, k, 1).to(torch.int32) * 8 +
+                torch.arange(8, dtype=torch.int32, device=self.dev).view(1, 1, 1, 8)).expand(Mb, 8, k, 8).reshape(-1)
+        vals = self.a.blocks.view(Mb, k, 8, 8).permute(0, 2, 1, 3).reshape(-1).float().contiguous()
+        ptr = torch.arange(self.M + 1, dtype=torch.int64, device=self.dev) * (8 * k)
+        csr = hyb.DeviceCsr(ptr, cols.contiguous(), vals, (self.M, self.K))
+        times = []
+        for _ in range(4):
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            built = self.bsr.DeviceBsr8.from_csr_device(csr, dtype_name)
+            torch.cuda.synchronize()
+            times.append(time.perf_counter() - t0)
+        same = bool(torch.equal(built.indptr, self.a.indptr) and torch.equal(built.indices, self.a.indices) and
+                    torch.equal(built.blocks, self.a.blocks))
+        if not same:
+            raise RuntimeError("the device-built blocks differ from the generator's")
+        return {"format_build_ms": statistics.median(times[1:]) * 1e3,
+                "format_build": "CSR (device) -> 8x8 blocks (device), lf_bsr8_plan + lf_bsr8_fill, checked equal to the generated blocks"}
 
     def step(self):
         self.bsr.spmm_bsr8(self.a, self.B, out=self.C, block_row_range=(self.r0, self.r1))
@@ -579,6 +610,7 @@ def main():
     ap.add_argument("--gather", default="none", choices=["none", "nccl", "fused"],
                     help="multi-GPU only: also time product + full C on every rank (NCCL all-gather or fused epilogue)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-build-timing", action="store_true", help="block path: skip timing the device CSR -> blocks builder")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-memory end-to-end leg (profiling runs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup

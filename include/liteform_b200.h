@@ -56,6 +56,9 @@ const char* lf_last_error(void);
 #define LF_OPT_SPMM_SLOTS_PER_GROUP 1  /* ELL slots one thread group walks (0 = automatic: 256, less for small launches) */
 #define LF_OPT_SPMM_CACHE_POLICY 2     /* 0 plain; 1 stream slots and C (default); 2 also B rows evict-last */
 #define LF_OPT_SPMM_MIN_BLOCKS 3       /* resident thread blocks per SM the kernel is compiled for: 2..4 (default 3) */
+#define LF_OPT_BSR_COPY_ENGINE 4        /* how the 8x8 block kernels fill shared memory: 0 automatic, 1 per-lane
+                                          cp.async, 2 tiled bulk copies through a tensor map, 3 one bulk copy per row
+                                          of B (2 and 3 complete on mbarriers) */
 int lf_set_option(int32_t option, int32_t value);
 
 /* ---------------------------------------------------------------------------------------------
@@ -224,6 +227,29 @@ int lf_spmm_csr_f32(const int64_t* indptr /*[dev]*/, const int32_t* indices /*[d
                     int32_t N, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * CSR -> 8x8 block-sparse rows on the device.
+ * Replaces MTX.tobsr_with_padding (playground_pipline/format_matrix_market.py:116-138), which pads
+ * the shape and calls scipy.sparse.bsr_matrix on the host.  The result is what SciPy builds for
+ * blocksize (8, 8) after sort_indices(): bsr_indptr int64[ceil(M/8)+1], block columns ascending
+ * inside a block row, tiles [nb][8][8] row-major with zeros where the matrix has no entry; rows
+ * past M (padding up to a multiple of 8) are empty.  indptr/indices/data: canonical CSR (sorted
+ * columns, no duplicates); data == NULL stands for all ones (what MTX gives a pattern file,
+ * format_matrix_market.py:58-65).
+ *   lf_bsr8_plan  counts the blocks: writes bsr_indptr, returns *num_blocks on the host
+ *                 (synchronises the stream); the caller then allocates the block arrays.
+ *   lf_bsr8_fill  writes bsr_indices int32[nb] and blocks[nb*64] in the dtype asked for
+ *                 (values are rounded to nearest even from float32).
+ * ------------------------------------------------------------------------------------------- */
+#define LF_DTYPE_F32 0
+#define LF_DTYPE_BF16 1
+#define LF_DTYPE_F16 2
+int lf_bsr8_plan(const int64_t* indptr /*[dev]*/, const int32_t* indices /*[dev]*/, int64_t M,
+                 int64_t* bsr_indptr /*[dev] out*/, int64_t* num_blocks /*[host] out*/, void* stream);
+int lf_bsr8_fill(const int64_t* indptr /*[dev]*/, const int32_t* indices /*[dev]*/, const float* data /*[dev]*/,
+                 int64_t M, const int64_t* bsr_indptr /*[dev]*/, int32_t* bsr_indices /*[dev] out*/,
+                 void* blocks /*[dev] out*/, int32_t dtype, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
  * Block-sparse SpMM, 8x8 blocks (BSR): C[block_row_begin*8 : block_row_end*8, 0:N] = A * B.
  * Replaces the kernel of bench_bsrmm (playground_pipline/format_algos.py:1562-1643; arithmetic
  * format_algos.py:1204-1213), which runs 32x32 fp16 blocks through wmma with fp16 accumulators
@@ -242,6 +268,11 @@ int lf_spmm_bsr8_f32(const int64_t* indptr /*[dev]*/, const int32_t* indices /*[
  * kernel in units of 64 (0 = automatic, 1, 2), depth of the per-warp copy ring (0 = automatic, 3,
  * 4) and block rows one warp streams through (0 = automatic, 1..31). */
 int lf_bsr_set_tuning(int32_t feat_units, int32_t stages, int32_t rows_per_warp);
+/* The block kernels that copy through the tensor memory accelerator bound every wait for a copy; a
+ * warp that gives up leaves its rows of C unfinished and counts itself.  This call synchronises
+ * the stream and returns LF_ERR_KERNEL_TIMEOUT if any warp gave up since the last call (clearing
+ * the count), LF_OK otherwise.  No counterpart in the reference. */
+int lf_bsr_copy_status(void* stream);
 /* bf16 blocks and bf16 B (raw 16-bit patterns), float32 C */
 int lf_spmm_bsr8_bf16(const int64_t* indptr, const int32_t* indices, const uint16_t* blocks,
                       int64_t block_row_begin, int64_t block_row_end, const uint16_t* B, int64_t ldb,

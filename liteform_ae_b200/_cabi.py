@@ -21,6 +21,8 @@ LF_ERR_KERNEL_TIMEOUT = -5
 LF_OPT_SPMM_SLOTS_PER_GROUP = 1
 LF_OPT_SPMM_CACHE_POLICY = 2
 LF_OPT_SPMM_MIN_BLOCKS = 3
+LF_OPT_BSR_COPY_ENGINE = 4
+LF_DTYPE_F32, LF_DTYPE_BF16, LF_DTYPE_F16 = 0, 1, 2
 LF_SPMM_OVERWRITE = 0
 LF_SPMM_ACCUMULATE = 1
 NUM_WIDTH_CLASSES = 11
@@ -72,7 +74,10 @@ SIGNATURES = {
     "lf_spmm_hyb_f32_host_workspace_bytes": (C.c_size_t, [C.POINTER(LfHyb), C.c_int32]),
     "lf_spmm_hyb_f32_host": (C.c_int, [C.POINTER(LfHyb), vp, vp, C.c_int32, C.c_int32, vp, C.c_size_t, vp]),
     "lf_spmm_csr_f32": (C.c_int, [vp, vp, vp, C.c_int64, C.c_int64, C.c_int64, vp, C.c_int64, vp, C.c_int64, C.c_int32, vp]),
+    "lf_bsr8_plan": (C.c_int, [vp, vp, C.c_int64, vp, C.POINTER(C.c_int64), vp]),
+    "lf_bsr8_fill": (C.c_int, [vp, vp, vp, C.c_int64, vp, vp, vp, C.c_int32, vp]),
     "lf_bsr_set_tuning": (C.c_int, [C.c_int32, C.c_int32, C.c_int32]),
+    "lf_bsr_copy_status": (C.c_int, [vp]),
     "lf_spmm_bsr8_f32": (C.c_int, [vp, vp, vp, C.c_int64, C.c_int64, vp, C.c_int64, vp, C.c_int64, C.c_int32, vp]),
     "lf_spmm_bsr8_bf16": (C.c_int, [vp, vp, vp, C.c_int64, C.c_int64, vp, C.c_int64, vp, C.c_int64, C.c_int32, vp]),
     "lf_spmm_bsr8_f16": (C.c_int, [vp, vp, vp, C.c_int64, C.c_int64, vp, C.c_int64, vp, C.c_int64, C.c_int32, vp]),

@@ -5,6 +5,7 @@ playground_pipline/format_matrix_market.py:116-138, block size 32, fp16) and tim
 wmma kernel (``bench_bsrmm``, playground_pipline/format_algos.py:1562-1643).  Here the format
 stays SciPy's (``indptr``, sorted ``indices``, dense ``data[nb, R, C]``), re-blocked to 8x8 on
 the host when it comes in coarser, and the product runs on ``lf_spmm_bsr8_{f32,bf16,f16}``.
+``DeviceBsr8.from_csr_device`` converts a CSR matrix that already lies in device memory.
 """
 from __future__ import annotations
 
@@ -48,6 +49,35 @@ class DeviceBsr8:
                           b, (int(shape[0]), int(shape[1])))
 
     @staticmethod
+    def from_csr_device(csr, dtype="float32", padded_shape: Optional[Tuple[int, int]] = None) -> "DeviceBsr8":
+        """CSR in device memory (``hyb.DeviceCsr``) -> 8x8 blocks, without leaving the device
+        (``lf_bsr8_plan`` + ``lf_bsr8_fill``).  ``padded_shape`` (multiples of 8, at least the
+        matrix shape) plays the role of the ``shape`` argument of ``MTX.tobsr_with_padding``
+        (format_matrix_market.py:116-138); by default each dimension is rounded up to 8."""
+        torch = _torch()
+        lib = _cabi.load()
+        import ctypes
+        M, K = csr.shape
+        M8, K8 = (-(-M // 8) * 8, -(-K // 8) * 8) if padded_shape is None else map(int, padded_shape)
+        assert M8 % 8 == 0 and K8 % 8 == 0 and M8 >= M and K8 >= K, "padded shape must be multiples of 8 covering the matrix"
+        dev = csr.indptr.device
+        tdt, code = {"float32": (torch.float32, _cabi.LF_DTYPE_F32), "bfloat16": (torch.bfloat16, _cabi.LF_DTYPE_BF16),
+                     "float16": (torch.float16, _cabi.LF_DTYPE_F16)}[str(dtype)]
+        with torch.cuda.device(dev):
+            stream = torch.cuda.current_stream().cuda_stream
+            indptr8 = torch.empty(M8 // 8 + 1, dtype=torch.int64, device=dev)
+            nb = ctypes.c_int64(0)
+            check(lib.lf_bsr8_plan(t_ptr(csr.indptr), t_ptr(csr.indices), M, t_ptr(indptr8), ctypes.byref(nb), stream))
+            Mb = -(-M // 8)
+            if M8 // 8 > Mb:                       # block rows that exist only as padding
+                indptr8[Mb + 1:] = indptr8[Mb]
+            indices8 = torch.empty(nb.value, dtype=torch.int32, device=dev)
+            blocks = torch.empty((nb.value, 8, 8), dtype=tdt, device=dev)
+            check(lib.lf_bsr8_fill(t_ptr(csr.indptr), t_ptr(csr.indices), t_ptr(csr.data) if csr.data is not None else None,
+                                   M, t_ptr(indptr8), t_ptr(indices8), t_ptr(blocks), code, stream))
+        return DeviceBsr8(indptr8, indices8, blocks, (M8, K8))
+
+    @staticmethod
     def from_scipy(bsr_mat, dtype: Optional[str] = None, device="cuda") -> "DeviceBsr8":
         """Accepts a ``scipy.sparse.bsr_matrix`` with square blocks whose size is a multiple of 8
         (re-blocked to 8x8, all-zero sub-blocks dropped) on a shape that is a multiple of 8."""
@@ -60,7 +90,9 @@ class DeviceBsr8:
         # rebuild in float32 from the raw arrays (SciPy itself has no float16 support)
         m32 = sp.bsr_matrix((m.data.astype(np.float32), m.indices, m.indptr), shape=m.shape, blocksize=(R, Cb))
         if (R, Cb) != (8, 8):
-            m32 = sp.bsr_matrix(m32.tocsr(), blocksize=(8, 8))
+            csr = m32.tocsr()
+            csr.eliminate_zeros()       # the padding inside coarse blocks must not become 8x8 tiles
+            m32 = sp.bsr_matrix(csr, blocksize=(8, 8))
         m32.sort_indices()
         return DeviceBsr8.from_arrays(m32.indptr, m32.indices, m32.data, m32.shape, dtype, device)
 

@@ -32,52 +32,14 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include "lf_bsr8_mma.cuh"
+#include "lf_bsr8_tma.cuh"
 #include "lf_common.cuh"
 
 namespace lf {
 namespace {
 
-constexpr int kWarps = 8;
-constexpr int kThreadsBsr = kWarps * 32;
-
-__device__ __forceinline__ void mma_tf32(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  asm(
-      "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-
-template <bool BF16>
-__device__ __forceinline__ void mma_16bit(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  if (BF16) {
-    asm(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-  } else {
-    asm(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-  }
-}
-
-// 16-byte asynchronous copy global -> shared, bypassing L1; src_bytes = 0 writes zeros.
-__device__ __forceinline__ void cp_async16(uint32_t smem, const void* gmem, int src_bytes) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem), "l"(gmem), "r"(src_bytes) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-// x = hi + lo with hi holding the top 10 mantissa bits (what a tf32 operand keeps); the tensor
-// core ignores the low 13 bits of a tf32 register, so `lo` is passed as it is.
-__device__ __forceinline__ void split_tf32(float x, uint32_t& hi, uint32_t& lo) {
-  hi = __float_as_uint(x) & 0xffffe000u;
-  lo = __float_as_uint(x - __uint_as_float(hi));
-}
+using namespace bsr8;
 
 // ---------------------------------------------------------------------------------------------
 // float32 in / float32 out, 3xTF32.  One warp = one block row x one tile of 64*T features.
@@ -402,6 +364,22 @@ int set_smem(K kernel, int bytes) {
 }
 
 }  // namespace
+
+// 0 = automatic, 1 = per-lane cp.async, 2 = tiled bulk copies, 3 = one bulk copy per B row
+// (LF_OPT_BSR_COPY_ENGINE)
+int g_bsr_copy_engine = 0;
+
+namespace {
+int copy_engine() {
+  static int env = -1;
+  if (env < 0) {
+    const char* e = getenv("LF_BSR_COPY_ENGINE");
+    env = e ? atoi(e) : 0;
+  }
+  const int v = g_bsr_copy_engine ? g_bsr_copy_engine : env;
+  return v >= 1 && v <= 3 ? v : 1;
+}
+}  // namespace
 }  // namespace lf
 
 using namespace lf;
@@ -416,6 +394,13 @@ int lf_bsr_set_tuning(int32_t feat_units, int32_t stages, int32_t rows_per_warp)
   g_bsr_rows_per_warp = rows_per_warp;
   const char* e = getenv("LF_BSR_TILE_MAJOR");
   if (e) g_bsr_tile_major = atoi(e) > 0 ? 1 : (atoi(e) == 0 ? 0 : -1);
+  return LF_OK;
+}
+
+int lf_bsr_copy_status(void* stream) {
+  int n = 0;
+  if (int s = bsr8_tma_timeouts((cudaStream_t)stream, &n)) return s;
+  if (n) return fail(LF_ERR_KERNEL_TIMEOUT, "%d warps of a block kernel gave up waiting for a copy", n);
   return LF_OK;
 }
 
@@ -436,6 +421,9 @@ int lf_spmm_bsr8_f32(const int64_t* indptr, const int32_t* indices, const float*
   // faster with four (N = 512), where the B rows of all tiles together no longer fit the L2
   const int64_t tile_major = (g_bsr_tile_major < 0 ? tiles > 3 : g_bsr_tile_major > 0) ? groups : 0;
   LF_REQUIRE(grid < (1ll << 31), "too many thread blocks");
+  if (T == 2 && copy_engine() > 1)
+    return bsr8_f32_tma_launch(copy_engine() == 3, indptr, indices, blocks, block_row_begin, block_row_end, B, ldb, C, ldc, N, D, rpw,
+                               tile_major > 0, st);
 #define LF_BSR(T_, D_, M_)                                                                                   \
   do {                                                                                                       \
     auto k = bsr8_spmm_f32_kernel<T_, D_, M_>;                                                               \
@@ -461,6 +449,7 @@ static int launch_16bit(bool bf16, const int64_t* indptr, const int32_t* indices
   const int64_t grid = ceil_div64(ceil_div64(r1 - r0, rpw) * tiles, kWarps);
   LF_REQUIRE(grid < (1ll << 31), "too many thread blocks");
   const int D = g_bsr_stages ? g_bsr_stages : 3;
+  if (copy_engine() > 1) return bsr8_16bit_tma_launch(copy_engine() == 3, bf16, indptr, indices, blocks, r0, r1, B, ldb, C, ldc, N, D, rpw, st);
 #define LF_BSR16(B_, D_, M_)                                                                                  \
   do {                                                                                                        \
     auto k = bsr8_spmm_16bit_kernel<B_, D_, M_>;                                                              \

@@ -22,6 +22,7 @@
 //   * padded slots (val == 0) issue no gather;
 //   * variants of the same code: B in bf16 (8 features per lane), and a broadcasting epilogue that
 //     stores every row into several full-size C matrices (the GPUs of a group) at once.
+#include "lf_bsr8_tma.cuh"
 #include "lf_common.cuh"
 
 namespace lf {
@@ -660,6 +661,10 @@ int lf_set_option(int32_t option, int32_t value) {
     case LF_OPT_SPMM_MIN_BLOCKS:
       LF_REQUIRE(value >= 2 && value <= 4, "min blocks %d out of range", value);
       g_min_blocks = value;
+      return LF_OK;
+    case LF_OPT_BSR_COPY_ENGINE:
+      LF_REQUIRE(value >= 0 && value <= 3, "copy engine %d out of range", value);
+      g_bsr_copy_engine = value;
       return LF_OK;
     default:
       return fail(LF_ERR_INVALID_ARGUMENT, "unknown option %d", option);

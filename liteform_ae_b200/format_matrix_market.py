@@ -110,6 +110,12 @@ class MTX:
         bsr.data = bsr.data.astype(np.float16)
         return bsr
 
+    def tobsr_device(self, shape=None, dtype="float16", device="cuda"):
+        """Device-side counterpart of ``tobsr_with_padding`` for 8x8 blocks: the CSR form is
+        uploaded once (and cached), the blocks are cut on the device.  Returns ``bsr.DeviceBsr8``."""
+        from .bsr import DeviceBsr8
+        return DeviceBsr8.from_csr_device(self.csr_device(device), dtype=dtype, padded_shape=shape)
+
     def tocsr(self, copy=False):
         return self.coo_mtx.tocsr(copy=copy)
 
