@@ -48,6 +48,12 @@ typedef enum {
 #define LF_SPMM_ACCUMULATE 1      /* C += A * B  (what the generated reference kernel does,
                                      format_algos.py:508-515, 550, 595)                     */
 
+#define LF_SPMM_NO_SYNC 2         /* lf_spmm_hyb_f32_host only, may be OR-ed with the above: enqueue the
+                                     copies and the product and return; C is valid and the workspace free
+                                     again once the stream has been synchronised.  Lets a caller keep two
+                                     products in flight on two streams with two workspaces, so that the
+                                     copy of one result overlaps the upload of the next operands.        */
+
 int lf_version(void);
 const char* lf_last_error(void);
 
@@ -205,7 +211,8 @@ int lf_spmm_hyb_f32_bcast(const lf_hyb* A, const float* B /*[dev] K x N*/, int64
 /* Same product with every operand in HOST memory: the arrays of build_hyb_format as NumPy holds
  * them after the int32/float32 casts of format_algos.py:568-577, B and C row-major.  The call
  * copies the format and B into `device_workspace`, runs lf_spmm_hyb_f32 and copies C back, all on
- * `stream`, and synchronises.  It is what one call of bench_hyb_with_config does between
+ * `stream`, and synchronises (unless LF_SPMM_NO_SYNC is set; host buffers must then be pinned for
+ * the copies to run asynchronously).  It is what one call of bench_hyb_with_config does between
  * format_algos.py:546 and format_algos.py:595, without the run-time code generation. */
 size_t lf_spmm_hyb_f32_host_workspace_bytes(const lf_hyb* A_host, int32_t N);
 int lf_spmm_hyb_f32_host(const lf_hyb* A_host /* rows/cols/vals/zero_rows are [host] here */,

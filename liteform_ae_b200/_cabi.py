@@ -25,6 +25,7 @@ LF_OPT_BSR_COPY_ENGINE = 4
 LF_DTYPE_F32, LF_DTYPE_BF16, LF_DTYPE_F16 = 0, 1, 2
 LF_SPMM_OVERWRITE = 0
 LF_SPMM_ACCUMULATE = 1
+LF_SPMM_NO_SYNC = 2
 NUM_WIDTH_CLASSES = 11
 COLMASK_BINS = 2048
 STATIC_STATS_MAX_COLS = 1 << 20

@@ -49,5 +49,32 @@ __device__ __forceinline__ void split_tf32(float x, uint32_t& hi, uint32_t& lo) 
   lo = __float_as_uint(x - __uint_as_float(hi));
 }
 
+// Work item of a warp -> (group of block rows, feature tile).  Default order: tile index fastest;
+// with tile_major_groups > 0 all groups of tile 0 come first, then tile 1, ...  The common
+// shapes avoid the 64-bit division (a warp's whole job is a few thousand cycles; a software
+// division is a measurable part of that).
+__device__ __forceinline__ void split_work(int64_t work, int tiles, int64_t tile_major_groups, int64_t& grp, int& tile) {
+  if (tile_major_groups > 0) {
+    if ((work | tile_major_groups) >> 32) {
+      grp = work % tile_major_groups;
+      tile = (int)(work / tile_major_groups);
+    } else {
+      const uint32_t q = (uint32_t)work / (uint32_t)tile_major_groups;
+      tile = (int)q;
+      grp = (uint32_t)work - q * (uint32_t)tile_major_groups;
+    }
+  } else if (tiles == 1) {
+    grp = work;
+    tile = 0;
+  } else if (work >> 32) {
+    grp = work / tiles;
+    tile = (int)(work % tiles);
+  } else {
+    const uint32_t q = (uint32_t)work / (uint32_t)tiles;
+    grp = q;
+    tile = (int)((uint32_t)work - q * (uint32_t)tiles);
+  }
+}
+
 }  // namespace bsr8
 }  // namespace lf

@@ -74,8 +74,9 @@ bsr8_spmm_f32_kernel(const int64_t* __restrict__ indptr, const int32_t* __restri
   // (band x N) outgrow the L2; then (tile_major_groups > 0) all row groups of tile 0 run first,
   // then tile 1, ...: B is read from HBM once per tile and A once per tile.
   const int64_t work = (int64_t)blockIdx.x * kWarps + warp;
-  const int64_t grp = tile_major_groups > 0 ? work % tile_major_groups : work / tiles;
-  const int tile = (int)(tile_major_groups > 0 ? work / tile_major_groups : work % tiles);
+  int64_t grp;
+  int tile;
+  split_work(work, tiles, tile_major_groups, grp, tile);
   const int64_t I0 = block_row_begin + grp * rows_per_warp;
   if (I0 >= block_row_end || tile >= tiles) return;
   const int R = (int)min((int64_t)rows_per_warp, block_row_end - I0);
@@ -223,10 +224,13 @@ bsr8_spmm_16bit_kernel(const int64_t* __restrict__ indptr, const int32_t* __rest
   extern __shared__ __align__(128) uint8_t smem_raw[];
   const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3, warp = threadIdx.x >> 5;
   const int64_t work = (int64_t)blockIdx.x * kWarps + warp;
-  const int64_t I0 = block_row_begin + (work / tiles) * rows_per_warp;
+  int64_t grp;
+  int tile;
+  split_work(work, tiles, 0, grp, tile);
+  const int64_t I0 = block_row_begin + grp * rows_per_warp;
   if (I0 >= block_row_end) return;
   const int R = (int)min((int64_t)rows_per_warp, block_row_end - I0);
-  const int F = (int)(work % tiles) * 128;
+  const int F = tile * 128;
   uint8_t* ring = smem_raw + warp * (D * Cfg::kStage);
   const uint32_t ring_u32 = smem_u32(ring);
 

@@ -172,8 +172,9 @@ bsr8_spmm_f32_tma_kernel(const __grid_constant__ CUtensorMap mapB, const int64_t
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3, warp = threadIdx.x >> 5;
   const int64_t work = (int64_t)blockIdx.x * kWarps + warp;
-  const int64_t grp = tile_major_groups > 0 ? work % tile_major_groups : work / tiles;
-  const int tile = (int)(tile_major_groups > 0 ? work / tile_major_groups : work % tiles);
+  int64_t grp;
+  int tile;
+  split_work(work, tiles, tile_major_groups, grp, tile);
   const int64_t I0 = block_row_begin + grp * rows_per_warp;
   if (I0 >= block_row_end || tile >= tiles) return;
   const int R = (int)min((int64_t)rows_per_warp, block_row_end - I0);
@@ -300,10 +301,13 @@ bsr8_spmm_16bit_tma_kernel(const __grid_constant__ CUtensorMap mapB, const int64
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3, warp = threadIdx.x >> 5;
   const int64_t work = (int64_t)blockIdx.x * kWarps + warp;
-  const int64_t I0 = block_row_begin + (work / tiles) * rows_per_warp;
+  int64_t grp;
+  int tile;
+  split_work(work, tiles, 0, grp, tile);
+  const int64_t I0 = block_row_begin + grp * rows_per_warp;
   if (I0 >= block_row_end) return;
   const int R = (int)min((int64_t)rows_per_warp, block_row_end - I0);
-  const int F = (int)(work % tiles) * 128;
+  const int F = tile * 128;
   const int halves = min(2, (N - F + 63) / 64);
   const uint32_t row_bytes = (uint32_t)min(128, N - F) * 2;   // ROWS: bytes of one B row inside N
   Ring<D, kData> ring(smem_raw, warp, lane);

@@ -829,6 +829,8 @@ int lf_spmm_hyb_f32_host(const lf_hyb* A, const float* B, float* C, int32_t N, i
                          void* device_workspace, size_t workspace_bytes, void* stream) {
   if (int s = check_hyb(A)) return s;
   LF_REQUIRE(B && C && N >= 1 && device_workspace, "bad arguments");
+  LF_REQUIRE((flags & ~(LF_SPMM_ACCUMULATE | LF_SPMM_NO_SYNC)) == 0, "unknown flags %d", flags);
+  const bool accumulate = (flags & LF_SPMM_ACCUMULATE) != 0;
   size_t off[7];
   if (workspace_bytes < host_ws_layout(A, N, off)) return fail(LF_ERR_WORKSPACE_TOO_SMALL, "host-call workspace too small");
   cudaStream_t st = (cudaStream_t)stream;
@@ -843,7 +845,7 @@ int lf_spmm_hyb_f32_host(const lf_hyb* A, const float* B, float* C, int32_t N, i
   }
   if (A->num_zero_rows) LF_CUDA_CHECK(cudaMemcpyAsync(ws + off[3], A->zero_rows, (size_t)A->num_zero_rows * 4, cudaMemcpyHostToDevice, st));
   LF_CUDA_CHECK(cudaMemcpyAsync(ws + off[4], B, (size_t)A->num_cols * N * 4, cudaMemcpyHostToDevice, st));
-  if (flags == LF_SPMM_ACCUMULATE && c_bytes) LF_CUDA_CHECK(cudaMemcpyAsync(ws + off[5], C, c_bytes, cudaMemcpyHostToDevice, st));
+  if (accumulate && c_bytes) LF_CUDA_CHECK(cudaMemcpyAsync(ws + off[5], C, c_bytes, cudaMemcpyHostToDevice, st));
   lf_hyb dev = *A;
   dev.rows = (const int32_t*)(ws + off[0]);
   dev.cols = (const int32_t*)(ws + off[1]);
@@ -851,9 +853,11 @@ int lf_spmm_hyb_f32_host(const lf_hyb* A, const float* B, float* C, int32_t N, i
   dev.mask = nullptr;
   dev.hot_bits = nullptr;
   dev.zero_rows = (const int32_t*)(ws + off[3]);
-  if (int s = lf_spmm_hyb_f32(&dev, (const float*)(ws + off[4]), N, (float*)(ws + off[5]), N, N, flags, st)) return s;
+  if (int s = lf_spmm_hyb_f32(&dev, (const float*)(ws + off[4]), N, (float*)(ws + off[5]), N, N,
+                              accumulate ? LF_SPMM_ACCUMULATE : LF_SPMM_OVERWRITE, st))
+    return s;
   if (c_bytes) LF_CUDA_CHECK(cudaMemcpyAsync(C, ws + off[5], c_bytes, cudaMemcpyDeviceToHost, st));
-  LF_CUDA_CHECK(cudaStreamSynchronize(st));
+  if (!(flags & LF_SPMM_NO_SYNC)) LF_CUDA_CHECK(cudaStreamSynchronize(st));
   return LF_OK;
 }
 

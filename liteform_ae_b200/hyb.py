@@ -289,17 +289,20 @@ def spmm_csr(csr: DeviceCsr, B, out=None, row_range=None):
 
 
 def spmm_hyb_host(fmt_host_arrays, fmt: HybFormat, B_host: np.ndarray, C_host: np.ndarray, workspace,
-                  accumulate: bool = False):
+                  accumulate: bool = False, sync: bool = True, stream=None):
     """``lf_spmm_hyb_f32_host``: all operands in (ideally pinned) host memory; ``workspace`` is a
-    device byte tensor of at least ``host_workspace_bytes(fmt, N)`` bytes."""
+    device byte tensor of at least ``host_workspace_bytes(fmt, N)`` bytes.  ``sync=False`` only
+    enqueues on ``stream`` (a ``torch.cuda.Stream``, default: the current one): ``C_host`` is valid
+    and the workspace reusable after that stream has been synchronised."""
     torch = _torch()
     lib = _cabi.load()
     N = int(B_host.shape[1])
     s = fmt.c_struct(host_arrays=fmt_host_arrays)
+    flags = (_cabi.LF_SPMM_ACCUMULATE if accumulate else _cabi.LF_SPMM_OVERWRITE) | (0 if sync else _cabi.LF_SPMM_NO_SYNC)
     with torch.cuda.device(workspace.device):
-        check(lib.lf_spmm_hyb_f32_host(C.byref(s), np_ptr(B_host), np_ptr(C_host), N,
-                                       _cabi.LF_SPMM_ACCUMULATE if accumulate else _cabi.LF_SPMM_OVERWRITE,
-                                       workspace.data_ptr(), workspace.numel(), _stream_ptr(torch)))
+        st = _stream_ptr(torch) if stream is None else stream.cuda_stream
+        check(lib.lf_spmm_hyb_f32_host(C.byref(s), np_ptr(B_host), np_ptr(C_host), N, flags,
+                                       workspace.data_ptr(), workspace.numel(), st))
     return C_host
 
 

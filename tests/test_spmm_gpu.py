@@ -160,6 +160,38 @@ def test_host_memory_entry_point(cuda_device, N, pinned):
         Ch[:] = np.nan
 
 
+def test_host_memory_entry_point_two_calls_in_flight(cuda_device):
+    """LF_SPMM_NO_SYNC: two products enqueued on two streams with their own workspaces and result
+    buffers, then one synchronisation; both results must be complete and correct."""
+    import torch
+    N = 64
+    csr, d, fmt, B, Bd = _setup("zipf_16384_s0", 1, N, cuda_device)
+    r, c, m, v = fmt.to_nested_numpy(with_values=True)
+    ell_rows, row_off, slot_off, rows, cols, vals, zero_rows = hyb.HybFormat.host_layout(
+        fmt.bucket_widths, r, c, v, csr.shape[0])
+    host_fmt = hyb.HybFormat(csr.shape, (0, csr.shape[0]), fmt.bucket_widths, ell_rows, row_off, slot_off,
+                             None, None, None, None, zero_rows)
+    pin = lambda a: torch.from_numpy(np.ascontiguousarray(a)).pin_memory().numpy()
+    h = tuple(pin(a) for a in (rows, cols, vals, zero_rows))
+    Bs = [pin(B), pin(2.0 * B)]
+    Cs = [pin(np.full((csr.shape[0], N), np.nan, dtype=np.float32)) for _ in range(2)]
+    ws = [torch.empty(hyb.host_workspace_bytes(host_fmt, N), dtype=torch.uint8, device=cuda_device) for _ in range(2)]
+    streams = [torch.cuda.Stream(device=cuda_device) for _ in range(2)]
+    for rep in range(3):
+        for k in (0, 1):
+            hyb.spmm_hyb_host(h, host_fmt, Bs[k], Cs[k], ws[k], sync=False, stream=streams[k])
+    for st in streams:
+        st.synchronize()
+    want = _ref(csr, B)
+    np.testing.assert_allclose(Cs[0], want, rtol=RTOL, atol=ATOL)
+    np.testing.assert_allclose(Cs[1], 2.0 * want, rtol=RTOL, atol=2 * ATOL)
+    lib = __import__("liteform_ae_b200._cabi", fromlist=["load"]).load()
+    s = host_fmt.c_struct(host_arrays=h)
+    import ctypes
+    assert lib.lf_spmm_hyb_f32_host(ctypes.byref(s), Bs[0].ctypes.data, Cs[0].ctypes.data, N, 8,
+                                    ws[0].data_ptr(), ws[0].numel(), None) == -1     # unknown flag bits
+
+
 def test_full_size_linearity_and_checksum(cuda_device):
     """Benchmark-size power-law matrix: properties that need no CPU product of the same size.
     (1) column sums: 1^T (A B) == (1^T A) B in float64; (2) linearity in B; (3) sampled rows."""
