@@ -38,3 +38,19 @@ def test_workspace_queries_are_pure():
     b = lib.lf_hyb_build_workspace_bytes(0, 200000, 4, 20)
     assert 0 < a < b
     assert lib.lf_hyb_fill_scratch_bytes(1000) >= 8000
+
+
+def test_public_header_is_plain_c():
+    """The boundary is a C ABI: the header must compile as C99 on its own (a cgo / JNI / ctypes
+    binding generator sees nothing else)."""
+    import os
+    import shutil
+    import subprocess
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        import pytest
+        pytest.skip("no C compiler")
+    header = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "include", "liteform_b200.h")
+    res = subprocess.run([gcc, "-fsyntax-only", "-x", "c", "-std=c99", "-Wall", "-Werror", header],
+                         capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr
