@@ -94,8 +94,9 @@ int lf_hyb_stats(const int64_t* indptr /*[dev] M+1*/, const int32_t* indices /*[
  * buffer either: a call site inside a serving loop that promised the rest of the process a fixed
  * memory footprint, or a plugin whose host owns the allocator (a cudaMalloc there would also
  * synchronise the whole device in the middle of somebody else's work).  The per-column scratch
- * lives in a static device array inside the library instead, LF_STATIC_STATS_MAX_COLS * 4 bytes
- * (4 MiB) on every GPU that loads the library, until the process exits.
+ * lives in a static device array inside the library instead: LF_STATIC_STATS_MAX_COLS * 4 bytes
+ * plus the 128 KiB list of long row segments, 4 MiB + 128 KiB on every GPU that loads the
+ * library, until the process exits.
  *   - matrices with more than LF_STATIC_STATS_MAX_COLS columns are refused (LF_ERR_UNSUPPORTED);
  *   - the first call on a device looks up the array's device address (a one-time set-up that is
  *     not stream work), so make that first call before any stream capture begins;

@@ -44,13 +44,27 @@ __device__ __forceinline__ int64_t segment_end(const int32_t* __restrict__ indic
 // ------------------------------------------------------------------------------------------
 // statistics
 // ------------------------------------------------------------------------------------------
+// A (row, partition) segment of at least kLongSegMin entries is not marked by the warp that
+// found it (a 100 000-entry row would keep one warp busy for thousands of iterations while the
+// rest of the grid has long finished): the warp appends it to a list, and stats_long_kernel
+// spreads the listed segments over the whole grid in chunks.  Such a segment is always in the
+// widest class.  A full list is not an error: further segments are marked in place.
+struct LongSeg {
+  long long pos, end;
+};
+constexpr int kLongSegMin = 8192;
+constexpr int kLongSegCap = 8192;
+constexpr int kLongChunk = 2048;
+constexpr size_t kLongListBytes = 256 + sizeof(LongSeg) * kLongSegCap;   // counter slot + list
+static_assert(kLongSegMin > (1 << (kClasses - 1)), "a deferred segment must belong to the widest class");
+
 // One warp per matrix row.  For each column partition the row touches: degree -> width class,
 // three counters per (partition, class), and the class bit OR-ed into every touched column.
 __global__ void __launch_bounds__(256)
 stats_rows_kernel(const int64_t* __restrict__ indptr, const int32_t* __restrict__ indices,
                   int64_t num_rows, int64_t psz, int num_parts,
                   unsigned long long* __restrict__ class_stats, uint32_t* __restrict__ colmask,
-                  int use_smem) {
+                  int use_smem, unsigned int* __restrict__ long_count, LongSeg* __restrict__ long_list) {
   extern __shared__ unsigned long long s_stats[];
   const int n_stat = num_parts * kClasses * 3;
   if (use_smem) {
@@ -85,9 +99,21 @@ stats_rows_kernel(const int64_t* __restrict__ indptr, const int32_t* __restrict_
         atomicAdd(a + 2, 1ull);
       }
       const uint32_t bit = 1u << kc;
-      for (int64_t i = pos + lane; i < nxt; i += 32) {
-        const int32_t c = indices[i];
-        if (!(colmask[c] & bit)) atomicOr(colmask + c, bit);
+      bool deferred = false;
+      if (deg >= (uint32_t)kLongSegMin) {
+        unsigned int slot = 0;
+        if (lane == 0) slot = atomicAdd(long_count, 1u);
+        slot = __shfl_sync(0xffffffffu, slot, 0);
+        if (slot < (unsigned int)kLongSegCap) {
+          if (lane == 0) long_list[slot] = LongSeg{(long long)pos, (long long)nxt};
+          deferred = true;
+        }
+      }
+      if (!deferred) {
+        for (int64_t i = pos + lane; i < nxt; i += 32) {
+          const int32_t c = indices[i];
+          if (!(colmask[c] & bit)) atomicOr(colmask + c, bit);
+        }
       }
       pos = nxt;
     }
@@ -96,6 +122,33 @@ stats_rows_kernel(const int64_t* __restrict__ indptr, const int32_t* __restrict_
     __syncthreads();
     for (int i = threadIdx.x; i < n_stat; i += blockDim.x)
       if (s_stats[i]) atomicAdd(class_stats + i, s_stats[i]);
+  }
+}
+
+// Marks the columns of the listed long segments.  Chunks of kLongChunk entries are dealt round
+// robin over the thread blocks, continuing across segments, so that a handful of very long rows
+// still occupies the whole grid.
+__global__ void __launch_bounds__(256)
+stats_long_kernel(const int32_t* __restrict__ indices, const unsigned int* __restrict__ long_count,
+                  const LongSeg* __restrict__ long_list, uint32_t* __restrict__ colmask) {
+  const unsigned int listed = *long_count;
+  const int n = (int)(listed < (unsigned int)kLongSegCap ? listed : (unsigned int)kLongSegCap);
+  const uint32_t bit = 1u << (kClasses - 1);
+  long long dealt = 0;   // chunks of the segments before this one
+  for (int s = 0; s < n; ++s) {
+    const LongSeg seg = long_list[s];
+    const long long chunks = (seg.end - seg.pos + kLongChunk - 1) / kLongChunk;
+    long long first = ((long long)blockIdx.x - dealt) % (long long)gridDim.x;
+    if (first < 0) first += gridDim.x;
+    for (long long c = first; c < chunks; c += gridDim.x) {
+      const long long lo = seg.pos + c * kLongChunk;
+      const long long hi = lo + kLongChunk < seg.end ? lo + kLongChunk : seg.end;
+      for (long long i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+        const int32_t col = indices[i];
+        if (!(colmask[col] & bit)) atomicOr(colmask + col, bit);
+      }
+    }
+    dealt += chunks;
   }
 }
 
@@ -418,7 +471,7 @@ int lf_version(void) { return 100; }
 const char* lf_last_error(void) { return lf::error_buffer(); }
 
 size_t lf_hyb_stats_workspace_bytes(int64_t /*num_rows*/, int64_t num_cols, int32_t /*num_parts*/) {
-  return align_up(sizeof(uint32_t) * (size_t)(num_cols > 0 ? num_cols : 1), 256);
+  return align_up(sizeof(uint32_t) * (size_t)(num_cols > 0 ? num_cols : 1), 256) + kLongListBytes;
 }
 
 int lf_hyb_stats(const int64_t* indptr, const int32_t* indices, int64_t num_rows, int64_t num_cols,
@@ -432,8 +485,12 @@ int lf_hyb_stats(const int64_t* indptr, const int32_t* indices, int64_t num_rows
   cudaStream_t st = (cudaStream_t)stream;
   const int64_t psz = ceil_div64(num_cols, num_parts);
   uint32_t* colmask = (uint32_t*)workspace;
+  char* long_base = (char*)workspace + align_up(sizeof(uint32_t) * (size_t)num_cols, 256);
+  unsigned int* long_count = (unsigned int*)long_base;
+  LongSeg* long_list = (LongSeg*)(long_base + 256);
   const size_t n_stat = (size_t)num_parts * kClasses * 3;
   LF_CUDA_CHECK(cudaMemsetAsync(colmask, 0, sizeof(uint32_t) * num_cols, st));
+  LF_CUDA_CHECK(cudaMemsetAsync(long_count, 0, sizeof(unsigned int), st));
   LF_CUDA_CHECK(cudaMemsetAsync(class_stats, 0, sizeof(int64_t) * n_stat, st));
   LF_CUDA_CHECK(cudaMemsetAsync(colmask_hist, 0, sizeof(int64_t) * (size_t)num_parts * LF_COLMASK_BINS, st));
   if (num_rows > 0) {
@@ -442,7 +499,10 @@ int lf_hyb_stats(const int64_t* indptr, const int32_t* indices, int64_t num_rows
     const int64_t want = ceil_div64(num_rows, 8 * 4);  // 8 warps per block, ~4 rows per warp
     const int grid = (int)(want < 1 ? 1 : (want > 148 * 64 ? 148 * 64 : want));
     stats_rows_kernel<<<grid, 256, use_smem ? smem : 0, st>>>(
-        indptr, indices, num_rows, psz, num_parts, (unsigned long long*)class_stats, colmask, use_smem);
+        indptr, indices, num_rows, psz, num_parts, (unsigned long long*)class_stats, colmask, use_smem, long_count,
+        long_list);
+    LF_CUDA_CHECK(cudaGetLastError());
+    stats_long_kernel<<<148 * 4, 256, 0, st>>>(indices, long_count, long_list, colmask);
     LF_CUDA_CHECK(cudaGetLastError());
   }
   {
@@ -459,7 +519,8 @@ int lf_hyb_stats(const int64_t* indptr, const int32_t* indices, int64_t num_rows
 // Scratch of lf_hyb_stats_static: the per-column class-mask array, resident in every device
 // that loads this library until the process exits.
 #define LF_STATIC_STATS_MAX_COLS_IMPL (1 << 20)
-static __device__ __align__(256) uint32_t g_static_colmask[LF_STATIC_STATS_MAX_COLS_IMPL];
+constexpr size_t kStaticScratchBytes = sizeof(uint32_t) * LF_STATIC_STATS_MAX_COLS_IMPL + kLongListBytes;
+static __device__ __align__(256) uint32_t g_static_colmask[kStaticScratchBytes / sizeof(uint32_t)];
 static_assert(LF_STATIC_STATS_MAX_COLS_IMPL == LF_STATIC_STATS_MAX_COLS, "header and implementation disagree");
 
 // In host code `g_static_colmask` is only a handle of the symbol, not an address a kernel can
@@ -499,7 +560,7 @@ int lf_hyb_stats_static(const int64_t* indptr, const int32_t* indices, int64_t n
   if (!scratch) return status;
   // same launches as lf_hyb_stats, which clears the part of the scratch it is about to use
   return lf_hyb_stats(indptr, indices, num_rows, num_cols, num_parts, class_stats, colmask_hist, scratch,
-                      sizeof(uint32_t) * (size_t)LF_STATIC_STATS_MAX_COLS, stream);
+                      kStaticScratchBytes, stream);
 }
 
 int64_t lf_row_stats_blocks(int64_t row_begin, int64_t row_end) {
