@@ -78,6 +78,33 @@ stats_rows_kernel(const int64_t* __restrict__ indptr, const int32_t* __restrict_
   for (int64_t r = warp; r < num_rows; r += n_warps) {
     const int64_t s = indptr[r], e = indptr[r + 1];
     int64_t pos = s;
+    if (num_parts > 1 && e - s <= 32) {
+      // short row, several partitions: one entry per lane.  A lane whose partition differs from
+      // its left neighbour's heads a segment; segment lengths come from the ballot of heads, so
+      // all segments of the row are counted and marked at once instead of one after the other.
+      const int n = (int)(e - s);
+      const bool on = lane < n;
+      const int32_t c = on ? indices[s + lane] : 0;
+      const int p = on ? (int)((uint32_t)c / (uint32_t)psz) : -1;
+      const int left = __shfl_up_sync(0xffffffffu, p, 1);
+      const bool head = on && (lane == 0 || p != left);
+      const unsigned heads = __ballot_sync(0xffffffffu, head);
+      int kc = 0;
+      if (head) {
+        const unsigned later = lane == 31 ? 0u : heads >> (lane + 1);
+        const uint32_t deg = later ? (uint32_t)__ffs(later) : (uint32_t)(n - lane);
+        kc = ceil_log2_u32(deg);   // deg <= 32: never beyond the widest class
+        unsigned long long* a = acc + (p * kClasses + kc) * 3;
+        atomicAdd(a + 0, 1ull);
+        atomicAdd(a + 1, (unsigned long long)deg);
+        atomicAdd(a + 2, 1ull);
+      }
+      const unsigned upto = heads & (0xffffffffu >> (31 - lane));   // heads at or before this lane
+      const int my_head = on ? 31 - __clz(upto) : 0;
+      const uint32_t bit = 1u << __shfl_sync(0xffffffffu, kc, my_head);
+      if (on && !(colmask[c] & bit)) atomicOr(colmask + c, bit);
+      pos = e;
+    }
     while (pos < e) {
       int64_t nxt;
       int p;
