@@ -75,16 +75,45 @@ stats_rows_kernel(const int64_t* __restrict__ indptr, const int32_t* __restrict_
   const int lane = threadIdx.x & 31;
   const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int64_t n_warps = (int64_t)gridDim.x * (blockDim.x >> 5);
-  for (int64_t r = warp; r < num_rows; r += n_warps) {
-    const int64_t s = indptr[r], e = indptr[r + 1];
+  // The chain row pointer -> column -> class mask of the column is three dependent loads; the
+  // row pointer and the first 32 columns of the warp's NEXT row are fetched before the current
+  // row is worked on, so that two chains are in flight per warp.
+  int64_t r = warp, s = 0, e = 0;
+  int32_t c_first = 0;
+  if (r < num_rows) {
+    s = indptr[r];
+    e = indptr[r + 1];
+    c_first = s + lane < e ? indices[s + lane] : 0;
+  }
+  while (r < num_rows) {
+    const int64_t r_next = r + n_warps;
+    int64_t s_next = 0, e_next = 0;
+    int32_t c_next = 0;
+    if (r_next < num_rows) {
+      s_next = indptr[r_next];
+      e_next = indptr[r_next + 1];
+      c_next = s_next + lane < e_next ? indices[s_next + lane] : 0;
+    }
     int64_t pos = s;
-    if (num_parts > 1 && e - s <= 32) {
+    if (num_parts == 1 && e - s <= 32 && e > s) {
+      const uint32_t deg = (uint32_t)(e - s);
+      const int kc = ceil_log2_u32(deg);
+      if (lane == 0) {
+        unsigned long long* a = acc + kc * 3;
+        atomicAdd(a + 0, 1ull);
+        atomicAdd(a + 1, (unsigned long long)deg);
+        atomicAdd(a + 2, 1ull);
+      }
+      const uint32_t bit = 1u << kc;
+      if (lane < (int)deg && !(colmask[c_first] & bit)) atomicOr(colmask + c_first, bit);
+      pos = e;
+    } else if (num_parts > 1 && e - s <= 32) {
       // short row, several partitions: one entry per lane.  A lane whose partition differs from
       // its left neighbour's heads a segment; segment lengths come from the ballot of heads, so
       // all segments of the row are counted and marked at once instead of one after the other.
       const int n = (int)(e - s);
       const bool on = lane < n;
-      const int32_t c = on ? indices[s + lane] : 0;
+      const int32_t c = on ? c_first : 0;
       const int p = on ? (int)((uint32_t)c / (uint32_t)psz) : -1;
       const int left = __shfl_up_sync(0xffffffffu, p, 1);
       const bool head = on && (lane == 0 || p != left);
@@ -144,6 +173,10 @@ stats_rows_kernel(const int64_t* __restrict__ indptr, const int32_t* __restrict_
       }
       pos = nxt;
     }
+    r = r_next;
+    s = s_next;
+    e = e_next;
+    c_first = c_next;
   }
   if (use_smem) {
     __syncthreads();
@@ -365,36 +398,64 @@ hyb_fill_rows_kernel(const int64_t* __restrict__ indptr, const int32_t* __restri
 }
 
 // One thread per slot of the cols/vals/mask arenas (alignment gaps included, they get zeros).
+// A slot costs three dependent rounds of loads (bucket tables, the ELL row's source range, the
+// entry itself); a thread therefore works on kFillUnroll slots at once, a grid stride apart, so
+// that their rounds overlap.
+constexpr int kFillUnroll = 4;
 __global__ void __launch_bounds__(256)
 hyb_fill_slots_kernel(const int32_t* __restrict__ indices, const float* __restrict__ data,
                       BuildMeta meta, int nb, const int32_t* __restrict__ src_start,
                       const int32_t* __restrict__ src_len, int32_t* __restrict__ cols,
                       float* __restrict__ vals, uint8_t* __restrict__ mask, int64_t total_slots) {
-  for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total_slots;
-       t += (int64_t)gridDim.x * blockDim.x) {
-    int lo = 0, hi = nb;  // last bucket i with slot_off[i] <= t
-    while (hi - lo > 1) {
-      const int mid = (lo + hi) >> 1;
-      if (meta.slot_off[mid] <= t) lo = mid; else hi = mid;
-    }
-    const int w = meta.widths[lo];
-    const int64_t local = t - meta.slot_off[lo];
-    int32_t c = 0;
-    float v = 0.f;
-    uint8_t m = 0;
-    if (local < meta.ell_rows[lo] * w) {
-      const int64_t er = meta.row_off[lo] + local / w;
-      const int j = (int)(local % w);
-      if (j < src_len[er]) {
-        const int64_t src = (int64_t)src_start[er] + j;
-        c = indices[src];
-        v = data ? data[src] : 1.f;
-        m = 1;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t t0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t0 < total_slots; t0 += stride * kFillUnroll) {
+    int64_t er[kFillUnroll];
+    int j[kFillUnroll];
+    bool in_row[kFillUnroll];
+#pragma unroll
+    for (int u = 0; u < kFillUnroll; ++u) {
+      const int64_t t = t0 + u * stride;
+      in_row[u] = false;
+      er[u] = 0;
+      j[u] = 0;
+      if (t < total_slots) {
+        int lo = 0, hi = nb;  // last bucket i with slot_off[i] <= t
+        while (hi - lo > 1) {
+          const int mid = (lo + hi) >> 1;
+          if (meta.slot_off[mid] <= t) lo = mid; else hi = mid;
+        }
+        const int w = meta.widths[lo];
+        const int shift = 31 - __clz(w);   // widths are powers of two
+        const int64_t local = t - meta.slot_off[lo];
+        if (local < (meta.ell_rows[lo] << shift)) {
+          in_row[u] = true;
+          er[u] = meta.row_off[lo] + (local >> shift);
+          j[u] = (int)(local & (w - 1));
+        }
       }
     }
-    cols[t] = c;
-    vals[t] = v;
-    if (mask) mask[t] = m;
+    int64_t src[kFillUnroll];
+#pragma unroll
+    for (int u = 0; u < kFillUnroll; ++u) {
+      src[u] = -1;
+      if (in_row[u] && j[u] < src_len[er[u]]) src[u] = (int64_t)src_start[er[u]] + j[u];
+    }
+    int32_t c[kFillUnroll];
+    float v[kFillUnroll];
+#pragma unroll
+    for (int u = 0; u < kFillUnroll; ++u) {
+      c[u] = src[u] >= 0 ? indices[src[u]] : 0;
+      v[u] = src[u] >= 0 ? (data ? data[src[u]] : 1.f) : 0.f;
+    }
+#pragma unroll
+    for (int u = 0; u < kFillUnroll; ++u) {
+      const int64_t t = t0 + u * stride;
+      if (t < total_slots) {
+        cols[t] = c[u];
+        vals[t] = v[u];
+        if (mask) mask[t] = src[u] >= 0 ? 1 : 0;
+      }
+    }
   }
 }
 
