@@ -198,6 +198,7 @@ class HybProblem:
         from liteform_ae_b200 import hyb, width_search
         from liteform_ae_b200.sharding import my_range
         self.hyb, self.torch, self.dev = hyb, torch, dev
+        self.rank, self.world = rank, world
         desc, gen, full_rows, N0 = WORKLOADS[args.workload]
         self.N = N = args.feat or N0
         self.P = P = args.parts
@@ -258,11 +259,21 @@ class HybProblem:
         torch, hyb, fmt = self.torch, self.hyb, self.fmt
         if self.eb != 4:
             raise RuntimeError("the host-memory entry point is float32 only")
+        pin = lambda a: torch.from_numpy(a).pin_memory().numpy()
+        if self.world > 1:
+            # several ranks: each uploads its format shard and 1/world of B's rows, an all-gather over
+            # NVLink completes B on every GPU (sharding.HostShardedSpmm)
+            from liteform_ae_b200.sharding import HostShardedSpmm
+            self.hs = HostShardedSpmm(fmt, self.N, self.rank, self.world, slots=2)
+            self.B_rows = torch.from_numpy(self.B_host[self.hs.first:self.hs.last]).pin_memory()
+            self.Cp = [torch.empty((self.r1 - self.r0, self.N), dtype=torch.float32).pin_memory() for _ in range(2)]
+            return (self.hs.h2d_bytes, self.hs.d2h_bytes,
+                    "sharding.HostShardedSpmm: pinned host format shard + 1/world of B in, all-gather of B over "
+                    "NVLink, lf_spmm_hyb_f32, C rows out (bytes are per rank)")
         r_nd, c_nd, _, v_nd = fmt.to_nested_numpy(with_values=True)
         ell_rows, row_off, slot_off, h_rows, h_cols, h_vals, h_zero = hyb.HybFormat.host_layout(
             fmt.bucket_widths, r_nd, c_nd, v_nd, self.M, (self.r0, self.r1))
         del r_nd, c_nd, v_nd
-        pin = lambda a: torch.from_numpy(a).pin_memory().numpy()
         self.h = tuple(pin(a) for a in (h_rows, h_cols, h_vals, h_zero))
         self.Bp = pin(self.B_host)
         self.host_fmt = hyb.HybFormat((self.M, self.K), (self.r0, self.r1), fmt.bucket_widths, ell_rows, row_off,
@@ -276,15 +287,23 @@ class HybProblem:
         return h2d, self.Cp[0].nbytes, "lf_spmm_hyb_f32_host (pinned host format + B in, C out, per rank)"
 
     def e2e_step(self, slot=0, sync=True):
+        if self.world > 1:
+            self.hs.enqueue(self.B_rows, self.Cp[slot], slot)
+            if sync:
+                self.hs.slots[slot]["stream"].synchronize()
+            return
         self.hyb.spmm_hyb_host(self.h, self.host_fmt, self.Bp, self.Cp[slot], self.ws[slot], sync=sync,
                                stream=self.e2e_streams[slot])
 
     def e2e_sync(self):
+        if self.world > 1:
+            self.hs.synchronize()
+            return
         for st in self.e2e_streams:
             st.synchronize()
 
     def e2e_result(self, slot=0):
-        return self.Cp[slot]
+        return self.Cp[slot].numpy() if self.world > 1 else self.Cp[slot]
 
     def cpu_matrix(self):
         return self.csr.toscipy()

@@ -97,3 +97,67 @@ class ShardedSpmm:
         hyb.spmm_hyb_bcast(self.fmt, B, self._dest_ptrs, self.C_full.stride(0))
         self._symm.barrier()                      # every rank's rows have landed everywhere
         return self.C_full
+
+
+def b_chunk(num_cols: int, world: int, rank: int) -> Tuple[int, int, int]:
+    """Rows of B a rank uploads when B starts in host memory: ``(first, last, chunk)`` with equal
+    chunks of ``ceil(K / world)`` rows (the last one may be short)."""
+    chunk = -(-int(num_cols) // int(world))
+    first = min(rank * chunk, num_cols)
+    return first, min(first + chunk, num_cols), chunk
+
+
+class HostShardedSpmm:
+    """Row-sharded product whose operands start in HOST memory and whose result returns there.
+
+    Every rank needs all of B.  Uploading it once per rank sends ``world`` copies over the
+    host links, which the GPUs of a node share; here each rank uploads only its ``1 / world`` of
+    B's rows (``b_chunk``) next to its shard of the format, and one all-gather over NVLink
+    completes B on every GPU -- the one exchange step of this path.  Then the device product runs
+    and the rank's rows of C go back to the host.  ``slots`` independent sets of device buffers
+    and streams let a caller keep several products in flight (the result of one crosses the bus
+    while the operands of the next come in); the collectives are issued in call order, so all
+    ranks must enqueue the same sequence of slots.
+    """
+
+    def __init__(self, fmt, N: int, rank: int, world: int, group=None, slots: int = 2):
+        import copy
+        import torch
+        self.torch, self.rank, self.world, self.group, self.N = torch, rank, world, group, int(N)
+        dev = fmt.device
+        self.K = fmt.shape[1]
+        self.first, self.last, self.chunk = b_chunk(self.K, world, rank)
+        pin = lambda t: t.cpu().pin_memory()
+        names = ("rows", "cols", "vals") + (("zero_rows",) if fmt.num_zero_rows else ())
+        self.h_fmt = {n: pin(getattr(fmt, n)) for n in names}
+        self.slots = []
+        for _ in range(slots):
+            f = copy.copy(fmt)
+            f.mask, f.hot_bits = None, None
+            for n in names:
+                setattr(f, n, torch.empty_like(getattr(fmt, n)))
+            self.slots.append({
+                "fmt": f, "stream": torch.cuda.Stream(device=dev),
+                "B_chunk": torch.empty((self.chunk, self.N), dtype=torch.float32, device=dev),
+                "B_full": torch.empty((self.chunk * world, self.N), dtype=torch.float32, device=dev),
+                "C": torch.empty((fmt.row_end - fmt.row_begin, self.N), dtype=torch.float32, device=dev)})
+        self.h2d_bytes = sum(t.numel() * t.element_size() for t in self.h_fmt.values()) + (self.last - self.first) * self.N * 4
+        self.d2h_bytes = (fmt.row_end - fmt.row_begin) * self.N * 4
+
+    def enqueue(self, B_rows_host, C_host, slot: int = 0):
+        """``B_rows_host``: pinned float32 tensor holding THIS rank's rows ``first:last`` of B;
+        ``C_host``: pinned float32 tensor for this rank's rows of C.  Returns after enqueueing."""
+        import torch.distributed as dist
+        from . import hyb
+        torch, s = self.torch, self.slots[slot]
+        with torch.cuda.stream(s["stream"]):
+            for n, h in self.h_fmt.items():
+                getattr(s["fmt"], n).copy_(h, non_blocking=True)
+            s["B_chunk"][:self.last - self.first].copy_(B_rows_host, non_blocking=True)
+            dist.all_gather_into_tensor(s["B_full"], s["B_chunk"], group=self.group)
+            hyb.spmm_hyb(s["fmt"], s["B_full"][:self.K], out=s["C"])
+            C_host.copy_(s["C"], non_blocking=True)
+
+    def synchronize(self):
+        for s in self.slots:
+            s["stream"].synchronize()

@@ -66,3 +66,15 @@ def test_all_gather_rows_gloo(world):
         assert p.exitcode == 0
     assert sorted(r[0] for r in results) == list(range(world))
     assert all(r[1] for r in results), results
+
+
+def test_b_chunks_cover_all_rows_once():
+    from liteform_ae_b200.sharding import b_chunk
+    for K, world in ((1 << 20, 8), (1000, 3), (7, 8), (1, 1), (4096, 5)):
+        spans = [b_chunk(K, world, r) for r in range(world)]
+        assert all(c == spans[0][2] for _, _, c in spans) and spans[0][2] * world >= K
+        covered = np.zeros(K, dtype=int)
+        for r, (a, b, c) in enumerate(spans):
+            assert 0 <= a <= b <= K and b - a <= c and a == min(r * c, K)
+            covered[a:b] += 1
+        assert (covered == 1).all()
