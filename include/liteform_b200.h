@@ -65,6 +65,10 @@ const char* lf_last_error(void);
 #define LF_OPT_BSR_COPY_ENGINE 4        /* how the 8x8 block kernels fill shared memory: 0 automatic, 1 per-lane
                                           cp.async, 2 tiled bulk copies through a tensor map, 3 one bulk copy per row
                                           of B (2 and 3 complete on mbarriers) */
+#define LF_OPT_BSR_TILE_ORDER 5         /* float32 block kernel with several 128-feature tiles: 0 automatic (2 from
+                                          four tiles on), 1 the tiles of a block row run together (A read once),
+                                          2 one tile after the other over all rows (the B rows of one tile stay
+                                          in the L2) */
 int lf_set_option(int32_t option, int32_t value);
 
 /* ---------------------------------------------------------------------------------------------

@@ -22,6 +22,7 @@ LF_OPT_SPMM_SLOTS_PER_GROUP = 1
 LF_OPT_SPMM_CACHE_POLICY = 2
 LF_OPT_SPMM_MIN_BLOCKS = 3
 LF_OPT_BSR_COPY_ENGINE = 4
+LF_OPT_BSR_TILE_ORDER = 5
 LF_DTYPE_F32, LF_DTYPE_BF16, LF_DTYPE_F16 = 0, 1, 2
 LF_SPMM_OVERWRITE = 0
 LF_SPMM_ACCUMULATE = 1

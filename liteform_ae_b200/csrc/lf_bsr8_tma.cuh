@@ -9,6 +9,7 @@
 namespace lf {
 
 extern int g_bsr_copy_engine;   // LF_OPT_BSR_COPY_ENGINE
+extern int g_bsr_tile_order;    // LF_OPT_BSR_TILE_ORDER
 
 int bsr8_f32_tma_launch(bool rows, const int64_t* indptr, const int32_t* indices, const float* blocks, int64_t r0, int64_t r1,
                         const float* B, int64_t ldb, float* C, int64_t ldc, int N, int stages, int rows_per_warp,

@@ -344,7 +344,6 @@ bsr8_spmm_16bit_kernel(const int64_t* __restrict__ indptr, const int32_t* __rest
 // tuning state of the block kernels (lf_bsr_set_tuning)
 int g_bsr_feat_units = 0;   // 0 = automatic, 1 or 2 = features per warp / 64 of the float32 kernel
 int g_bsr_stages = 0;       // 0 = automatic, 3 or 4 = depth of the per-warp copy ring
-int g_bsr_tile_major = -1;  // -1 = automatic (float32, more than three feature tiles), 0 = never, 1 = always
 int g_bsr_rows_per_warp = 0;  // 0 = automatic (4 float32, 8 16-bit); block rows one warp streams through, 1..31
 
 int check_common(const void* indptr, const void* indices, const void* blocks, int64_t r0, int64_t r1,
@@ -372,6 +371,9 @@ int set_smem(K kernel, int bytes) {
 // 0 = automatic, 1 = per-lane cp.async, 2 = tiled bulk copies, 3 = one bulk copy per B row
 // (LF_OPT_BSR_COPY_ENGINE)
 int g_bsr_copy_engine = 0;
+// 0 = automatic (one after the other from four feature tiles on), 1 = the feature tiles of a block
+// row together, 2 = one tile after the other (LF_OPT_BSR_TILE_ORDER)
+int g_bsr_tile_order = 0;
 
 namespace {
 int copy_engine() {
@@ -396,8 +398,6 @@ int lf_bsr_set_tuning(int32_t feat_units, int32_t stages, int32_t rows_per_warp)
   g_bsr_feat_units = feat_units;
   g_bsr_stages = stages;
   g_bsr_rows_per_warp = rows_per_warp;
-  const char* e = getenv("LF_BSR_TILE_MAJOR");
-  if (e) g_bsr_tile_major = atoi(e) > 0 ? 1 : (atoi(e) == 0 ? 0 : -1);
   return LF_OK;
 }
 
@@ -423,7 +423,7 @@ int lf_spmm_bsr8_f32(const int64_t* indptr, const int32_t* indices, const float*
   const int64_t grid = ceil_div64(groups * tiles, kWarps);
   // measured on the banded benchmark matrix: no difference up to three tiles (N <= 384), 10 %
   // faster with four (N = 512), where the B rows of all tiles together no longer fit the L2
-  const int64_t tile_major = (g_bsr_tile_major < 0 ? tiles > 3 : g_bsr_tile_major > 0) ? groups : 0;
+  const int64_t tile_major = (g_bsr_tile_order == 0 ? tiles > 3 : g_bsr_tile_order == 2) ? groups : 0;
   LF_REQUIRE(grid < (1ll << 31), "too many thread blocks");
   if (T == 2 && copy_engine() > 1)
     return bsr8_f32_tma_launch(copy_engine() == 3, indptr, indices, blocks, block_row_begin, block_row_end, B, ldb, C, ldc, N, D, rpw,

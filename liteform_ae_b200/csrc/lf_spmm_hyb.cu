@@ -666,6 +666,10 @@ int lf_set_option(int32_t option, int32_t value) {
       LF_REQUIRE(value >= 0 && value <= 3, "copy engine %d out of range", value);
       g_bsr_copy_engine = value;
       return LF_OK;
+    case LF_OPT_BSR_TILE_ORDER:
+      LF_REQUIRE(value >= 0 && value <= 2, "tile order %d out of range", value);
+      g_bsr_tile_order = value;
+      return LF_OK;
     default:
       return fail(LF_ERR_INVALID_ARGUMENT, "unknown option %d", option);
   }

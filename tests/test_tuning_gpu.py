@@ -19,6 +19,7 @@ def restore_defaults():
     lib.lf_set_option(_cabi.LF_OPT_SPMM_SLOTS_PER_GROUP, 0)
     lib.lf_bsr_set_tuning(0, 0, 0)
     lib.lf_set_option(_cabi.LF_OPT_BSR_COPY_ENGINE, 0)
+    lib.lf_set_option(_cabi.LF_OPT_BSR_TILE_ORDER, 0)
 
 
 def test_every_spmm_variant_gives_the_same_product(cuda_device, restore_defaults):
@@ -68,5 +69,11 @@ def test_every_block_kernel_variant_gives_the_same_product(cuda_device, restore_
             np.testing.assert_allclose(bsr.spmm_bsr8(a32, Bd).cpu().numpy(), want, rtol=1e-5, atol=1e-4)
             np.testing.assert_allclose(bsr.spmm_bsr8(a16, B16).cpu().numpy(), want16, rtol=1e-5, atol=1e-4)
         assert lib.lf_bsr_copy_status(None) == 0   # no warp gave up waiting for a bulk copy
+        for engine, order in itertools.product((1, 2, 3), (0, 1, 2)):
+            assert lib.lf_set_option(_cabi.LF_OPT_BSR_COPY_ENGINE, engine) == 0
+            assert lib.lf_set_option(_cabi.LF_OPT_BSR_TILE_ORDER, order) == 0
+            assert lib.lf_bsr_set_tuning(2, 0, 0) == 0
+            np.testing.assert_allclose(bsr.spmm_bsr8(a32, Bd).cpu().numpy(), want, rtol=1e-5, atol=1e-4)
+        assert lib.lf_set_option(_cabi.LF_OPT_BSR_TILE_ORDER, 0) == 0
     assert lib.lf_bsr_set_tuning(3, 0, 0) == _cabi.LF_ERR_INVALID_ARGUMENT
     assert lib.lf_set_option(_cabi.LF_OPT_BSR_COPY_ENGINE, 4) == _cabi.LF_ERR_INVALID_ARGUMENT
