@@ -17,8 +17,12 @@ def one_rank_group(cuda_device):
     import torch.distributed as dist
     if dist.is_initialized():
         pytest.skip("a process group is already active in this process")
+    import socket
+    with socket.socket() as sock:                      # a port nobody uses right now
+        sock.bind(("127.0.0.1", 0))
+        port = sock.getsockname()[1]
     torch.cuda.set_device(cuda_device)
-    dist.init_process_group("nccl", init_method="tcp://127.0.0.1:29733", rank=0, world_size=1)
+    dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=0, world_size=1)
     yield
     dist.destroy_process_group()
 
