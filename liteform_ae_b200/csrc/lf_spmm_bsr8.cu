@@ -197,6 +197,122 @@ bsr8_spmm_f32_kernel(const int64_t* __restrict__ indptr, const int32_t* __restri
 }
 
 // ---------------------------------------------------------------------------------------------
+// float32, narrow tile: 32 features per warp, for N <= 32.  The 64-feature unit above would leave
+// the upper half of every MMA (rows m = g + 8) on padding; here both halves carry features:
+//   MMA tile j (j = 0, 1): m = g <-> feature F + 4g + j,  m = g + 8 <-> feature F + 4g + 2 + j
+// so one 128-bit shared load per B row feeds both tiles, and a block costs 6 MMAs instead of 12.
+// A stage is 8 rows of 128 bytes (chunk c of row r at c ^ r) plus the block: 1280 bytes, which
+// lets the ring be twice as deep at three thread blocks per SM -- with so little work per block
+// the kernel lives on the number of blocks in flight.
+// ---------------------------------------------------------------------------------------------
+template <int D>
+struct F32NarrowCfg {
+  static constexpr int kStage = 8 * 128 + 256;
+  static constexpr int kSmem = kWarps * D * kStage;
+};
+
+template <int D, int MINB>
+__global__ void __launch_bounds__(kThreadsBsr, MINB)
+bsr8_spmm_f32_narrow_kernel(const int64_t* __restrict__ indptr, const int32_t* __restrict__ indices,
+                            const float* __restrict__ blocks, int64_t block_row_begin, int64_t block_row_end,
+                            const float* __restrict__ B, int ldb, float* __restrict__ C, int64_t ldc, int N,
+                            int tiles, int rows_per_warp) {
+  using Cfg = F32NarrowCfg<D>;
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3, warp = threadIdx.x >> 5;
+  const int64_t work = (int64_t)blockIdx.x * kWarps + warp;
+  int64_t grp;
+  int tile;
+  split_work(work, tiles, 0, grp, tile);
+  const int64_t I0 = block_row_begin + grp * rows_per_warp;
+  if (I0 >= block_row_end) return;
+  const int R = (int)min((int64_t)rows_per_warp, block_row_end - I0);
+  const int F = tile * 32;
+  uint8_t* ring = smem_raw + warp * (D * Cfg::kStage);
+  const uint32_t ring_u32 = smem_u32(ring);
+
+  const int64_t my_ptr = indptr[I0 + min(lane, R)];
+  const int64_t stream_end = __shfl_sync(0xffffffffu, my_ptr, R);
+  auto row_start = [&](int r) { return __shfl_sync(0xffffffffu, my_ptr, r); };
+
+  int my_idx = 0;
+  int64_t win = -(int64_t)64;
+  int64_t ib = row_start(0);
+  int slot_in = 0;
+  const int cc = lane & 7, rr = lane >> 3;                // chunk of the row, row within a group of four
+  const int ok = (F + 4 * cc < N) ? 16 : 0;
+
+  auto issue_next = [&]() {
+    if (ib < stream_end) {
+      const int64_t b = ib;
+      if (b >= win + 32) {
+        win = b;
+        my_idx = (b + lane < stream_end) ? indices[b + lane] : 0;
+      }
+      const int J = __shfl_sync(0xffffffffu, my_idx, (int)(b - win));
+      const uint32_t dst = ring_u32 + slot_in * Cfg::kStage;
+      const float* src = B + (int64_t)J * 8 * ldb + F + (ok ? 4 * cc : 0);
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int r = 4 * i + rr;
+        cp_async16(dst + r * 128 + ((cc ^ r) << 4), src + (int64_t)r * ldb, ok);
+      }
+      if (lane < 16) cp_async16(dst + 8 * 128 + lane * 16, blocks + b * 64 + lane * 4, 16);
+      ib = b + 1;
+      slot_in = slot_in + 1 == D ? 0 : slot_in + 1;
+    }
+    cp_async_commit();
+  };
+
+#pragma unroll
+  for (int s = 0; s < D - 1; ++s) issue_next();
+
+  int slot_out = 0;
+  for (int r = 0; r < R; ++r) {
+    float acc[2][4];
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
+
+    const int64_t be = row_start(r + 1);
+    for (int64_t b = row_start(r); b < be; ++b) {
+      cp_async_wait<D - 2>();
+      __syncwarp();
+      issue_next();
+
+      const uint8_t* st = ring + slot_out * Cfg::kStage;
+      slot_out = slot_out + 1 == D ? 0 : slot_out + 1;
+      const float2 av = *reinterpret_cast<const float2*>(st + 8 * 128 + (g * 8 + 2 * t) * 4);
+      uint32_t b0h, b0l, b1h, b1l;
+      split_tf32(av.x, b0h, b0l);
+      split_tf32(av.y, b1h, b1l);
+      const float4 x = *reinterpret_cast<const float4*>(st + (2 * t) * 128 + (((g ^ (2 * t)) & 7) << 4));          // k = t
+      const float4 y = *reinterpret_cast<const float4*>(st + (2 * t + 1) * 128 + (((g ^ (2 * t + 1)) & 7) << 4));  // k = t+4
+      const float a_f[2][4] = {{x.x, x.z, y.x, y.z}, {x.y, x.w, y.y, y.w}};
+      uint32_t ah[2][4], al[2][4];
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) split_tf32(a_f[j][i], ah[j][i], al[j][i]);
+#pragma unroll
+      for (int j = 0; j < 2; ++j) mma_tf32(acc[j], al[j], b0h, b1h);
+#pragma unroll
+      for (int j = 0; j < 2; ++j) mma_tf32(acc[j], ah[j], b0l, b1l);
+#pragma unroll
+      for (int j = 0; j < 2; ++j) mma_tf32(acc[j], ah[j], b0h, b1h);
+    }
+
+    if (F + 4 * g < N) {
+      float* c0 = C + ((I0 + r - block_row_begin) * 8 + 2 * t) * ldc + F + 4 * g;
+      __stcs(reinterpret_cast<float4*>(c0), make_float4(acc[0][0], acc[1][0], acc[0][2], acc[1][2]));
+      __stcs(reinterpret_cast<float4*>(c0 + ldc), make_float4(acc[0][1], acc[1][1], acc[0][3], acc[1][3]));
+    }
+  }
+  cp_async_wait<0>();
+}
+
+// ---------------------------------------------------------------------------------------------
 // 16-bit in (bf16 or fp16) / float32 out.  One warp = one block row x one tile of 128 features;
 // two blocks per m16n8k16 MMA.  Index maps:
 //   k-slots 2t, 2t+1   <-> block 0, columns 2t, 2t+1      k-slots 2t+8, 2t+9 <-> block 1, same columns
@@ -425,6 +541,16 @@ int lf_spmm_bsr8_f32(const int64_t* indptr, const int32_t* indices, const float*
   // faster with four (N = 512), where the B rows of all tiles together no longer fit the L2
   const int64_t tile_major = (g_bsr_tile_order == 0 ? tiles > 3 : g_bsr_tile_order == 2) ? groups : 0;
   LF_REQUIRE(grid < (1ll << 31), "too many thread blocks");
+  if (N <= 32 && !g_bsr_feat_units) {   // narrow tile: both halves of every MMA carry features
+    const int ntiles = (N + 31) / 32;
+    const int64_t ngrid = ceil_div64(groups * ntiles, kWarps);
+    auto k = bsr8_spmm_f32_narrow_kernel<6, 3>;
+    if (int s = set_smem(k, F32NarrowCfg<6>::kSmem)) return s;
+    k<<<(unsigned)ngrid, kThreadsBsr, F32NarrowCfg<6>::kSmem, st>>>(indptr, indices, blocks, block_row_begin,
+                                                                    block_row_end, B, (int)ldb, C, ldc, N, ntiles, rpw);
+    LF_CUDA_CHECK(cudaGetLastError());
+    return LF_OK;
+  }
   if (T == 2 && copy_engine() > 1)
     return bsr8_f32_tma_launch(copy_engine() == 3, indptr, indices, blocks, block_row_begin, block_row_end, B, ldb, C, ldc, N, D, rpw,
                                tile_major > 0, st);
