@@ -457,6 +457,268 @@ bsr8_spmm_16bit_kernel(const int64_t* __restrict__ indptr, const int32_t* __rest
   cp_async_wait<0>();
 }
 
+// ---------------------------------------------------------------------------------------------
+// 16-bit, narrow tile: 32 features per warp, for N <= 32 (the 128-feature tile above would spend
+// three quarters of every MMA on padding).  As in the float32 narrow kernel both halves of an
+// MMA carry features:  tile j (j = 0, 1): m = g <-> feature F + 4g + j,  m = g + 8 <-> F + 4g + 2 + j,
+// so a lane needs 4 consecutive 16-bit features (64 bits) of each of its four B rows and a block
+// pair costs 2 MMAs.  Stage: 16 rows of 64 bytes cut into 32-byte pieces (piece h of row r holds
+// features 16h .. 16h + 15) plus the two blocks, 1280 bytes.  Piece (r, h) lies in 128-byte line
+// (r & 1) + 2h + 4(r >> 3) at byte 32 ((r >> 1) & 3): the 16 lanes of one 64-bit load phase
+// (g = 0..3 or 4..7, t = 0..3) then read one whole line, each its own 8 bytes.
+// ---------------------------------------------------------------------------------------------
+template <int D>
+struct H16NarrowCfg {
+  static constexpr int kStage = 16 * 64 + 256;
+  static constexpr int kSmem = kWarps * D * kStage;
+};
+
+__device__ __forceinline__ int narrow16_offset(int r, int h) {
+  return ((r & 1) + 2 * h + 4 * (r >> 3)) * 128 + ((r >> 1) & 3) * 32;
+}
+
+template <bool BF16, int D, int MINB>
+__global__ void __launch_bounds__(kThreadsBsr, MINB)
+bsr8_spmm_16bit_narrow_kernel(const int64_t* __restrict__ indptr, const int32_t* __restrict__ indices,
+                              const uint16_t* __restrict__ blocks, int64_t block_row_begin, int64_t block_row_end,
+                              const uint16_t* __restrict__ B, int ldb, float* __restrict__ C, int64_t ldc, int N,
+                              int tiles, int rows_per_warp) {
+  using Cfg = H16NarrowCfg<D>;
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3, warp = threadIdx.x >> 5;
+  const int64_t work = (int64_t)blockIdx.x * kWarps + warp;
+  int64_t grp;
+  int tile;
+  split_work(work, tiles, 0, grp, tile);
+  const int64_t I0 = block_row_begin + grp * rows_per_warp;
+  if (I0 >= block_row_end) return;
+  const int R = (int)min((int64_t)rows_per_warp, block_row_end - I0);
+  const int F = tile * 32;
+  uint8_t* ring = smem_raw + warp * (D * Cfg::kStage);
+  const uint32_t ring_u32 = smem_u32(ring);
+
+  const int64_t my_ptr = indptr[I0 + min(lane, R)];
+  const int64_t stream_end = __shfl_sync(0xffffffffu, my_ptr, R);
+  auto row_start = [&](int r) { return __shfl_sync(0xffffffffu, my_ptr, r); };
+
+  int my_idx = 0;
+  int64_t win = -(int64_t)64;
+  int ir = 0;
+  int64_t ib = row_start(0), ire = row_start(1);
+  while (ib == ire && ir + 1 < R) { ++ir; ire = row_start(ir + 1); }
+  int slot_in = 0;
+  const int cc = lane & 3, rl = lane >> 2;      // 16-byte chunk of a 64-byte row, row of the block
+  const bool in = F + 8 * cc < N;
+  // chunk cc = piece cc >> 1, second half of the piece when cc is odd
+  const uint32_t off0 = narrow16_offset(rl, cc >> 1) + (cc & 1) * 16;
+  const uint32_t off1 = narrow16_offset(8 + rl, cc >> 1) + (cc & 1) * 16;
+
+  auto issue_next = [&]() {
+    if (ib < stream_end) {
+      const int64_t b = ib;
+      const bool two = b + 1 < ire;
+      if (b + 1 >= win + 32) {
+        win = b;
+        my_idx = (b + lane < stream_end) ? indices[b + lane] : 0;
+      }
+      const int J0 = __shfl_sync(0xffffffffu, my_idx, (int)(b - win));
+      const int J1 = __shfl_sync(0xffffffffu, my_idx, (int)(b + 1 - win));
+      const uint32_t dst = ring_u32 + slot_in * Cfg::kStage;
+      const int64_t col = F + (in ? 8 * cc : 0);
+      cp_async16(dst + off0, B + ((int64_t)J0 * 8 + rl) * ldb + col, in ? 16 : 0);
+      cp_async16(dst + off1, B + ((int64_t)(two ? J1 : J0) * 8 + rl) * ldb + col, (in && two) ? 16 : 0);
+      if (lane < 16)
+        cp_async16(dst + 1024 + lane * 16, blocks + (b + ((lane >= 8 && two) ? 1 : 0)) * 64 + (lane & 7) * 8,
+                   (lane < 8 || two) ? 16 : 0);
+      ib = two ? b + 2 : b + 1;
+      while (ib == ire && ir + 1 < R) { ++ir; ire = row_start(ir + 1); }
+      slot_in = slot_in + 1 == D ? 0 : slot_in + 1;
+    }
+    cp_async_commit();
+  };
+
+#pragma unroll
+  for (int s = 0; s < D - 1; ++s) issue_next();
+
+  // where this lane reads: rows 2t, 2t+1 of block 0 and of block 1, piece g >> 2, 8 bytes at 8 (g & 3)
+  const int rd0 = narrow16_offset(2 * t, g >> 2) + (g & 3) * 8;
+  const int rd1 = narrow16_offset(2 * t + 1, g >> 2) + (g & 3) * 8;
+  const int rd2 = narrow16_offset(8 + 2 * t, g >> 2) + (g & 3) * 8;
+  const int rd3 = narrow16_offset(8 + 2 * t + 1, g >> 2) + (g & 3) * 8;
+
+  int slot_out = 0;
+  for (int r = 0; r < R; ++r) {
+    float acc[2][4];
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
+
+    const int64_t be = row_start(r + 1);
+    for (int64_t b = row_start(r); b < be; b += 2) {
+      cp_async_wait<D - 2>();
+      __syncwarp();
+      issue_next();
+
+      const uint8_t* st = ring + slot_out * Cfg::kStage;
+      slot_out = slot_out + 1 == D ? 0 : slot_out + 1;
+      const uint32_t b0 = *reinterpret_cast<const uint32_t*>(st + 1024 + (g * 8 + 2 * t) * 2);
+      const uint32_t b1 = *reinterpret_cast<const uint32_t*>(st + 1024 + 128 + (g * 8 + 2 * t) * 2);
+      const uint2 v0 = *reinterpret_cast<const uint2*>(st + rd0);   // block 0, column 2t:   features 4g .. 4g+3
+      const uint2 v1 = *reinterpret_cast<const uint2*>(st + rd1);   // block 0, column 2t+1
+      const uint2 v2 = *reinterpret_cast<const uint2*>(st + rd2);   // block 1, column 2t
+      const uint2 v3 = *reinterpret_cast<const uint2*>(st + rd3);   // block 1, column 2t+1
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const uint32_t sel = j ? 0x7632u : 0x5410u;   // second / first feature of each 32-bit word
+        uint32_t a[4];
+        a[0] = __byte_perm(v0.x, v1.x, sel);   // m = g   (feature 4g + j),     k = 2t, 2t+1
+        a[1] = __byte_perm(v0.y, v1.y, sel);   // m = g+8 (feature 4g + 2 + j), k = 2t, 2t+1
+        a[2] = __byte_perm(v2.x, v3.x, sel);   // m = g,   k = 2t+8, 2t+9
+        a[3] = __byte_perm(v2.y, v3.y, sel);   // m = g+8, k = 2t+8, 2t+9
+        mma_16bit<BF16>(acc[j], a, b0, b1);
+      }
+    }
+
+    if (F + 4 * g < N) {
+      float* c0 = C + ((I0 + r - block_row_begin) * 8 + 2 * t) * ldc + F + 4 * g;
+      __stcs(reinterpret_cast<float4*>(c0), make_float4(acc[0][0], acc[1][0], acc[0][2], acc[1][2]));
+      __stcs(reinterpret_cast<float4*>(c0 + ldc), make_float4(acc[0][1], acc[1][1], acc[0][3], acc[1][3]));
+    }
+  }
+  cp_async_wait<0>();
+}
+
+// ---------------------------------------------------------------------------------------------
+// 16-bit, 64 features per warp, for 32 < N <= 64 (the 128-feature tile would leave the upper half
+// of every MMA on padding and, with its 4.3 KB stages, only two thread blocks of three stages
+// per SM).  tile j (j = 0..3): m = g <-> feature F + 8g + j,  m = g + 8 <-> F + 8g + 4 + j: one
+// 128-bit load per B row, 4 MMAs per block pair.  Stage: 16 rows of 128 bytes (chunk c of row r
+// at c ^ (r & 7)) plus the two blocks, 2304 bytes; four stages, three thread blocks per SM.
+// ---------------------------------------------------------------------------------------------
+template <int D>
+struct H16MidCfg {
+  static constexpr int kStage = 16 * 128 + 256;
+  static constexpr int kSmem = kWarps * D * kStage;
+};
+
+template <bool BF16, int D, int MINB>
+__global__ void __launch_bounds__(kThreadsBsr, MINB)
+bsr8_spmm_16bit_mid_kernel(const int64_t* __restrict__ indptr, const int32_t* __restrict__ indices,
+                           const uint16_t* __restrict__ blocks, int64_t block_row_begin, int64_t block_row_end,
+                           const uint16_t* __restrict__ B, int ldb, float* __restrict__ C, int64_t ldc, int N,
+                           int tiles, int rows_per_warp) {
+  using Cfg = H16MidCfg<D>;
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3, warp = threadIdx.x >> 5;
+  const int64_t work = (int64_t)blockIdx.x * kWarps + warp;
+  int64_t grp;
+  int tile;
+  split_work(work, tiles, 0, grp, tile);
+  const int64_t I0 = block_row_begin + grp * rows_per_warp;
+  if (I0 >= block_row_end) return;
+  const int R = (int)min((int64_t)rows_per_warp, block_row_end - I0);
+  const int F = tile * 64;
+  uint8_t* ring = smem_raw + warp * (D * Cfg::kStage);
+  const uint32_t ring_u32 = smem_u32(ring);
+
+  const int64_t my_ptr = indptr[I0 + min(lane, R)];
+  const int64_t stream_end = __shfl_sync(0xffffffffu, my_ptr, R);
+  auto row_start = [&](int r) { return __shfl_sync(0xffffffffu, my_ptr, r); };
+
+  int my_idx = 0;
+  int64_t win = -(int64_t)64;
+  int ir = 0;
+  int64_t ib = row_start(0), ire = row_start(1);
+  while (ib == ire && ir + 1 < R) { ++ir; ire = row_start(ir + 1); }
+  int slot_in = 0;
+  const int cc = lane & 7, rr = lane >> 3;      // chunk of a 128-byte row, row within a group of four
+  const bool in = F + 8 * cc < N;
+
+  auto issue_next = [&]() {
+    if (ib < stream_end) {
+      const int64_t b = ib;
+      const bool two = b + 1 < ire;
+      if (b + 1 >= win + 32) {
+        win = b;
+        my_idx = (b + lane < stream_end) ? indices[b + lane] : 0;
+      }
+      const int J0 = __shfl_sync(0xffffffffu, my_idx, (int)(b - win));
+      const int J1 = __shfl_sync(0xffffffffu, my_idx, (int)(b + 1 - win));
+      const uint32_t dst = ring_u32 + slot_in * Cfg::kStage;
+      const uint16_t* s0 = B + (int64_t)J0 * 8 * ldb + F + (in ? 8 * cc : 0);
+      const uint16_t* s1 = B + (int64_t)(two ? J1 : J0) * 8 * ldb + F + (in ? 8 * cc : 0);
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int r = 4 * i + rr;
+        const uint32_t off = r * 128 + ((cc ^ r) << 4);
+        cp_async16(dst + off, s0 + (int64_t)r * ldb, in ? 16 : 0);
+        cp_async16(dst + 8 * 128 + off, s1 + (int64_t)r * ldb, (in && two) ? 16 : 0);
+      }
+      if (lane < 16)
+        cp_async16(dst + 16 * 128 + lane * 16, blocks + (b + ((lane >= 8 && two) ? 1 : 0)) * 64 + (lane & 7) * 8,
+                   (lane < 8 || two) ? 16 : 0);
+      ib = two ? b + 2 : b + 1;
+      while (ib == ire && ir + 1 < R) { ++ir; ire = row_start(ir + 1); }
+      slot_in = slot_in + 1 == D ? 0 : slot_in + 1;
+    }
+    cp_async_commit();
+  };
+
+#pragma unroll
+  for (int s = 0; s < D - 1; ++s) issue_next();
+
+  const int rd0 = (2 * t) * 128 + (((g ^ (2 * t)) & 7) << 4);
+  const int rd1 = (2 * t + 1) * 128 + (((g ^ (2 * t + 1)) & 7) << 4);
+
+  int slot_out = 0;
+  for (int r = 0; r < R; ++r) {
+    float acc[4][4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
+
+    const int64_t be = row_start(r + 1);
+    for (int64_t b = row_start(r); b < be; b += 2) {
+      cp_async_wait<D - 2>();
+      __syncwarp();
+      issue_next();
+
+      const uint8_t* st = ring + slot_out * Cfg::kStage;
+      slot_out = slot_out + 1 == D ? 0 : slot_out + 1;
+      const uint32_t b0 = *reinterpret_cast<const uint32_t*>(st + 16 * 128 + (g * 8 + 2 * t) * 2);
+      const uint32_t b1 = *reinterpret_cast<const uint32_t*>(st + 16 * 128 + 128 + (g * 8 + 2 * t) * 2);
+      const uint4 v0 = *reinterpret_cast<const uint4*>(st + rd0);             // block 0, column 2t: features 8g .. 8g+7
+      const uint4 v1 = *reinterpret_cast<const uint4*>(st + rd1);             // block 0, column 2t+1
+      const uint4 v2 = *reinterpret_cast<const uint4*>(st + 8 * 128 + rd0);   // block 1, column 2t
+      const uint4 v3 = *reinterpret_cast<const uint4*>(st + 8 * 128 + rd1);   // block 1, column 2t+1
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t sel = (j & 1) ? 0x7632u : 0x5410u;
+        auto lo = [&](const uint4& u) { return j < 2 ? u.x : u.y; };   // features 8g + j
+        auto hi = [&](const uint4& u) { return j < 2 ? u.z : u.w; };   // features 8g + 4 + j
+        uint32_t a[4];
+        a[0] = __byte_perm(lo(v0), lo(v1), sel);   // m = g,   k = 2t, 2t+1
+        a[1] = __byte_perm(hi(v0), hi(v1), sel);   // m = g+8, k = 2t, 2t+1
+        a[2] = __byte_perm(lo(v2), lo(v3), sel);   // m = g,   k = 2t+8, 2t+9
+        a[3] = __byte_perm(hi(v2), hi(v3), sel);   // m = g+8, k = 2t+8, 2t+9
+        mma_16bit<BF16>(acc[j], a, b0, b1);
+      }
+    }
+
+    if (F + 8 * g < N) {
+      float* c0 = C + ((I0 + r - block_row_begin) * 8 + 2 * t) * ldc + F + 8 * g;
+      float* c1 = c0 + ldc;
+      __stcs(reinterpret_cast<float4*>(c0), make_float4(acc[0][0], acc[1][0], acc[2][0], acc[3][0]));
+      __stcs(reinterpret_cast<float4*>(c0 + 4), make_float4(acc[0][2], acc[1][2], acc[2][2], acc[3][2]));
+      __stcs(reinterpret_cast<float4*>(c1), make_float4(acc[0][1], acc[1][1], acc[2][1], acc[3][1]));
+      __stcs(reinterpret_cast<float4*>(c1 + 4), make_float4(acc[0][3], acc[1][3], acc[2][3], acc[3][3]));
+    }
+  }
+  cp_async_wait<0>();
+}
+
 // tuning state of the block kernels (lf_bsr_set_tuning)
 int g_bsr_feat_units = 0;   // 0 = automatic, 1 or 2 = features per warp / 64 of the float32 kernel
 int g_bsr_stages = 0;       // 0 = automatic, 3 or 4 = depth of the per-warp copy ring
@@ -579,6 +841,39 @@ static int launch_16bit(bool bf16, const int64_t* indptr, const int32_t* indices
   const int64_t grid = ceil_div64(ceil_div64(r1 - r0, rpw) * tiles, kWarps);
   LF_REQUIRE(grid < (1ll << 31), "too many thread blocks");
   const int D = g_bsr_stages ? g_bsr_stages : 3;
+  if (N <= 32 && !g_bsr_stages) {   // narrow tile: both halves of every MMA carry features
+    const int ntiles = (N + 31) / 32;
+    const int64_t ngrid = ceil_div64(ceil_div64(r1 - r0, rpw) * ntiles, kWarps);
+    if (bf16) {
+      auto k = bsr8_spmm_16bit_narrow_kernel<true, 6, 3>;
+      if (int s = set_smem(k, H16NarrowCfg<6>::kSmem)) return s;
+      k<<<(unsigned)ngrid, kThreadsBsr, H16NarrowCfg<6>::kSmem, st>>>(indptr, indices, blocks, r0, r1, B, (int)ldb, C,
+                                                                      ldc, N, ntiles, rpw);
+    } else {
+      auto k = bsr8_spmm_16bit_narrow_kernel<false, 6, 3>;
+      if (int s = set_smem(k, H16NarrowCfg<6>::kSmem)) return s;
+      k<<<(unsigned)ngrid, kThreadsBsr, H16NarrowCfg<6>::kSmem, st>>>(indptr, indices, blocks, r0, r1, B, (int)ldb, C,
+                                                                      ldc, N, ntiles, rpw);
+    }
+    LF_CUDA_CHECK(cudaGetLastError());
+    return LF_OK;
+  }
+  if (N <= 64 && !g_bsr_stages) {   // 64 features per warp
+    const int64_t ngrid = ceil_div64(ceil_div64(r1 - r0, rpw), kWarps);
+    if (bf16) {
+      auto k = bsr8_spmm_16bit_mid_kernel<true, 4, 3>;
+      if (int s = set_smem(k, H16MidCfg<4>::kSmem)) return s;
+      k<<<(unsigned)ngrid, kThreadsBsr, H16MidCfg<4>::kSmem, st>>>(indptr, indices, blocks, r0, r1, B, (int)ldb, C, ldc,
+                                                                   N, 1, rpw);
+    } else {
+      auto k = bsr8_spmm_16bit_mid_kernel<false, 4, 3>;
+      if (int s = set_smem(k, H16MidCfg<4>::kSmem)) return s;
+      k<<<(unsigned)ngrid, kThreadsBsr, H16MidCfg<4>::kSmem, st>>>(indptr, indices, blocks, r0, r1, B, (int)ldb, C, ldc,
+                                                                   N, 1, rpw);
+    }
+    LF_CUDA_CHECK(cudaGetLastError());
+    return LF_OK;
+  }
   if (copy_engine() > 1) return bsr8_16bit_tma_launch(copy_engine() == 3, bf16, indptr, indices, blocks, r0, r1, B, ldb, C, ldc, N, D, rpw, st);
 #define LF_BSR16(B_, D_, M_)                                                                                  \
   do {                                                                                                        \
