@@ -402,7 +402,11 @@ class BsrProblem:
         self.r0, self.r1 = (Mb * rank) // world, (Mb * (rank + 1)) // world   # block rows
         self.tdt = {"f32": torch.float32, "bf16": torch.bfloat16, "f16": torch.float16}[args.dtype]
         self.dtype = args.dtype
-        self.kernel = "bsr8_spmm_f32_kernel" if args.dtype == "f32" else "bsr8_spmm_16bit_kernel"
+        if args.dtype == "f32":
+            self.kernel = "bsr8_spmm_f32_narrow_kernel" if N <= 32 else "bsr8_spmm_f32_kernel"
+        else:
+            self.kernel = ("bsr8_spmm_16bit_narrow_kernel" if N <= 32 else
+                           "bsr8_spmm_16bit_mid_kernel" if N <= 64 else "bsr8_spmm_16bit_kernel")
         name = {"f32": "float32", "bf16": "bfloat16", "f16": "float16"}[args.dtype]
         self.a = bsr.DeviceBsr8.from_arrays(indptr, indices, blocks, shape, name, dev)
         self.B = torch.from_numpy(self.B_host).to(dev).to(self.tdt)
