@@ -75,9 +75,10 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
                : "memory");
 }
 
-// Shared memory of one thread block: [warp][stage] boxes (kBoxes x 1024 bytes, the region starts
-// on a 1024-byte boundary so that the swizzle of a box depends on the row only), then
-// [warp][stage] A blocks (256 bytes), then [warp][stage] mbarriers.
+// Shared memory of one thread block: [warp][stage] B data (DATA bytes: four swizzled 1024-byte
+// boxes, or the pitched rows; the region starts on a 1024-byte boundary so that the swizzle of a
+// box depends on the row only), then [warp][stage] A blocks (256 bytes), then [warp][stage]
+// mbarriers.
 template <int D, int DATA>
 struct TmaCfg {
   static constexpr int kData = DATA;
