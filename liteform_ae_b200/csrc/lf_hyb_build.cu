@@ -46,20 +46,39 @@ __device__ __forceinline__ int64_t segment_end(const int32_t* __restrict__ indic
 // ------------------------------------------------------------------------------------------
 // A (row, partition) segment of at least kLongSegMin entries is not marked by the warp that
 // found it (a 100 000-entry row would keep one warp busy for thousands of iterations while the
-// rest of the grid has long finished): the warp appends it to a list, and stats_long_kernel
+// rest of the grid has long finished; even 8 000 entries are 250 dependent steps, as long as the
+// whole rest of the pass on a million-row graph): the warp appends it to a list, and stats_long_kernel
 // spreads the listed segments over the whole grid in chunks.  Such a segment is always in the
 // widest class.  A full list is not an error: further segments are marked in place.
 struct LongSeg {
   long long pos, end;
 };
-constexpr int kLongSegMin = 8192;
+constexpr int kLongSegMin = 2048;
 constexpr int kLongSegCap = 8192;
 constexpr int kLongChunk = 2048;
 constexpr size_t kLongListBytes = 256 + sizeof(LongSeg) * kLongSegCap;   // counter slot + list
 static_assert(kLongSegMin > (1 << (kClasses - 1)), "a deferred segment must belong to the widest class");
 
-// One warp per matrix row.  For each column partition the row touches: degree -> width class,
-// three counters per (partition, class), and the class bit OR-ed into every touched column.
+// A warp marks the columns of entries [lo, hi) with `bit`: four strided entries per lane and
+// step, their columns and masks loaded before the first atomic, so that the loads overlap.
+__device__ __forceinline__ void warp_mark(const int32_t* __restrict__ indices, uint32_t* __restrict__ colmask,
+                                          int64_t lo, int64_t hi, int lane, uint32_t bit) {
+  for (int64_t i = lo + lane; i < hi; i += 128) {
+    int32_t c[4];
+    uint32_t m[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) c[u] = i + 32 * u < hi ? indices[i + 32 * u] : -1;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) m[u] = c[u] >= 0 ? colmask[c[u]] : bit;
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (!(m[u] & bit)) atomicOr(colmask + c[u], bit);
+  }
+}
+
+// Several partitions: one warp per matrix row.  For each column partition the row touches:
+// degree -> width class, three counters per (partition, class), and the class bit OR-ed into
+// every touched column.
 __global__ void __launch_bounds__(256)
 stats_rows_kernel(const int64_t* __restrict__ indptr, const int32_t* __restrict__ indices,
                   int64_t num_rows, int64_t psz, int num_parts,
@@ -95,19 +114,7 @@ stats_rows_kernel(const int64_t* __restrict__ indptr, const int32_t* __restrict_
       c_next = s_next + lane < e_next ? indices[s_next + lane] : 0;
     }
     int64_t pos = s;
-    if (num_parts == 1 && e - s <= 32 && e > s) {
-      const uint32_t deg = (uint32_t)(e - s);
-      const int kc = ceil_log2_u32(deg);
-      if (lane == 0) {
-        unsigned long long* a = acc + kc * 3;
-        atomicAdd(a + 0, 1ull);
-        atomicAdd(a + 1, (unsigned long long)deg);
-        atomicAdd(a + 2, 1ull);
-      }
-      const uint32_t bit = 1u << kc;
-      if (lane < (int)deg && !(colmask[c_first] & bit)) atomicOr(colmask + c_first, bit);
-      pos = e;
-    } else if (num_parts > 1 && e - s <= 32) {
+    if (num_parts > 1 && e - s <= 32) {
       // short row, several partitions: one entry per lane.  A lane whose partition differs from
       // its left neighbour's heads a segment; segment lengths come from the ballot of heads, so
       // all segments of the row are counted and marked at once instead of one after the other.
@@ -165,12 +172,7 @@ stats_rows_kernel(const int64_t* __restrict__ indptr, const int32_t* __restrict_
           deferred = true;
         }
       }
-      if (!deferred) {
-        for (int64_t i = pos + lane; i < nxt; i += 32) {
-          const int32_t c = indices[i];
-          if (!(colmask[c] & bit)) atomicOr(colmask + c, bit);
-        }
-      }
+      if (!deferred) warp_mark(indices, colmask, pos, nxt, lane, bit);
       pos = nxt;
     }
     r = r_next;
@@ -185,30 +187,148 @@ stats_rows_kernel(const int64_t* __restrict__ indptr, const int32_t* __restrict_
   }
 }
 
-// Marks the columns of the listed long segments.  Chunks of kLongChunk entries are dealt round
-// robin over the thread blocks, continuing across segments, so that a handful of very long rows
-// still occupies the whole grid.
+// One partition: a warp takes 32 consecutive rows.  Most rows of a graph matrix hold a handful
+// of entries, and a warp per row spends its time waiting on the chain row pointer -> column ->
+// class mask for one row at a time.  Here a row of up to kLaneRowMax entries belongs to ONE lane,
+// which walks its few entries alone -- 32 such chains in flight per warp; the longer rows of the
+// batch are then taken by the whole warp, one after the other, the next one's columns requested
+// before the current one is marked.
+constexpr int kLaneRowMax = 8;
+__global__ void __launch_bounds__(256)
+stats_rows_p1_kernel(const int64_t* __restrict__ indptr, const int32_t* __restrict__ indices, int64_t num_rows,
+                     unsigned long long* __restrict__ class_stats, uint32_t* __restrict__ colmask,
+                     unsigned int* __restrict__ long_count, LongSeg* __restrict__ long_list) {
+  __shared__ unsigned long long s_stats[kClasses * 3];
+  for (int i = threadIdx.x; i < kClasses * 3; i += blockDim.x) s_stats[i] = 0ull;
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int64_t n_warps = (int64_t)gridDim.x * (blockDim.x >> 5);
+  for (int64_t base = warp * 32; base < num_rows; base += n_warps * 32) {
+    const int64_t r = base + lane;
+    const bool live = r < num_rows;
+    const int64_t s = live ? indptr[r] : 0;
+    const int64_t e = live ? indptr[r + 1] : 0;
+    const int64_t len = e - s;
+    if (len > 0 && len <= kLaneRowMax) {
+      const int kc = ceil_log2_u32((uint32_t)len);
+      unsigned long long* a = s_stats + kc * 3;
+      atomicAdd(a + 0, 1ull);
+      atomicAdd(a + 1, (unsigned long long)len);
+      atomicAdd(a + 2, 1ull);
+      const uint32_t bit = 1u << kc;
+      for (int64_t i = s; i < e; ++i) {
+        const int32_t c = indices[i];
+        if (!(colmask[c] & bit)) atomicOr(colmask + c, bit);
+      }
+    }
+    unsigned todo = __ballot_sync(0xffffffffu, len > kLaneRowMax);
+    int64_t s_cur = 0, e_cur = 0;
+    int32_t c_cur = 0;
+    if (todo) {
+      const int src = __ffs(todo) - 1;
+      s_cur = __shfl_sync(0xffffffffu, s, src);
+      e_cur = __shfl_sync(0xffffffffu, e, src);
+      c_cur = s_cur + lane < e_cur ? indices[s_cur + lane] : 0;
+    }
+    while (todo) {
+      todo &= todo - 1;
+      int64_t s_nxt = 0, e_nxt = 0;
+      int32_t c_nxt = 0;
+      if (todo) {
+        const int src = __ffs(todo) - 1;
+        s_nxt = __shfl_sync(0xffffffffu, s, src);
+        e_nxt = __shfl_sync(0xffffffffu, e, src);
+        c_nxt = s_nxt + lane < e_nxt ? indices[s_nxt + lane] : 0;
+      }
+      const uint32_t deg = (uint32_t)(e_cur - s_cur);
+      const int k = ceil_log2_u32(deg);
+      const int kc = k > kClasses - 1 ? kClasses - 1 : k;
+      if (lane == 0) {
+        const unsigned long long reps = k > kClasses - 1 ? (1ull << (k - (kClasses - 1))) : 1ull;
+        unsigned long long* a = s_stats + kc * 3;
+        atomicAdd(a + 0, reps);
+        atomicAdd(a + 1, (unsigned long long)deg);
+        atomicAdd(a + 2, 1ull);
+      }
+      const uint32_t bit = 1u << kc;
+      if (deg <= 32u) {
+        if (lane < (int)deg && !(colmask[c_cur] & bit)) atomicOr(colmask + c_cur, bit);
+      } else {
+        bool deferred = false;
+        if (deg >= (uint32_t)kLongSegMin) {
+          unsigned int slot = 0;
+          if (lane == 0) slot = atomicAdd(long_count, 1u);
+          slot = __shfl_sync(0xffffffffu, slot, 0);
+          if (slot < (unsigned int)kLongSegCap) {
+            if (lane == 0) long_list[slot] = LongSeg{(long long)s_cur, (long long)e_cur};
+            deferred = true;
+          }
+        }
+        if (!deferred) warp_mark(indices, colmask, s_cur, e_cur, lane, bit);
+      }
+      s_cur = s_nxt;
+      e_cur = e_nxt;
+      c_cur = c_nxt;
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < kClasses * 3; i += blockDim.x)
+    if (s_stats[i]) atomicAdd(class_stats + i, s_stats[i]);
+}
+
+// Marks the columns of the listed long segments.  The list is taken in tiles of 256 segments: the
+// block scans their chunk counts in shared memory, and chunk number c of the running count goes
+// to thread block c mod gridDim.x, which finds its segment by bisection -- a handful of very long
+// rows occupies the whole grid, and thousands of listed segments cost no serial walk.
 __global__ void __launch_bounds__(256)
 stats_long_kernel(const int32_t* __restrict__ indices, const unsigned int* __restrict__ long_count,
                   const LongSeg* __restrict__ long_list, uint32_t* __restrict__ colmask) {
+  __shared__ long long s_pos[256], s_end[256];
+  __shared__ int s_pre[257];
+  __shared__ int s_scan[256 / 32 + 1];
   const unsigned int listed = *long_count;
   const int n = (int)(listed < (unsigned int)kLongSegCap ? listed : (unsigned int)kLongSegCap);
   const uint32_t bit = 1u << (kClasses - 1);
-  long long dealt = 0;   // chunks of the segments before this one
-  for (int s = 0; s < n; ++s) {
-    const LongSeg seg = long_list[s];
-    const long long chunks = (seg.end - seg.pos + kLongChunk - 1) / kLongChunk;
+  long long dealt = 0;   // chunks of the tiles before this one
+  for (int t0 = 0; t0 < n; t0 += 256) {
+    const int i = t0 + threadIdx.x;
+    LongSeg seg = {0, 0};
+    if (i < n) seg = long_list[i];
+    const int chunks = (int)((seg.end - seg.pos + kLongChunk - 1) / kLongChunk);
+    int total;
+    const int before = block_exclusive_scan<256>(chunks, s_scan, &total);
+    s_pos[threadIdx.x] = seg.pos;
+    s_end[threadIdx.x] = seg.end;
+    s_pre[threadIdx.x] = before;
+    if (threadIdx.x == 0) s_pre[256] = total;
+    __syncthreads();
     long long first = ((long long)blockIdx.x - dealt) % (long long)gridDim.x;
     if (first < 0) first += gridDim.x;
-    for (long long c = first; c < chunks; c += gridDim.x) {
-      const long long lo = seg.pos + c * kLongChunk;
-      const long long hi = lo + kLongChunk < seg.end ? lo + kLongChunk : seg.end;
-      for (long long i = lo + threadIdx.x; i < hi; i += blockDim.x) {
-        const int32_t col = indices[i];
-        if (!(colmask[col] & bit)) atomicOr(colmask + col, bit);
+    for (long long c = first; c < total; c += gridDim.x) {
+      int lo = 0, hi = 256;   // last segment of the tile whose first chunk is <= c
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (s_pre[mid] <= c) lo = mid; else hi = mid;
       }
+      const long long from = s_pos[lo] + (c - s_pre[lo]) * kLongChunk;
+      const long long to = from + kLongChunk < s_end[lo] ? from + kLongChunk : s_end[lo];
+      constexpr int kPer = kLongChunk / 256;
+      int32_t col[kPer];
+      uint32_t m[kPer];
+#pragma unroll
+      for (int u = 0; u < kPer; ++u) {
+        const long long e = from + threadIdx.x + 256 * u;
+        col[u] = e < to ? indices[e] : -1;
+      }
+#pragma unroll
+      for (int u = 0; u < kPer; ++u) m[u] = col[u] >= 0 ? colmask[col[u]] : bit;
+#pragma unroll
+      for (int u = 0; u < kPer; ++u)
+        if (!(m[u] & bit)) atomicOr(colmask + col[u], bit);
     }
-    dealt += chunks;
+    dealt += total;
+    __syncthreads();
   }
 }
 
@@ -582,13 +702,20 @@ int lf_hyb_stats(const int64_t* indptr, const int32_t* indices, int64_t num_rows
   LF_CUDA_CHECK(cudaMemsetAsync(class_stats, 0, sizeof(int64_t) * n_stat, st));
   LF_CUDA_CHECK(cudaMemsetAsync(colmask_hist, 0, sizeof(int64_t) * (size_t)num_parts * LF_COLMASK_BINS, st));
   if (num_rows > 0) {
-    const size_t smem = n_stat * sizeof(unsigned long long);
-    const int use_smem = smem <= 40 * 1024;
-    const int64_t want = ceil_div64(num_rows, 8 * 4);  // 8 warps per block, ~4 rows per warp
-    const int grid = (int)(want < 1 ? 1 : (want > 148 * 64 ? 148 * 64 : want));
-    stats_rows_kernel<<<grid, 256, use_smem ? smem : 0, st>>>(
-        indptr, indices, num_rows, psz, num_parts, (unsigned long long*)class_stats, colmask, use_smem, long_count,
-        long_list);
+    if (num_parts == 1) {
+      const int64_t want = ceil_div64(num_rows, 8 * 32);  // 8 warps per block, 32 rows per warp and step
+      const int grid = (int)(want < 1 ? 1 : (want > 148 * 16 ? 148 * 16 : want));
+      stats_rows_p1_kernel<<<grid, 256, 0, st>>>(indptr, indices, num_rows, (unsigned long long*)class_stats, colmask,
+                                                 long_count, long_list);
+    } else {
+      const size_t smem = n_stat * sizeof(unsigned long long);
+      const int use_smem = smem <= 40 * 1024;
+      const int64_t want = ceil_div64(num_rows, 8 * 4);  // 8 warps per block, ~4 rows per warp
+      const int grid = (int)(want < 1 ? 1 : (want > 148 * 64 ? 148 * 64 : want));
+      stats_rows_kernel<<<grid, 256, use_smem ? smem : 0, st>>>(
+          indptr, indices, num_rows, psz, num_parts, (unsigned long long*)class_stats, colmask, use_smem, long_count,
+          long_list);
+    }
     LF_CUDA_CHECK(cudaGetLastError());
     stats_long_kernel<<<148 * 4, 256, 0, st>>>(indices, long_count, long_list, colmask);
     LF_CUDA_CHECK(cudaGetLastError());

@@ -1,4 +1,4 @@
-"""Statistics pass on matrices made of very long rows.  Row segments of 8192 entries or more are
+"""Statistics pass on matrices made of very long rows.  Row segments of 2048 entries or more are
 listed and marked by a second, grid-wide kernel; the list holds 8192 segments and further ones are
 marked in place.  8300 rows of 8192 consecutive columns exercise the deferred path, the overflow
 path and (with two partitions) their mixture with ordinary segments.  Expected counters follow from
