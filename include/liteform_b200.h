@@ -163,7 +163,8 @@ typedef struct lf_hyb {
  *
  * lf_hyb_plan counts: it fills ell_rows[], row_off[], slot_off[] (host) and *num_zero_rows, and
  * leaves per-block offsets in `workspace` for lf_hyb_fill, which must be given the same
- * workspace contents, the same matrix, widths and row range.
+ * workspace contents, the same matrix, widths and row range.  lf_hyb_fill writes four slots at a
+ * time: cols and vals must be 16-byte aligned, mask (if given) 4-byte aligned.
  * ------------------------------------------------------------------------------------------- */
 size_t lf_hyb_build_workspace_bytes(int64_t row_begin, int64_t row_end, int32_t num_parts,
                                     int32_t num_buckets);

@@ -517,65 +517,51 @@ hyb_fill_rows_kernel(const int64_t* __restrict__ indptr, const int32_t* __restri
   }
 }
 
-// One thread per slot of the cols/vals/mask arenas (alignment gaps included, they get zeros).
-// A slot costs three dependent rounds of loads (bucket tables, the ELL row's source range, the
-// entry itself); a thread therefore works on kFillUnroll slots at once, a grid stride apart, so
-// that their rounds overlap.
-constexpr int kFillUnroll = 4;
+// One thread per group of four consecutive slots of the cols/vals/mask arenas (alignment gaps
+// included, they get zeros; bucket starts are multiples of 64 slots, so a group never straddles
+// two buckets).  A slot costs three dependent rounds of loads (bucket tables, the ELL row's
+// source range, the entry itself); the four slots of a group go through the rounds together and
+// leave as one 128-bit store per array (32 bits for the mask).
 __global__ void __launch_bounds__(256)
 hyb_fill_slots_kernel(const int32_t* __restrict__ indices, const float* __restrict__ data,
                       BuildMeta meta, int nb, const int32_t* __restrict__ src_start,
                       const int32_t* __restrict__ src_len, int32_t* __restrict__ cols,
                       float* __restrict__ vals, uint8_t* __restrict__ mask, int64_t total_slots) {
-  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  for (int64_t t0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t0 < total_slots; t0 += stride * kFillUnroll) {
-    int64_t er[kFillUnroll];
-    int j[kFillUnroll];
-    bool in_row[kFillUnroll];
+  const int64_t groups = total_slots >> 2;   // total_slots is a multiple of 64
+  for (int64_t q = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; q < groups; q += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t t = q << 2;
+    int lo = 0, hi = nb;  // last bucket i with slot_off[i] <= t
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (meta.slot_off[mid] <= t) lo = mid; else hi = mid;
+    }
+    const int w = meta.widths[lo];
+    const int shift = 31 - __clz(w);   // widths are powers of two
+    const int64_t local = t - meta.slot_off[lo];
+    const int64_t live = meta.ell_rows[lo] << shift;
+    const int64_t row0 = meta.row_off[lo];
+    int64_t src[4];
 #pragma unroll
-    for (int u = 0; u < kFillUnroll; ++u) {
-      const int64_t t = t0 + u * stride;
-      in_row[u] = false;
-      er[u] = 0;
-      j[u] = 0;
-      if (t < total_slots) {
-        int lo = 0, hi = nb;  // last bucket i with slot_off[i] <= t
-        while (hi - lo > 1) {
-          const int mid = (lo + hi) >> 1;
-          if (meta.slot_off[mid] <= t) lo = mid; else hi = mid;
-        }
-        const int w = meta.widths[lo];
-        const int shift = 31 - __clz(w);   // widths are powers of two
-        const int64_t local = t - meta.slot_off[lo];
-        if (local < (meta.ell_rows[lo] << shift)) {
-          in_row[u] = true;
-          er[u] = meta.row_off[lo] + (local >> shift);
-          j[u] = (int)(local & (w - 1));
-        }
+    for (int u = 0; u < 4; ++u) {
+      src[u] = -1;
+      if (local + u < live) {
+        const int64_t er = row0 + ((local + u) >> shift);
+        const int j = (int)((local + u) & (w - 1));
+        if (j < src_len[er]) src[u] = (int64_t)src_start[er] + j;
       }
     }
-    int64_t src[kFillUnroll];
+    int32_t c[4];
+    float v[4];
 #pragma unroll
-    for (int u = 0; u < kFillUnroll; ++u) {
-      src[u] = -1;
-      if (in_row[u] && j[u] < src_len[er[u]]) src[u] = (int64_t)src_start[er[u]] + j[u];
-    }
-    int32_t c[kFillUnroll];
-    float v[kFillUnroll];
-#pragma unroll
-    for (int u = 0; u < kFillUnroll; ++u) {
+    for (int u = 0; u < 4; ++u) {
       c[u] = src[u] >= 0 ? indices[src[u]] : 0;
       v[u] = src[u] >= 0 ? (data ? data[src[u]] : 1.f) : 0.f;
     }
-#pragma unroll
-    for (int u = 0; u < kFillUnroll; ++u) {
-      const int64_t t = t0 + u * stride;
-      if (t < total_slots) {
-        cols[t] = c[u];
-        vals[t] = v[u];
-        if (mask) mask[t] = src[u] >= 0 ? 1 : 0;
-      }
-    }
+    *reinterpret_cast<int4*>(cols + t) = make_int4(c[0], c[1], c[2], c[3]);
+    *reinterpret_cast<float4*>(vals + t) = make_float4(v[0], v[1], v[2], v[3]);
+    if (mask)
+      *reinterpret_cast<uint32_t*>(mask + t) = (src[0] >= 0 ? 1u : 0u) | (src[1] >= 0 ? 0x100u : 0u) |
+                                               (src[2] >= 0 ? 0x10000u : 0u) | (src[3] >= 0 ? 0x1000000u : 0u);
   }
 }
 
@@ -898,7 +884,9 @@ int lf_hyb_fill(const int64_t* indptr, const int32_t* indices, const float* data
     LF_CUDA_CHECK(cudaGetLastError());
   }
   if (total_slots > 0) {
-    const int64_t want = ceil_div64(total_slots, 256 * 4);
+    LF_REQUIRE(total_slots % 4 == 0 && (uintptr_t)L->cols % 16 == 0 && (uintptr_t)L->vals % 16 == 0 &&
+                   (uintptr_t)L->mask % 4 == 0, "cols / vals must be 16-byte aligned, mask 4-byte aligned");
+    const int64_t want = ceil_div64(total_slots, 256 * 4 * 4);
     const int grid = (int)(want > 148 * 32 ? 148 * 32 : want);
     hyb_fill_slots_kernel<<<grid, 256, 0, st>>>(indices, data, meta, nb, src_start, src_len,
                                                 (int32_t*)L->cols, (float*)L->vals, (uint8_t*)L->mask, total_slots);
