@@ -187,13 +187,16 @@ stats_rows_kernel(const int64_t* __restrict__ indptr, const int32_t* __restrict_
   }
 }
 
-// One partition: a warp takes 32 consecutive rows.  Most rows of a graph matrix hold a handful
-// of entries, and a warp per row spends its time waiting on the chain row pointer -> column ->
-// class mask for one row at a time.  Here a row of up to kLaneRowMax entries belongs to ONE lane,
-// which walks its few entries alone -- 32 such chains in flight per warp; the longer rows of the
-// batch are then taken by the whole warp, one after the other, the next one's columns requested
-// before the current one is marked.
-constexpr int kLaneRowMax = 8;
+// One partition: a warp takes 32 consecutive rows, one row pointer per lane.  Counters are added
+// by the lane that holds the row.  The entries of the 32 rows are one contiguous range of the
+// CSR arrays: the warp walks it with coalesced loads, 128 entries per step, and every entry finds
+// its row (hence its class bit) by a five-step bisection over the row ends held in the lanes'
+// registers.  Short and medium rows cost the same per entry and there is no per-row chain of
+// dependent loads; a warp per row spent its time waiting on exactly that chain.  Rows of
+// kLongSegMin entries or more go to the list; a batch that holds one (rare) marks its other rows
+// one after the other instead, so that the walk does not have to step over the long row.
+// Measured against a warp per row (with the next row prefetched): 0.55 against 0.62 ms on 134 M
+// entries at 32 per row, 0.12 against 0.15 ms on a power-law graph of 14 entries per row.
 __global__ void __launch_bounds__(256)
 stats_rows_p1_kernel(const int64_t* __restrict__ indptr, const int32_t* __restrict__ indices, int64_t num_rows,
                      unsigned long long* __restrict__ class_stats, uint32_t* __restrict__ colmask,
@@ -206,70 +209,106 @@ stats_rows_p1_kernel(const int64_t* __restrict__ indptr, const int32_t* __restri
   const int64_t n_warps = (int64_t)gridDim.x * (blockDim.x >> 5);
   for (int64_t base = warp * 32; base < num_rows; base += n_warps * 32) {
     const int64_t r = base + lane;
-    const bool live = r < num_rows;
-    const int64_t s = live ? indptr[r] : 0;
-    const int64_t e = live ? indptr[r + 1] : 0;
+    // lanes past the last row hold an empty row at the end of the arrays: row ends stay monotone
+    const int64_t s = indptr[r < num_rows ? r : num_rows];
+    const int64_t e = indptr[r + 1 < num_rows ? r + 1 : num_rows];
     const int64_t len = e - s;
-    if (len > 0 && len <= kLaneRowMax) {
-      const int kc = ceil_log2_u32((uint32_t)len);
-      unsigned long long* a = s_stats + kc * 3;
-      atomicAdd(a + 0, 1ull);
-      atomicAdd(a + 1, (unsigned long long)len);
-      atomicAdd(a + 2, 1ull);
-      const uint32_t bit = 1u << kc;
-      for (int64_t i = s; i < e; ++i) {
-        const int32_t c = indices[i];
-        if (!(colmask[c] & bit)) atomicOr(colmask + c, bit);
+    const int k = len > 0 ? ceil_log2_u32((uint32_t)len) : 0;
+    const int kc = k > kClasses - 1 ? kClasses - 1 : k;
+    // counters: the rows of a batch mostly share a few classes, and 32 lanes adding to the same
+    // shared-memory words one after the other cost more than the marking; one lane per class
+    // present adds the batch's totals instead
+    for (unsigned pending = __ballot_sync(0xffffffffu, len > 0); pending;) {
+      const int leader = __ffs(pending) - 1;
+      const int k_lead = __shfl_sync(0xffffffffu, kc, leader);
+      const bool mine = len > 0 && kc == k_lead;
+      const unsigned group = __ballot_sync(0xffffffffu, mine);
+      unsigned long long sum_len = mine ? (unsigned long long)len : 0ull;
+      unsigned long long sum_rows = mine ? (k > kClasses - 1 ? (1ull << (k - (kClasses - 1))) : 1ull) : 0ull;
+#pragma unroll
+      for (int o = 16; o; o >>= 1) {
+        sum_len += __shfl_xor_sync(0xffffffffu, sum_len, o);
+        sum_rows += __shfl_xor_sync(0xffffffffu, sum_rows, o);
+      }
+      if (lane == leader) {
+        unsigned long long* a = s_stats + k_lead * 3;
+        atomicAdd(a + 0, sum_rows);
+        atomicAdd(a + 1, sum_len);
+        atomicAdd(a + 2, (unsigned long long)__popc(group));
+      }
+      pending &= ~group;
+    }
+    bool deferred = false;
+    if (len >= kLongSegMin) {
+      const unsigned int slot = atomicAdd(long_count, 1u);
+      if (slot < (unsigned int)kLongSegCap) {
+        long_list[slot] = LongSeg{(long long)s, (long long)e};
+        deferred = true;
       }
     }
-    unsigned todo = __ballot_sync(0xffffffffu, len > kLaneRowMax);
-    int64_t s_cur = 0, e_cur = 0;
-    int32_t c_cur = 0;
-    if (todo) {
-      const int src = __ffs(todo) - 1;
-      s_cur = __shfl_sync(0xffffffffu, s, src);
-      e_cur = __shfl_sync(0xffffffffu, e, src);
-      c_cur = s_cur + lane < e_cur ? indices[s_cur + lane] : 0;
-    }
-    while (todo) {
-      todo &= todo - 1;
-      int64_t s_nxt = 0, e_nxt = 0;
-      int32_t c_nxt = 0;
-      if (todo) {
-        const int src = __ffs(todo) - 1;
-        s_nxt = __shfl_sync(0xffffffffu, s, src);
-        e_nxt = __shfl_sync(0xffffffffu, e, src);
-        c_nxt = s_nxt + lane < e_nxt ? indices[s_nxt + lane] : 0;
-      }
-      const uint32_t deg = (uint32_t)(e_cur - s_cur);
-      const int k = ceil_log2_u32(deg);
-      const int kc = k > kClasses - 1 ? kClasses - 1 : k;
-      if (lane == 0) {
-        const unsigned long long reps = k > kClasses - 1 ? (1ull << (k - (kClasses - 1))) : 1ull;
-        unsigned long long* a = s_stats + kc * 3;
-        atomicAdd(a + 0, reps);
-        atomicAdd(a + 1, (unsigned long long)deg);
-        atomicAdd(a + 2, 1ull);
-      }
-      const uint32_t bit = 1u << kc;
-      if (deg <= 32u) {
-        if (lane < (int)deg && !(colmask[c_cur] & bit)) atomicOr(colmask + c_cur, bit);
-      } else {
-        bool deferred = false;
-        if (deg >= (uint32_t)kLongSegMin) {
-          unsigned int slot = 0;
-          if (lane == 0) slot = atomicAdd(long_count, 1u);
-          slot = __shfl_sync(0xffffffffu, slot, 0);
-          if (slot < (unsigned int)kLongSegCap) {
-            if (lane == 0) long_list[slot] = LongSeg{(long long)s_cur, (long long)e_cur};
-            deferred = true;
+    const bool has_long = __any_sync(0xffffffffu, len >= kLongSegMin);
+    const int64_t first = __shfl_sync(0xffffffffu, s, 0);
+    const int64_t batch_entries = __shfl_sync(0xffffffffu, e, 31) - first;
+    if (!has_long) {   // fewer than 32 * kLongSegMin entries
+      const uint32_t total = (uint32_t)batch_entries;
+      const uint32_t my_end = (uint32_t)(e - first);
+      for (uint32_t step = 0; step < total; step += 128) {
+        int32_t c[4];
+        uint32_t bit[4], m[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const uint32_t i = step + 32 * u + lane;
+          int lo = 0, hi = 31;   // smallest lane whose row ends after entry i
+#pragma unroll
+          for (int it = 0; it < 5; ++it) {
+            const int mid = (lo + hi) >> 1;
+            const uint32_t end_mid = __shfl_sync(0xffffffffu, my_end, mid);
+            if (end_mid > i) hi = mid; else lo = mid + 1;
           }
+          bit[u] = 1u << __shfl_sync(0xffffffffu, kc, lo);
+          c[u] = i < total ? indices[first + i] : -1;
         }
-        if (!deferred) warp_mark(indices, colmask, s_cur, e_cur, lane, bit);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) m[u] = c[u] >= 0 ? colmask[c[u]] : 0xffffffffu;
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (!(m[u] & bit[u])) atomicOr(colmask + c[u], bit[u]);
       }
-      s_cur = s_nxt;
-      e_cur = e_nxt;
-      c_cur = c_nxt;
+    } else {
+      // a batch around a listed row: one row after the other, the next row's first 32 columns
+      // requested before the current row is marked
+      unsigned todo = __ballot_sync(0xffffffffu, len > 0 && !deferred);
+      int src = 0;
+      int64_t s_cur = 0, e_cur = 0;
+      int32_t c_cur = 0;
+      if (todo) {
+        src = __ffs(todo) - 1;
+        s_cur = __shfl_sync(0xffffffffu, s, src);
+        e_cur = __shfl_sync(0xffffffffu, e, src);
+        c_cur = s_cur + lane < e_cur ? indices[s_cur + lane] : 0;
+      }
+      while (todo) {
+        todo &= todo - 1;
+        int src_nxt = 0;
+        int64_t s_nxt = 0, e_nxt = 0;
+        int32_t c_nxt = 0;
+        if (todo) {
+          src_nxt = __ffs(todo) - 1;
+          s_nxt = __shfl_sync(0xffffffffu, s, src_nxt);
+          e_nxt = __shfl_sync(0xffffffffu, e, src_nxt);
+          c_nxt = s_nxt + lane < e_nxt ? indices[s_nxt + lane] : 0;
+        }
+        const uint32_t bit = 1u << __shfl_sync(0xffffffffu, kc, src);
+        if (e_cur - s_cur <= 32) {
+          if (s_cur + lane < e_cur && !(colmask[c_cur] & bit)) atomicOr(colmask + c_cur, bit);
+        } else {
+          warp_mark(indices, colmask, s_cur, e_cur, lane, bit);
+        }
+        src = src_nxt;
+        s_cur = s_nxt;
+        e_cur = e_nxt;
+        c_cur = c_nxt;
+      }
     }
   }
   __syncthreads();
