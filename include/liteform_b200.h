@@ -48,6 +48,10 @@ typedef enum {
 #define LF_SPMM_ACCUMULATE 1      /* C += A * B  (what the generated reference kernel does,
                                      format_algos.py:508-515, 550, 595)                     */
 
+#define LF_SPMM_FORMAT_RESIDENT 4 /* lf_spmm_hyb_f32_host only, may be OR-ed with the others: the format arrays
+                                     are NOT uploaded; the workspace still holds them from an earlier call with
+                                     the same A_host and N (the reference uploads them on every call,
+                                     format_algos.py:568-578).  B is uploaded and C downloaded as always.   */
 #define LF_SPMM_NO_SYNC 2         /* lf_spmm_hyb_f32_host only, may be OR-ed with the above: enqueue the
                                      copies and the product and return; C is valid and the workspace free
                                      again once the stream has been synchronised.  Lets a caller keep two
@@ -60,7 +64,7 @@ const char* lf_last_error(void);
 /* Process-wide tuning knobs of the SpMM launch (no counterpart in the reference, whose launch
  * shape is fixed by its code generator, format_algos.py:503-539).  Results do not depend on them. */
 #define LF_OPT_SPMM_SLOTS_PER_GROUP 1  /* ELL slots one thread group walks (0 = automatic: 256, less for small launches) */
-#define LF_OPT_SPMM_CACHE_POLICY 2     /* 0 plain; 1 stream slots and C (default); 2 also B rows evict-last */
+#define LF_OPT_SPMM_CACHE_POLICY 2     /* 0 plain loads and stores; 1 slots, row ids and C stream through (default) */
 #define LF_OPT_SPMM_MIN_BLOCKS 3       /* resident thread blocks per SM the kernel is compiled for: 2..4 (default 3) */
 #define LF_OPT_BSR_COPY_ENGINE 4        /* how the 8x8 block kernels fill shared memory: 0 automatic, 1 per-lane
                                           cp.async, 2 tiled bulk copies through a tensor map, 3 one bulk copy per row
@@ -69,7 +73,23 @@ const char* lf_last_error(void);
                                           four tiles on), 1 the tiles of a block row run together (A read once),
                                           2 one tile after the other over all rows (the B rows of one tile stay
                                           in the L2) */
+#define LF_OPT_SPMM_TILE_SEGMENTS 6     /* order of the thread blocks of the composed-format product: 0 bucket after
+                                          bucket (default); S > 0: every bucket is cut into S segments of consecutive
+                                          rows and the launch runs segment 0 of all buckets, then segment 1, ... */
 int lf_set_option(int32_t option, int32_t value);
+
+/* ---------------------------------------------------------------------------------------------
+ * Structural check of a CSR matrix in device memory -- what every entry point below assumes and
+ * what SciPy guarantees for the reference (coo.tocsr(), format_matrix_market.py:74-76): row
+ * pointers run from 0 to nnz without decreasing, column indices lie in [0, num_cols) and ascend
+ * strictly inside a row.  Returns LF_ERR_INVALID_ARGUMENT (with a message naming the defect)
+ * otherwise.  Synchronises the stream; calls on one device must not overlap (the verdict travels
+ * through one device word).  The builder kernels never use an out-of-range column as an index
+ * (they skip it, lf_hyb_plan reports it), so a malformed matrix cannot make them touch memory
+ * they do not own; unsorted rows give a wrong format without notice -- validate first.
+ * ------------------------------------------------------------------------------------------- */
+int lf_csr_validate(const int64_t* indptr /*[dev] M+1*/, const int32_t* indices /*[dev] nnz*/,
+                    int64_t num_rows, int64_t num_cols, int64_t nnz, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Bucket statistics for the width search.
@@ -147,9 +167,6 @@ typedef struct lf_hyb {
   const uint8_t* mask;              /* [dev] slot_off[num_buckets] or NULL                 */
   const int32_t* zero_rows;         /* [dev] num_zero_rows or NULL                         */
   int64_t num_zero_rows;
-  const uint32_t* hot_bits;         /* [dev] slot_off[num_buckets]/32 words or NULL: bit k of word j is
-                                       set when slot 32*j + k gathers a frequently used row of B; only
-                                       read under cache policy 2, a pure performance hint             */
 } lf_hyb;
 
 /* ---------------------------------------------------------------------------------------------
@@ -189,6 +206,8 @@ int lf_hyb_fill(const int64_t* indptr /*[dev]*/, const int32_t* indices /*[dev]*
  * (playground_pipline/format_algos.py:388-605; arithmetic format_algos.py:99-102; launch shape
  * format_algos.py:503-539).  All buckets of all partitions run in one launch.  C points at the
  * first row of the shard (row row_begin), ldb/ldc are in elements.
+ * Padding slots are recognised by their stored value 0 and gather nothing; a stored entry whose
+ * value is exactly 0 is skipped the same way, so it does not propagate an Inf or NaN of B into C.
  * ------------------------------------------------------------------------------------------- */
 int lf_spmm_hyb_f32(const lf_hyb* A, const float* B /*[dev] K x N*/, int64_t ldb,
                     float* C /*[dev] (row_end-row_begin) x N*/, int64_t ldc, int32_t N,

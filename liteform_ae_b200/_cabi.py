@@ -23,10 +23,12 @@ LF_OPT_SPMM_CACHE_POLICY = 2
 LF_OPT_SPMM_MIN_BLOCKS = 3
 LF_OPT_BSR_COPY_ENGINE = 4
 LF_OPT_BSR_TILE_ORDER = 5
+LF_OPT_SPMM_TILE_SEGMENTS = 6
 LF_DTYPE_F32, LF_DTYPE_BF16, LF_DTYPE_F16 = 0, 1, 2
 LF_SPMM_OVERWRITE = 0
 LF_SPMM_ACCUMULATE = 1
 LF_SPMM_NO_SYNC = 2
+LF_SPMM_FORMAT_RESIDENT = 4
 NUM_WIDTH_CLASSES = 11
 COLMASK_BINS = 2048
 STATIC_STATS_MAX_COLS = 1 << 20
@@ -46,7 +48,7 @@ class LfHyb(C.Structure):
         ("num_parts", C.c_int32), ("num_buckets", C.c_int32),
         ("part_bucket_off", vp), ("widths", vp), ("ell_rows", vp), ("row_off", vp), ("slot_off", vp),
         ("rows", vp), ("cols", vp), ("vals", vp), ("mask", vp), ("zero_rows", vp),
-        ("num_zero_rows", C.c_int64), ("hot_bits", vp),
+        ("num_zero_rows", C.c_int64),
     ]
 
 
@@ -62,6 +64,7 @@ SIGNATURES = {
     "lf_version": (C.c_int, []),
     "lf_last_error": (C.c_char_p, []),
     "lf_set_option": (C.c_int, [C.c_int32, C.c_int32]),
+    "lf_csr_validate": (C.c_int, [vp, vp, C.c_int64, C.c_int64, C.c_int64, vp]),
     "lf_hyb_stats_workspace_bytes": (C.c_size_t, [C.c_int64, C.c_int64, C.c_int32]),
     "lf_hyb_stats": (C.c_int, [vp, vp, C.c_int64, C.c_int64, C.c_int32, vp, vp, vp, C.c_size_t, vp]),
     "lf_hyb_stats_static": (C.c_int, [vp, vp, C.c_int64, C.c_int64, C.c_int32, vp, vp, vp]),

@@ -61,13 +61,18 @@ static_assert(kLongSegMin > (1 << (kClasses - 1)), "a deferred segment must belo
 
 // A warp marks the columns of entries [lo, hi) with `bit`: four strided entries per lane and
 // step, their columns and masks loaded before the first atomic, so that the loads overlap.
+// Columns outside [0, num_cols) are skipped everywhere below (never used as an index): a
+// malformed matrix gives wrong statistics, not a stray access; lf_csr_validate reports it.
 __device__ __forceinline__ void warp_mark(const int32_t* __restrict__ indices, uint32_t* __restrict__ colmask,
-                                          int64_t lo, int64_t hi, int lane, uint32_t bit) {
+                                          int64_t lo, int64_t hi, int lane, uint32_t bit, uint32_t num_cols) {
   for (int64_t i = lo + lane; i < hi; i += 128) {
     int32_t c[4];
     uint32_t m[4];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) c[u] = i + 32 * u < hi ? indices[i + 32 * u] : -1;
+    for (int u = 0; u < 4; ++u) {
+      c[u] = i + 32 * u < hi ? indices[i + 32 * u] : -1;
+      if ((uint32_t)c[u] >= num_cols) c[u] = -1;
+    }
 #pragma unroll
     for (int u = 0; u < 4; ++u) m[u] = c[u] >= 0 ? colmask[c[u]] : bit;
 #pragma unroll
@@ -81,7 +86,7 @@ __device__ __forceinline__ void warp_mark(const int32_t* __restrict__ indices, u
 // every touched column.
 __global__ void __launch_bounds__(256)
 stats_rows_kernel(const int64_t* __restrict__ indptr, const int32_t* __restrict__ indices,
-                  int64_t num_rows, int64_t psz, int num_parts,
+                  int64_t num_rows, uint32_t num_cols, int64_t psz, int num_parts,
                   unsigned long long* __restrict__ class_stats, uint32_t* __restrict__ colmask,
                   int use_smem, unsigned int* __restrict__ long_count, LongSeg* __restrict__ long_list) {
   extern __shared__ unsigned long long s_stats[];
@@ -119,7 +124,7 @@ stats_rows_kernel(const int64_t* __restrict__ indptr, const int32_t* __restrict_
       // its left neighbour's heads a segment; segment lengths come from the ballot of heads, so
       // all segments of the row are counted and marked at once instead of one after the other.
       const int n = (int)(e - s);
-      const bool on = lane < n;
+      const bool on = lane < n && (uint32_t)c_first < num_cols;
       const int32_t c = on ? c_first : 0;
       const int p = on ? (int)((uint32_t)c / (uint32_t)psz) : -1;
       const int left = __shfl_up_sync(0xffffffffu, p, 1);
@@ -128,7 +133,7 @@ stats_rows_kernel(const int64_t* __restrict__ indptr, const int32_t* __restrict_
       int kc = 0;
       if (head) {
         const unsigned later = lane == 31 ? 0u : heads >> (lane + 1);
-        const uint32_t deg = later ? (uint32_t)__ffs(later) : (uint32_t)(n - lane);
+        const uint32_t deg = later ? (uint32_t)__ffs(later) : (uint32_t)min(n - lane, 32);
         kc = ceil_log2_u32(deg);   // deg <= 32: never beyond the widest class
         unsigned long long* a = acc + (p * kClasses + kc) * 3;
         atomicAdd(a + 0, 1ull);
@@ -148,7 +153,9 @@ stats_rows_kernel(const int64_t* __restrict__ indptr, const int32_t* __restrict_
         p = 0;
         nxt = e;
       } else {
-        p = (int)(indices[pos] / psz);
+        const int32_t c0 = indices[pos];
+        if ((uint32_t)c0 >= num_cols) { ++pos; continue; }   // malformed entry: skipped
+        p = (int)(c0 / psz);
         nxt = segment_end(indices, pos, e, (int64_t)(p + 1) * psz);
       }
       const uint32_t deg = (uint32_t)(nxt - pos);
@@ -172,7 +179,7 @@ stats_rows_kernel(const int64_t* __restrict__ indptr, const int32_t* __restrict_
           deferred = true;
         }
       }
-      if (!deferred) warp_mark(indices, colmask, pos, nxt, lane, bit);
+      if (!deferred) warp_mark(indices, colmask, pos, nxt, lane, bit, num_cols);
       pos = nxt;
     }
     r = r_next;
@@ -199,7 +206,7 @@ stats_rows_kernel(const int64_t* __restrict__ indptr, const int32_t* __restrict_
 // entries at 32 per row, 0.12 against 0.15 ms on a power-law graph of 14 entries per row.
 __global__ void __launch_bounds__(256)
 stats_rows_p1_kernel(const int64_t* __restrict__ indptr, const int32_t* __restrict__ indices, int64_t num_rows,
-                     unsigned long long* __restrict__ class_stats, uint32_t* __restrict__ colmask,
+                     uint32_t num_cols, unsigned long long* __restrict__ class_stats, uint32_t* __restrict__ colmask,
                      unsigned int* __restrict__ long_count, LongSeg* __restrict__ long_list) {
   __shared__ unsigned long long s_stats[kClasses * 3];
   for (int i = threadIdx.x; i < kClasses * 3; i += blockDim.x) s_stats[i] = 0ull;
@@ -267,6 +274,7 @@ stats_rows_p1_kernel(const int64_t* __restrict__ indptr, const int32_t* __restri
           }
           bit[u] = 1u << __shfl_sync(0xffffffffu, kc, lo);
           c[u] = i < total ? indices[first + i] : -1;
+          if ((uint32_t)c[u] >= num_cols) c[u] = -1;
         }
 #pragma unroll
         for (int u = 0; u < 4; ++u) m[u] = c[u] >= 0 ? colmask[c[u]] : 0xffffffffu;
@@ -285,7 +293,7 @@ stats_rows_p1_kernel(const int64_t* __restrict__ indptr, const int32_t* __restri
         src = __ffs(todo) - 1;
         s_cur = __shfl_sync(0xffffffffu, s, src);
         e_cur = __shfl_sync(0xffffffffu, e, src);
-        c_cur = s_cur + lane < e_cur ? indices[s_cur + lane] : 0;
+        c_cur = s_cur + lane < e_cur ? indices[s_cur + lane] : -1;
       }
       while (todo) {
         todo &= todo - 1;
@@ -296,13 +304,13 @@ stats_rows_p1_kernel(const int64_t* __restrict__ indptr, const int32_t* __restri
           src_nxt = __ffs(todo) - 1;
           s_nxt = __shfl_sync(0xffffffffu, s, src_nxt);
           e_nxt = __shfl_sync(0xffffffffu, e, src_nxt);
-          c_nxt = s_nxt + lane < e_nxt ? indices[s_nxt + lane] : 0;
+          c_nxt = s_nxt + lane < e_nxt ? indices[s_nxt + lane] : -1;
         }
         const uint32_t bit = 1u << __shfl_sync(0xffffffffu, kc, src);
         if (e_cur - s_cur <= 32) {
-          if (s_cur + lane < e_cur && !(colmask[c_cur] & bit)) atomicOr(colmask + c_cur, bit);
+          if ((uint32_t)c_cur < num_cols && !(colmask[c_cur] & bit)) atomicOr(colmask + c_cur, bit);
         } else {
-          warp_mark(indices, colmask, s_cur, e_cur, lane, bit);
+          warp_mark(indices, colmask, s_cur, e_cur, lane, bit, num_cols);
         }
         src = src_nxt;
         s_cur = s_nxt;
@@ -322,7 +330,7 @@ stats_rows_p1_kernel(const int64_t* __restrict__ indptr, const int32_t* __restri
 // rows occupies the whole grid, and thousands of listed segments cost no serial walk.
 __global__ void __launch_bounds__(256)
 stats_long_kernel(const int32_t* __restrict__ indices, const unsigned int* __restrict__ long_count,
-                  const LongSeg* __restrict__ long_list, uint32_t* __restrict__ colmask) {
+                  const LongSeg* __restrict__ long_list, uint32_t* __restrict__ colmask, uint32_t num_cols) {
   __shared__ long long s_pos[256], s_end[256];
   __shared__ int s_pre[257];
   __shared__ int s_scan[256 / 32 + 1];
@@ -359,6 +367,7 @@ stats_long_kernel(const int32_t* __restrict__ indices, const unsigned int* __res
       for (int u = 0; u < kPer; ++u) {
         const long long e = from + threadIdx.x + 256 * u;
         col[u] = e < to ? indices[e] : -1;
+        if ((uint32_t)col[u] >= num_cols) col[u] = -1;
       }
 #pragma unroll
       for (int u = 0; u < kPer; ++u) m[u] = col[u] >= 0 ? colmask[col[u]] : bit;
@@ -413,7 +422,7 @@ __device__ __forceinline__ int pick_bucket(const int32_t* __restrict__ w, int n,
 // One thread per matrix row: ELL rows it contributes to every (partition, bucket).
 __global__ void __launch_bounds__(kRowsPerBlock)
 hyb_count_kernel(const int64_t* __restrict__ indptr, const int32_t* __restrict__ indices,
-                 int64_t row_begin, int64_t row_end, int64_t psz, int num_parts,
+                 int64_t row_begin, int64_t row_end, uint32_t num_cols, int64_t psz, int num_parts,
                  const int32_t* __restrict__ pbo, const int32_t* __restrict__ widths, int ncat,
                  int32_t* __restrict__ block_counts, int32_t* __restrict__ err) {
   extern __shared__ int32_t s_cnt[];
@@ -428,7 +437,12 @@ hyb_count_kernel(const int64_t* __restrict__ indptr, const int32_t* __restrict__
       int p = 0;
       int64_t nxt = e;
       if (num_parts > 1) {
-        p = (int)(indices[pos] / psz);
+        const int32_t c0 = indices[pos];
+        if ((uint32_t)c0 >= num_cols) {   // malformed matrix: report, touch nothing
+          atomicExch(err, -1);
+          break;
+        }
+        p = (int)(c0 / psz);
         nxt = segment_end(indices, pos, e, (int64_t)(p + 1) * psz);
       }
       const int deg = (int)(nxt - pos);
@@ -653,6 +667,49 @@ row_stats_kernel(const int64_t* __restrict__ indptr, int64_t row_begin, int64_t 
   }
 }
 
+// Structural check of a CSR matrix: row pointers non-decreasing from indptr[0] >= 0, every column in
+// [0, num_cols), columns strictly ascending inside a row.  A warp takes 32 rows; rows of up to 32
+// entries are checked by one lane each, longer rows by the whole warp.  Bit 0 of *flag: bad row
+// pointer, bit 1: column out of range, bit 2: columns not strictly ascending.
+__device__ int g_csr_flag;
+
+__global__ void __launch_bounds__(256)
+csr_validate_kernel(const int64_t* __restrict__ indptr, const int32_t* __restrict__ indices, int64_t num_rows,
+                    uint32_t num_cols, int64_t nnz_bound) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int64_t n_warps = (int64_t)gridDim.x * (blockDim.x >> 5);
+  int bad = 0;
+  for (int64_t base = warp * 32; base < num_rows; base += n_warps * 32) {
+    const int64_t r = base + lane;
+    int64_t s = 0, e = 0;
+    if (r < num_rows) {
+      s = indptr[r];
+      e = indptr[r + 1];
+      if (s < 0 || e < s || e > nnz_bound) { bad |= 1; e = s; }   // a broken row is not walked
+    }
+    if (e - s <= 32) {
+      int32_t prev = -1;
+      for (int64_t i = s; i < e; ++i) {
+        const int32_t c = indices[i];
+        if ((uint32_t)c >= num_cols) bad |= 2;
+        else if (c <= prev) bad |= 4;
+        prev = c;
+      }
+    }
+    for (unsigned todo = __ballot_sync(0xffffffffu, e - s > 32); todo; todo &= todo - 1) {
+      const int src = __ffs(todo) - 1;
+      const int64_t ls = __shfl_sync(0xffffffffu, s, src), le = __shfl_sync(0xffffffffu, e, src);
+      for (int64_t i = ls + lane; i < le; i += 32) {
+        const int32_t c = indices[i];
+        if ((uint32_t)c >= num_cols) bad |= 2;
+        else if (i > ls && c <= indices[i - 1]) bad |= 4;
+      }
+    }
+  }
+  if (bad) atomicOr(&g_csr_flag, bad);
+}
+
 // ---- workspace carving ---------------------------------------------------------------------
 struct BuildWs {
   int32_t* pbo; int32_t* widths; int64_t* row_off; int64_t* slot_off; int64_t* ell_rows;
@@ -713,6 +770,9 @@ int lf_hyb_stats(const int64_t* indptr, const int32_t* indices, int64_t num_rows
   LF_REQUIRE(indptr && class_stats && colmask_hist && workspace, "null pointer argument");
   LF_REQUIRE(num_rows >= 0 && num_cols >= 1, "bad shape %lld x %lld", (long long)num_rows, (long long)num_cols);
   LF_REQUIRE(num_parts >= 1 && num_parts <= num_cols, "num_parts %d out of range", num_parts);
+  LF_REQUIRE(num_parts <= 65535, "num_parts %d exceeds the grid limit", num_parts);
+  LF_REQUIRE(num_cols < (1ll << 31), "column indices are 32-bit: %lld columns are not supported", (long long)num_cols);
+  LF_REQUIRE(num_rows == 0 || indices, "indices missing");
   if (workspace_bytes < lf_hyb_stats_workspace_bytes(num_rows, num_cols, num_parts))
     return fail(LF_ERR_WORKSPACE_TOO_SMALL, "stats workspace too small");
   cudaStream_t st = (cudaStream_t)stream;
@@ -730,25 +790,24 @@ int lf_hyb_stats(const int64_t* indptr, const int32_t* indices, int64_t num_rows
     if (num_parts == 1) {
       const int64_t want = ceil_div64(num_rows, 8 * 32);  // 8 warps per block, 32 rows per warp and step
       const int grid = (int)(want < 1 ? 1 : (want > 148 * 16 ? 148 * 16 : want));
-      stats_rows_p1_kernel<<<grid, 256, 0, st>>>(indptr, indices, num_rows, (unsigned long long*)class_stats, colmask,
-                                                 long_count, long_list);
+      stats_rows_p1_kernel<<<grid, 256, 0, st>>>(indptr, indices, num_rows, (uint32_t)num_cols,
+                                                 (unsigned long long*)class_stats, colmask, long_count, long_list);
     } else {
       const size_t smem = n_stat * sizeof(unsigned long long);
       const int use_smem = smem <= 40 * 1024;
       const int64_t want = ceil_div64(num_rows, 8 * 4);  // 8 warps per block, ~4 rows per warp
       const int grid = (int)(want < 1 ? 1 : (want > 148 * 64 ? 148 * 64 : want));
       stats_rows_kernel<<<grid, 256, use_smem ? smem : 0, st>>>(
-          indptr, indices, num_rows, psz, num_parts, (unsigned long long*)class_stats, colmask, use_smem, long_count,
-          long_list);
+          indptr, indices, num_rows, (uint32_t)num_cols, psz, num_parts, (unsigned long long*)class_stats, colmask,
+          use_smem, long_count, long_list);
     }
     LF_CUDA_CHECK(cudaGetLastError());
-    stats_long_kernel<<<148 * 4, 256, 0, st>>>(indices, long_count, long_list, colmask);
+    stats_long_kernel<<<148 * 4, 256, 0, st>>>(indices, long_count, long_list, colmask, (uint32_t)num_cols);
     LF_CUDA_CHECK(cudaGetLastError());
   }
   {
     const int64_t want = ceil_div64(psz, 256 * 8);
     dim3 grid((unsigned)(want < 1 ? 1 : (want > 1024 ? 1024 : want)), (unsigned)num_parts);
-    LF_REQUIRE(num_parts <= 65535, "num_parts %d exceeds the grid limit", num_parts);
     colmask_hist_kernel<<<grid, 256, 0, st>>>(colmask, num_cols, psz, (unsigned long long*)colmask_hist);
     LF_CUDA_CHECK(cudaGetLastError());
   }
@@ -803,6 +862,35 @@ int lf_hyb_stats_static(const int64_t* indptr, const int32_t* indices, int64_t n
                       kStaticScratchBytes, stream);
 }
 
+int lf_csr_validate(const int64_t* indptr, const int32_t* indices, int64_t num_rows, int64_t num_cols, int64_t nnz,
+                    void* stream) {
+  LF_REQUIRE(indptr && num_rows >= 0 && num_cols >= 1 && nnz >= 0, "bad arguments");
+  LF_REQUIRE(num_cols < (1ll << 31) && nnz < (1ll << 31), "more than 2^31-1 columns or stored entries are not supported");
+  LF_REQUIRE(nnz == 0 || indices, "indices missing");
+  cudaStream_t st = (cudaStream_t)stream;
+  const int zero = 0;
+  LF_CUDA_CHECK(cudaMemcpyToSymbolAsync(g_csr_flag, &zero, sizeof(int), 0, cudaMemcpyHostToDevice, st));
+  if (num_rows > 0) {
+    const int64_t want = ceil_div64(num_rows, 8 * 32);
+    csr_validate_kernel<<<(unsigned)(want > 148 * 16 ? 148 * 16 : want), 256, 0, st>>>(indptr, indices, num_rows,
+                                                                                        (uint32_t)num_cols, nnz);
+    LF_CUDA_CHECK(cudaGetLastError());
+  }
+  int flag = 0;
+  int64_t ends[2] = {0, 0};
+  LF_CUDA_CHECK(cudaMemcpyFromSymbolAsync(&flag, g_csr_flag, sizeof(int), 0, cudaMemcpyDeviceToHost, st));
+  LF_CUDA_CHECK(cudaMemcpyAsync(&ends[0], indptr, sizeof(int64_t), cudaMemcpyDeviceToHost, st));
+  LF_CUDA_CHECK(cudaMemcpyAsync(&ends[1], indptr + num_rows, sizeof(int64_t), cudaMemcpyDeviceToHost, st));
+  LF_CUDA_CHECK(cudaStreamSynchronize(st));
+  if (flag & 1) return fail(LF_ERR_INVALID_ARGUMENT, "row pointers are negative, decreasing or beyond the number of stored entries");
+  if (ends[0] != 0 || ends[1] != nnz)
+    return fail(LF_ERR_INVALID_ARGUMENT, "row pointers run from %lld to %lld, expected 0 to %lld", (long long)ends[0],
+                (long long)ends[1], (long long)nnz);
+  if (flag & 2) return fail(LF_ERR_INVALID_ARGUMENT, "a column index lies outside [0, %lld)", (long long)num_cols);
+  if (flag & 4) return fail(LF_ERR_INVALID_ARGUMENT, "column indices are not strictly ascending inside a row (sort and merge duplicates first)");
+  return LF_OK;
+}
+
 int64_t lf_row_stats_blocks(int64_t row_begin, int64_t row_end) {
   return row_end > row_begin ? ceil_div64(row_end - row_begin, kRowsPerBlock) : 0;
 }
@@ -834,7 +922,7 @@ int lf_hyb_plan(const int64_t* indptr, const int32_t* indices, int64_t num_rows,
                 size_t workspace_bytes, void* stream) {
   LF_REQUIRE(indptr && part_bucket_off && ell_rows && row_off && slot_off && num_zero_rows && workspace,
              "null pointer argument");
-  LF_REQUIRE(num_cols >= 1 && 0 <= row_begin && row_begin <= row_end && row_end <= num_rows,
+  LF_REQUIRE(num_cols >= 1 && num_cols < (1ll << 31) && 0 <= row_begin && row_begin <= row_end && row_end <= num_rows,
              "bad shape or row range");
   if (int s = check_widths(num_parts, part_bucket_off, widths)) return s;
   LF_REQUIRE(num_parts <= num_cols, "num_parts %d exceeds the number of columns", num_parts);
@@ -853,7 +941,8 @@ int lf_hyb_plan(const int64_t* indptr, const int32_t* indices, int64_t num_rows,
   if (nb) LF_CUDA_CHECK(cudaMemcpyAsync(ws.widths, widths, sizeof(int32_t) * nb, cudaMemcpyHostToDevice, st));
   LF_CUDA_CHECK(cudaMemsetAsync(ws.err, 0, sizeof(int32_t) * 4, st));
   hyb_count_kernel<<<(unsigned)blocks, kRowsPerBlock, sizeof(int32_t) * ncat, st>>>(
-      indptr, indices, row_begin, row_end, psz, num_parts, ws.pbo, ws.widths, ncat, ws.block_counts, ws.err);
+      indptr, indices, row_begin, row_end, (uint32_t)num_cols, psz, num_parts, ws.pbo, ws.widths, ncat,
+      ws.block_counts, ws.err);
   LF_CUDA_CHECK(cudaGetLastError());
   scan_blocks_kernel<<<ncat, 256, 0, st>>>(ws.block_counts, blocks, ncat, ws.block_offsets, ws.totals);
   LF_CUDA_CHECK(cudaGetLastError());
@@ -871,6 +960,8 @@ int lf_hyb_plan(const int64_t* indptr, const int32_t* indices, int64_t num_rows,
   int status = LF_OK;
   if (ce != cudaSuccess) {
     status = fail(LF_ERR_CUDA, "lf_hyb_plan: %s", cudaGetErrorString(ce));
+  } else if (h_err < 0) {
+    status = fail(LF_ERR_INVALID_ARGUMENT, "the matrix holds a column index outside [0, %lld)", (long long)num_cols);
   } else if (h_err) {
     status = fail(LF_ERR_INVALID_ARGUMENT, "partition %d holds entries but was given no bucket width", h_err - 1);
   } else if (h_ptr[1] > 0x7fffffffll) {

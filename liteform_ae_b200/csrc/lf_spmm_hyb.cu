@@ -19,7 +19,9 @@
 //     U gathers are issued back to back before any FMA consumes them;
 //   * the kernel is specialised on min(width, 8): a row id is compared only where an ELL row can
 //     start, so buckets of width >= 8 pay one check per 8 gathers;
-//   * padded slots (val == 0) issue no gather;
+//   * padded slots issue no gather.  Padding is recognised by its stored value 0 (the builder writes
+//     exact zeros there); a stored ENTRY whose value is exactly 0 is skipped the same way, so
+//     0 * Inf and 0 * NaN from B do not reach C (SciPy would produce NaN there);
 //   * variants of the same code: B in bf16 (8 features per lane), and a broadcasting epilogue that
 //     stores every row into several full-size C matrices (the GPUs of a group) at once.
 #include "lf_bsr8_tma.cuh"
@@ -34,17 +36,23 @@ struct BucketDesc {
   int64_t row_off;        // first element of this bucket in the rows arena
   int64_t slot_off;       // first element in the cols / vals arenas
   int64_t ell_rows;       // R
-  int64_t tile_begin;     // first thread block of this bucket
+  int64_t tile_begin;     // bucket-major order: first thread block of this bucket;
+                          // interleaved order: first thread block of this bucket inside a segment
   int32_t wlog;           // log2(width)
   int32_t rows_per_group; // ELL rows one group walks
   int32_t force_atomic;   // every flush of this bucket must be an atomic add
-  int32_t pad_;
+  int32_t tiles_per_seg;  // interleaved order: thread blocks of this bucket per segment
 };
 
+// Order of the thread blocks.  Bucket-major (seg_tiles == 0): all thread blocks of bucket 0, then
+// bucket 1, ...  Interleaved (seg_tiles > 0): every bucket is cut into the same number of
+// segments (consecutive ELL rows, hence consecutive matrix rows) and the launch runs segment 0 of
+// all buckets, then segment 1, ...: thread blocks that are resident together then work on the
+// same stretch of matrix rows in every bucket.
 template <int MAXB>
 struct SpmmTable {
   int32_t n;
-  int32_t pad_;
+  int32_t seg_tiles;      // thread blocks per segment over all buckets (0 = bucket-major)
   BucketDesc b[MAXB];
 };
 
@@ -60,28 +68,18 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
-// L2 eviction policies (sm_80+ createpolicy): B rows are the only data with reuse, everything
-// else (slots, row ids, C) streams through once.
-__device__ __forceinline__ uint64_t l2_policy_evict_last() {
-  uint64_t p;
-  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
-  return p;
-}
-__device__ __forceinline__ uint64_t l2_policy_evict_first() {
-  uint64_t p;
-  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
-  return p;
-}
+// Programmatic dependent launch: the product kernel is launched while the launch that clears
+// rows is still running; everything up to this point (bucket look-up, first loads) overlaps with
+// it, and nothing is written to C before the clearing launch has completed and flushed.  Without
+// a programmatic dependency the instruction returns at once.
+__device__ __forceinline__ void wait_for_prior_grid() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void let_dependents_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 template <int VEC> struct Chunk;
 template <> struct Chunk<4> {
   float4 v;
   __device__ __forceinline__ void zero() { v = make_float4(0.f, 0.f, 0.f, 0.f); }
   __device__ __forceinline__ void load(const float* p) { v = __ldg(reinterpret_cast<const float4*>(p)); }
-  __device__ __forceinline__ void load_keep(const float* p, uint64_t pol) {
-    asm volatile("ld.global.nc.L2::cache_hint.v4.f32 {%0, %1, %2, %3}, [%4], %5;"
-                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p), "l"(pol));
-  }
   __device__ __forceinline__ void store_stream(float* p) const { __stcs(reinterpret_cast<float4*>(p), v); }
   __device__ __forceinline__ void fma(float a, const Chunk& x) {
     v.x = fmaf(a, x.v.x, v.x); v.y = fmaf(a, x.v.y, v.y); v.z = fmaf(a, x.v.z, v.z); v.w = fmaf(a, x.v.w, v.w);
@@ -93,9 +91,6 @@ template <> struct Chunk<1> {
   float v;
   __device__ __forceinline__ void zero() { v = 0.f; }
   __device__ __forceinline__ void load(const float* p) { v = __ldg(p); }
-  __device__ __forceinline__ void load_keep(const float* p, uint64_t pol) {
-    asm volatile("ld.global.nc.L2::cache_hint.f32 %0, [%1], %2;" : "=f"(v) : "l"(p), "l"(pol));
-  }
   __device__ __forceinline__ void store_stream(float* p) const { __stcs(p, v); }
   __device__ __forceinline__ void fma(float a, const Chunk& x) { v = fmaf(a, x.v, v); }
   __device__ __forceinline__ void store(float* p) const { *p = v; }
@@ -127,10 +122,6 @@ struct RawBf16x8 {
   uint4 v;
   __device__ __forceinline__ void zero() { v = make_uint4(0u, 0u, 0u, 0u); }
   __device__ __forceinline__ void load(const uint16_t* p) { v = __ldg(reinterpret_cast<const uint4*>(p)); }
-  __device__ __forceinline__ void load_keep(const uint16_t* p, uint64_t pol) {
-    asm volatile("ld.global.nc.L2::cache_hint.v4.u32 {%0, %1, %2, %3}, [%4], %5;"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p), "l"(pol));
-  }
 };
 // element type of B and the register image of one gathered chunk, per VEC
 template <int VEC> struct BTraits { using elem = float; using raw = Chunk<VEC>; };
@@ -152,7 +143,7 @@ __device__ __forceinline__ void chunk_fma(Chunk<8>& acc, float a, const RawBf16x
 //   WC = min(bucket width, 8): ELL rows start every WC slots at the earliest, so the row id has to
 //        be looked at only there (once per batch of 8 gathers when the bucket is 8 or wider).
 //   POL selects cache behaviour: 0 = default loads/stores; 1 = slots, row ids and C use streaming
-//        (evict-first) accesses; 2 = as 1, and B rows are loaded with an L2 evict-last policy.
+//        (evict-first) accesses, so that B rows -- the only data with reuse -- keep the L2.
 // The group stages G (column, value) pairs and row ids in shared memory with one coalesced load
 // each, then broadcasts a pair per gather with a single 64-bit shared load.
 template <int G, int V, int VEC, int WC, int POL, bool MD>
@@ -161,7 +152,7 @@ __device__ __forceinline__ void walk_slots(const int32_t* __restrict__ rows, con
                                            int64_t ell_rows, bool all_open,
                                            const typename BTraits<VEC>::elem* __restrict__ B, int ldb, float* __restrict__ C, int64_t ldc, int N,
                                            int64_t row_base, int lane, unsigned gmask, int2* cv, int* rd,
-                                           const uint32_t* __restrict__ hot, const DestList& dl) {
+                                           const DestList& dl) {
   constexpr int U = V == 1 ? 8 : (V == 2 ? 4 : 2);  // gathers in flight per lane (x V chunks)
   static_assert(G % U == 0 && 8 % U == 0, "unroll must divide the group size and the batch");
   const int first_row = rows[e0], last_row = rows[e1 - 1];
@@ -178,11 +169,7 @@ __device__ __forceinline__ void walk_slots(const int32_t* __restrict__ rows, con
     acc[v].zero();
   }
   int cur = first_row;
-  uint64_t keep = 0, drop = 0;
-  if (POL == 2) {
-    keep = l2_policy_evict_last();
-    drop = hot ? l2_policy_evict_first() : keep;
-  }
+  wait_for_prior_grid();   // no store or atomic to C before the row-clearing launch is complete
 
   auto flush = [&](int row) {
     const bool open = all_open || (row == first_row && head_open) || (row == last_row && tail_open);
@@ -222,8 +209,6 @@ __device__ __forceinline__ void walk_slots(const int32_t* __restrict__ rows, con
     const int my_col = POL >= 1 ? __ldcs(cols + cidx) : cols[cidx];
     const float my_val = in ? (POL >= 1 ? __ldcs(vals + cidx) : vals[cidx]) : 0.f;
     const int my_rid = rows[cidx >> wlog];
-    uint32_t hot_word = 0xffffffffu;   // bit k: slot s + k gathers a frequently used row of B
-    if (POL == 2 && hot) hot_word = __ldg(hot + (s >> 5)) >> (int)(s & 31);
     __syncwarp(gmask);  // the previous strip has been consumed by every lane of the group
     cv[lane] = make_int2(my_col, __float_as_int(my_val));
     rd[lane] = my_rid;
@@ -239,12 +224,8 @@ __device__ __forceinline__ void walk_slots(const int32_t* __restrict__ rows, con
         const typename BTraits<VEC>::elem* src = Bf + (int64_t)p.x * ldb;
 #pragma unroll
         for (int v = 0; v < V; ++v) {
-          if (val[u] != 0.f && active[v]) {
-            if (POL == 2) b[u][v].load_keep(src + v * G * VEC, ((hot_word >> (t + u)) & 1u) ? keep : drop);
-            else b[u][v].load(src + v * G * VEC);
-          } else {
-            b[u][v].zero();
-          }
+          if (val[u] != 0.f && active[v]) b[u][v].load(src + v * G * VEC);
+          else b[u][v].zero();
         }
       }
 #pragma unroll
@@ -271,23 +252,29 @@ __global__ void __launch_bounds__(kThreads, MINB)
 spmm_hyb_kernel(const __grid_constant__ SpmmTable<MAXB> tbl, const int32_t* __restrict__ rows_arena,
                 const int32_t* __restrict__ cols_arena, const float* __restrict__ vals_arena,
                 const typename BTraits<VEC>::elem* __restrict__ B, int ldb, float* __restrict__ C, int64_t ldc,
-                int N, int64_t row_base, const uint32_t* __restrict__ hot_arena,
-                const __grid_constant__ DestList dests) {
+                int N, int64_t row_base, const __grid_constant__ DestList dests) {
   constexpr int GPC = kThreads / G;  // groups per thread block
   __shared__ int2 s_cv[kThreads];
   __shared__ int s_rd[kThreads];
 
-  const int64_t tile = blockIdx.x;
+  int64_t tile = blockIdx.x;   // position of this thread block inside its bucket, once found
+  int64_t key = tile;
+  uint32_t seg = 0;
+  if (tbl.seg_tiles > 0) {
+    seg = (uint32_t)blockIdx.x / (uint32_t)tbl.seg_tiles;
+    key = (uint32_t)blockIdx.x - seg * (uint32_t)tbl.seg_tiles;
+  }
   int lo = 0, hi = tbl.n;
   while (hi - lo > 1) {
     const int mid = (lo + hi) >> 1;
-    if (tbl.b[mid].tile_begin <= tile) lo = mid; else hi = mid;
+    if (tbl.b[mid].tile_begin <= key) lo = mid; else hi = mid;
   }
   const BucketDesc& d = tbl.b[lo];
+  tile = tbl.seg_tiles > 0 ? (int64_t)seg * d.tiles_per_seg + (key - d.tile_begin) : key - d.tile_begin;
   const int wlog = d.wlog;
   const int g = threadIdx.x / G, lane = threadIdx.x % G;
   const unsigned gmask = G == 32 ? 0xffffffffu : (((1u << G) - 1u) << ((threadIdx.x & 31) / G * G));
-  const int64_t e0 = ((tile - d.tile_begin) * GPC + g) * (int64_t)d.rows_per_group;
+  const int64_t e0 = (tile * GPC + g) * (int64_t)d.rows_per_group;
   if (e0 >= d.ell_rows) return;
   const int64_t e1 = min(e0 + d.rows_per_group, d.ell_rows);
   const int32_t* __restrict__ rows = rows_arena + d.row_off;
@@ -296,10 +283,9 @@ spmm_hyb_kernel(const __grid_constant__ SpmmTable<MAXB> tbl, const int32_t* __re
   const bool all_open = d.force_atomic != 0;
   int2* cv = s_cv + g * G;
   int* rd = s_rd + g * G;
-  const uint32_t* hot = hot_arena ? hot_arena + (d.slot_off >> 5) : nullptr;
 #define LF_WALK(WC_)                                                                                     \
   walk_slots<G, V, VEC, WC_, POL, MD>(rows, cols, vals, wlog, e0, e1, d.ell_rows, all_open, B, ldb, C, ldc, \
-                                  N, row_base, lane, gmask, cv, rd, hot, dests)
+                                  N, row_base, lane, gmask, cv, rd, dests)
   switch (wlog) {
     case 0: LF_WALK(1); break;
     case 1: LF_WALK(2); break;
@@ -314,6 +300,7 @@ template <int VEC>
 __global__ void __launch_bounds__(kThreads)
 zero_rows_kernel(const int32_t* __restrict__ zero_rows, int64_t n, float* __restrict__ C, int64_t ldc,
                  int N, int64_t row_base) {
+  let_dependents_launch();   // the product kernel may become resident; it waits before touching C
   const int lane = threadIdx.x & 31;
   const int64_t warp = (int64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
   const int64_t n_warps = (int64_t)gridDim.x * (kThreads / 32);
@@ -331,6 +318,7 @@ zero_rows_kernel(const int32_t* __restrict__ zero_rows, int64_t n, float* __rest
 __global__ void __launch_bounds__(kThreads)
 zero_rows_multi_kernel(const int32_t* __restrict__ zero_rows, int64_t n, const __grid_constant__ DestList dests,
                        int64_t ldc, int N) {
+  let_dependents_launch();
   const int lane = threadIdx.x & 31;
   const int64_t warp = (int64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
   const int64_t n_warps = (int64_t)gridDim.x * (kThreads / 32);
@@ -349,33 +337,46 @@ zero_rows_multi_kernel(const int32_t* __restrict__ zero_rows, int64_t n, const _
 // together.  A row that lies inside one group's range is written with a plain store; a row cut
 // by a range boundary is accumulated with vector atomics after csr_prepare_kernel cleared it.
 // ---------------------------------------------------------------------------------------------
+// One warp per candidate: lane 0 decides which rows (at most two) have to be cleared, the warp
+// clears them with coalesced (128-bit when VEC == 4) stores.
+template <int VEC>
 __global__ void __launch_bounds__(256)
 csr_prepare_kernel(const int64_t* __restrict__ indptr, int64_t row_begin, int64_t row_end, int64_t spg,
                    float* __restrict__ C, int64_t ldc, int N) {
+  let_dependents_launch();
+  const int lane = threadIdx.x & 31;
   const int64_t rows = row_end - row_begin;
   const int64_t base = indptr[row_begin];
   const int64_t total = indptr[row_end] - base;
   const int64_t groups = (total + spg - 1) / spg;
   const int64_t n = rows > groups ? rows : groups;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
-    int64_t zero_row = -1;
-    if (i < rows && indptr[row_begin + i] == indptr[row_begin + i + 1]) zero_row = i;   // empty row
-    if (zero_row >= 0) {
-      float* dst = C + zero_row * ldc;
-      for (int f = 0; f < N; ++f) dst[f] = 0.f;
+  const int64_t n_warps = (int64_t)gridDim.x * (blockDim.x >> 5);
+  auto clear = [&](int64_t row) {
+    float* dst = C + row * ldc;
+    if (VEC == 4) {
+      for (int f = lane * 4; f < N; f += 128) *reinterpret_cast<float4*>(dst + f) = make_float4(0.f, 0.f, 0.f, 0.f);
+    } else {
+      for (int f = lane; f < N; f += 32) dst[f] = 0.f;
     }
-    if (i >= 1 && i < groups) {   // the row that contains the first entry of group i, if it started earlier
-      const int64_t x = base + i * spg;
-      int64_t lo = row_begin, hi = row_end;   // indptr[lo] <= x, answer in [lo, hi)
-      while (hi - lo > 1) {
-        const int64_t mid = (lo + hi) >> 1;
-        if (indptr[mid] <= x) lo = mid; else hi = mid;
-      }
-      if (indptr[lo] < x) {
-        float* dst = C + (lo - row_begin) * ldc;
-        for (int f = 0; f < N; ++f) dst[f] = 0.f;
+  };
+  for (int64_t i = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); i < n; i += n_warps) {
+    int64_t empty_row = -1, cut_row = -1;
+    if (lane == 0) {
+      if (i < rows && indptr[row_begin + i] == indptr[row_begin + i + 1]) empty_row = i;
+      if (i >= 1 && i < groups) {   // the row that contains the first entry of group i, if it started earlier
+        const int64_t x = base + i * spg;
+        int64_t lo = row_begin, hi = row_end;   // indptr[lo] <= x, answer in [lo, hi)
+        while (hi - lo > 1) {
+          const int64_t mid = (lo + hi) >> 1;
+          if (indptr[mid] <= x) lo = mid; else hi = mid;
+        }
+        if (indptr[lo] < x) cut_row = lo - row_begin;
       }
     }
+    empty_row = __shfl_sync(0xffffffffu, empty_row, 0);
+    cut_row = __shfl_sync(0xffffffffu, cut_row, 0);
+    if (empty_row >= 0) clear(empty_row);
+    if (cut_row >= 0) clear(cut_row);
   }
 }
 
@@ -446,6 +447,7 @@ spmm_csr_kernel(const int64_t* __restrict__ indptr, const int32_t* __restrict__ 
   };
 
   const float* __restrict__ Bf = B + f0;
+  wait_for_prior_grid();   // csr_prepare_kernel has cleared the rows that receive atomics
   for (int64_t s = s0; s < s1; s += G) {
     const int64_t idx = s + lane;
     const bool in = idx < s1;
@@ -488,6 +490,24 @@ spmm_csr_kernel(const int64_t* __restrict__ indptr, const int32_t* __restrict__ 
 }
 
 struct FeatCfg { int G, V, VEC, pass; };
+
+// Kernel launch with, optionally, a programmatic dependency on the previous kernel of the stream
+// (the row-clearing launch): the product kernel may start before that kernel has finished and
+// orders itself with griddepcontrol.wait.
+template <typename... Params, typename... Args>
+cudaError_t launch_dep(void (*kernel)(Params...), dim3 grid, int threads, cudaStream_t st, bool dependent, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3((unsigned)threads);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = dependent ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<Params>(args)...);
+}
 
 FeatCfg pick_cfg(const void* B, int64_t ldb, const void* C, int64_t ldc, int N) {
   const bool vec = (N % 4 == 0) && (ldb % 4 == 0) && (ldc % 4 == 0) && ((uintptr_t)B % 16 == 0) &&
@@ -550,6 +570,16 @@ int sm_count() {
   return cached[dev];
 }
 
+int g_tile_segments = -1;   // 0 = bucket-major order, S > 0 = interleaved over S segments
+int tile_segments() {
+  if (g_tile_segments < 0) {
+    const char* e = getenv("LF_SPMM_TILE_SEGMENTS");
+    const int v = e ? atoi(e) : 0;
+    g_tile_segments = (v >= 0 && v <= 4096) ? v : 0;
+  }
+  return g_tile_segments;
+}
+
 int g_min_blocks = 0;
 int min_blocks() {
   if (!g_min_blocks) {
@@ -564,35 +594,34 @@ int cache_policy() {
   if (g_cache_policy < 0) {
     const char* e = getenv("LF_SPMM_POLICY");
     const int v = e ? atoi(e) : 1;
-    g_cache_policy = (v >= 0 && v <= 2) ? v : 1;
+    g_cache_policy = (v >= 0 && v <= 1) ? v : 1;
   }
   return g_cache_policy;
 }
 
 template <int MAXB>
 int launch_hyb_bf16(const SpmmTable<MAXB>& tbl, int64_t tiles, const lf_hyb* A, const uint16_t* B, int64_t ldb,
-                    float* C, int64_t ldc, int N, FeatCfg cfg, cudaStream_t st, const DestList& dests) {
+                    float* C, int64_t ldc, int N, FeatCfg cfg, cudaStream_t st, const DestList& dests, bool dep) {
   dim3 grid((unsigned)tiles, (unsigned)((N + cfg.pass - 1) / cfg.pass));
-#define LF_LAUNCH(G_, V_)                                                                        \
-  spmm_hyb_kernel<G_, V_, 8, MAXB, 1, 3, false><<<grid, kThreads, 0, st>>>(                      \
-      tbl, A->rows, A->cols, A->vals, B, (int)ldb, C, ldc, N, A->row_begin, A->hot_bits, dests)
+#define LF_LAUNCH(G_, V_)                                                                                   \
+  LF_CUDA_CHECK(launch_dep(spmm_hyb_kernel<G_, V_, 8, MAXB, 1, 3, false>, grid, kThreads, st, dep, tbl, A->rows, \
+                           A->cols, A->vals, B, (int)ldb, C, ldc, N, A->row_begin, dests))
   if (cfg.G == 8) LF_LAUNCH(8, 1);
   else if (cfg.G == 16) LF_LAUNCH(16, 1);
   else if (cfg.V == 1) LF_LAUNCH(32, 1);
   else LF_LAUNCH(32, 2);
 #undef LF_LAUNCH
-  LF_CUDA_CHECK(cudaGetLastError());
   return LF_OK;
 }
 
 template <int MAXB, int POL, int MINB, bool MD>
 int launch_hyb_pol(const SpmmTable<MAXB>& tbl, int64_t tiles, const lf_hyb* A, const float* B, int64_t ldb,
-                   float* C, int64_t ldc, int N, FeatCfg cfg, cudaStream_t st, const DestList& dests) {
+                   float* C, int64_t ldc, int N, FeatCfg cfg, cudaStream_t st, const DestList& dests, bool dep) {
   const int64_t row_base = MD ? 0 : A->row_begin;
   dim3 grid((unsigned)tiles, (unsigned)((N + cfg.pass - 1) / cfg.pass));
-#define LF_LAUNCH(G_, V_, VEC_)                                                                          \
-  spmm_hyb_kernel<G_, V_, VEC_, MAXB, POL, MINB, MD><<<grid, kThreads, 0, st>>>(                              \
-      tbl, A->rows, A->cols, A->vals, B, (int)ldb, C, ldc, N, row_base, A->hot_bits, dests)
+#define LF_LAUNCH(G_, V_, VEC_)                                                                               \
+  LF_CUDA_CHECK(launch_dep(spmm_hyb_kernel<G_, V_, VEC_, MAXB, POL, MINB, MD>, grid, kThreads, st, dep, tbl,   \
+                           A->rows, A->cols, A->vals, B, (int)ldb, C, ldc, N, row_base, dests))
   if (cfg.VEC == 4) {
     if (cfg.G == 8) LF_LAUNCH(8, 1, 4);
     else if (cfg.G == 16) LF_LAUNCH(16, 1, 4);
@@ -605,23 +634,21 @@ int launch_hyb_pol(const SpmmTable<MAXB>& tbl, int64_t tiles, const lf_hyb* A, c
     else LF_LAUNCH(32, 4, 1);
   }
 #undef LF_LAUNCH
-  LF_CUDA_CHECK(cudaGetLastError());
   return LF_OK;
 }
 
 template <int MAXB>
 int launch_hyb(const SpmmTable<MAXB>& tbl, int64_t tiles, const lf_hyb* A, const void* Bv, int64_t ldb,
-               float* C, int64_t ldc, int N, FeatCfg cfg, cudaStream_t st, const DestList& dests) {
+               float* C, int64_t ldc, int N, FeatCfg cfg, cudaStream_t st, const DestList& dests, bool dep) {
   if (cfg.VEC == 8)   // bf16 B: one compiled variant per feature layout
-    return launch_hyb_bf16<MAXB>(tbl, tiles, A, (const uint16_t*)Bv, ldb, C, ldc, N, cfg, st, dests);
+    return launch_hyb_bf16<MAXB>(tbl, tiles, A, (const uint16_t*)Bv, ldb, C, ldc, N, cfg, st, dests, dep);
   const float* B = (const float*)Bv;
   if (dests.n > 0)   // broadcasting launch: one compiled variant
-    return launch_hyb_pol<MAXB, 1, 3, true>(tbl, tiles, A, B, ldb, C, ldc, N, cfg, st, dests);
+    return launch_hyb_pol<MAXB, 1, 3, true>(tbl, tiles, A, B, ldb, C, ldc, N, cfg, st, dests, dep);
   const int pol = cache_policy(), minb = min_blocks();
-#define LF_CASE(P_, M_) if (pol == P_ && minb == M_) return launch_hyb_pol<MAXB, P_, M_, false>(tbl, tiles, A, B, ldb, C, ldc, N, cfg, st, dests)
+#define LF_CASE(P_, M_) if (pol == P_ && minb == M_) return launch_hyb_pol<MAXB, P_, M_, false>(tbl, tiles, A, B, ldb, C, ldc, N, cfg, st, dests, dep)
   LF_CASE(0, 2); LF_CASE(0, 3); LF_CASE(0, 4);
   LF_CASE(1, 2); LF_CASE(1, 3); LF_CASE(1, 4);
-  LF_CASE(2, 2); LF_CASE(2, 3); LF_CASE(2, 4);
 #undef LF_CASE
   return fail(LF_ERR_INVALID_ARGUMENT, "bad tuning state");
 }
@@ -655,12 +682,16 @@ int lf_set_option(int32_t option, int32_t value) {
       g_slots_per_group = value;
       return LF_OK;
     case LF_OPT_SPMM_CACHE_POLICY:
-      LF_REQUIRE(value >= 0 && value <= 2, "cache policy %d out of range", value);
+      LF_REQUIRE(value >= 0 && value <= 1, "cache policy %d out of range", value);
       g_cache_policy = value;
       return LF_OK;
     case LF_OPT_SPMM_MIN_BLOCKS:
       LF_REQUIRE(value >= 2 && value <= 4, "min blocks %d out of range", value);
       g_min_blocks = value;
+      return LF_OK;
+    case LF_OPT_SPMM_TILE_SEGMENTS:
+      LF_REQUIRE(value >= 0 && value <= 4096, "segment count %d out of range", value);
+      g_tile_segments = value;
       return LF_OK;
     case LF_OPT_BSR_COPY_ENGINE:
       LF_REQUIRE(value >= 0 && value <= 3, "copy engine %d out of range", value);
@@ -726,6 +757,7 @@ static int spmm_hyb_impl(const lf_hyb* A, const void* B, bool b_is_bf16, int64_t
   const FeatCfg cfg = b_is_bf16 ? pick_cfg_bf16(N) : pick_cfg(B, ldb, C, ldc, N);
   const bool accumulate = flags == LF_SPMM_ACCUMULATE;
   const bool all_atomic = accumulate || A->num_parts > 1;
+  bool cleared_by_kernel = false;   // a row-clearing launch precedes: the product depends on it programmatically
 
   if (dests.n > 0) {
     if (A->num_parts > 1) {
@@ -738,6 +770,7 @@ static int spmm_hyb_impl(const lf_hyb* A, const void* B, bool b_is_bf16, int64_t
       const int grid = (int)(want > 148 * 16 ? 148 * 16 : want);
       zero_rows_multi_kernel<<<grid, kThreads, 0, st>>>(A->zero_rows, A->num_zero_rows, dests, ldc, N);
       LF_CUDA_CHECK(cudaGetLastError());
+      cleared_by_kernel = true;
     }
   } else if (!accumulate) {
     if (A->num_parts > 1) {
@@ -751,6 +784,7 @@ static int spmm_hyb_impl(const lf_hyb* A, const void* B, bool b_is_bf16, int64_t
       else
         zero_rows_kernel<1><<<grid, kThreads, 0, st>>>(A->zero_rows, A->num_zero_rows, C, ldc, N, A->row_begin);
       LF_CUDA_CHECK(cudaGetLastError());
+      cleared_by_kernel = true;
     }
   }
 
@@ -769,12 +803,12 @@ static int spmm_hyb_impl(const lf_hyb* A, const void* B, bool b_is_bf16, int64_t
       if (t >= want_tiles) break;
     }
   }
+  const int segs = tile_segments();
   int i = 0;
   while (i < A->num_buckets) {
     static thread_local SpmmTable<LF_MAX_BUCKETS_PER_LAUNCH> big;
-    SpmmTable<16> small;
     int n = 0;
-    int64_t tiles = 0;
+    int64_t tiles = 0, seg_tiles = 0;
     for (; i < A->num_buckets && n < LF_MAX_BUCKETS_PER_LAUNCH; ++i) {
       if (A->ell_rows[i] == 0) continue;
       BucketDesc d;
@@ -783,27 +817,35 @@ static int spmm_hyb_impl(const lf_hyb* A, const void* B, bool b_is_bf16, int64_t
       d.row_off = A->row_off[i];
       d.slot_off = A->slot_off[i];
       d.ell_rows = A->ell_rows[i];
-      d.tile_begin = tiles;
       d.wlog = wlog;
       d.rows_per_group = (spg >> wlog) > 0 ? (spg >> wlog) : 1;
       d.force_atomic = all_atomic ? 1 : 0;
-      d.pad_ = 0;
-      tiles += ceil_div64(d.ell_rows, (int64_t)d.rows_per_group * gpc);
+      const int64_t my_tiles = ceil_div64(d.ell_rows, (int64_t)d.rows_per_group * gpc);
+      const int64_t per_seg = segs > 0 ? ceil_div64(my_tiles, segs) : 0;
+      d.tile_begin = segs > 0 ? seg_tiles : tiles;
+      d.tiles_per_seg = (int32_t)per_seg;
+      tiles += my_tiles;
+      seg_tiles += per_seg;
       big.b[n] = d;
-      if (n < 16) small.b[n] = d;
       ++n;
     }
     if (n == 0) break;
-    LF_REQUIRE(tiles < (1ll << 31), "too many thread blocks for one launch");
+    const int64_t grid_tiles = segs > 0 ? seg_tiles * segs : tiles;   // interleaved: a few idle thread blocks at bucket ends
+    LF_REQUIRE(grid_tiles < (1ll << 31) && seg_tiles < (1ll << 31), "too many thread blocks for one launch");
     int s;
     if (n <= 16) {
-      small.n = n; small.pad_ = 0;
-      s = launch_hyb<16>(small, tiles, A, B, ldb, C, ldc, N, cfg, st, dests);
+      SpmmTable<16> small;
+      small.n = n;
+      small.seg_tiles = (int32_t)(segs > 0 ? seg_tiles : 0);
+      for (int k = 0; k < n; ++k) small.b[k] = big.b[k];
+      s = launch_hyb<16>(small, grid_tiles, A, B, ldb, C, ldc, N, cfg, st, dests, cleared_by_kernel);
     } else {
-      big.n = n; big.pad_ = 0;
-      s = launch_hyb<LF_MAX_BUCKETS_PER_LAUNCH>(big, tiles, A, B, ldb, C, ldc, N, cfg, st, dests);
+      big.n = n;
+      big.seg_tiles = (int32_t)(segs > 0 ? seg_tiles : 0);
+      s = launch_hyb<LF_MAX_BUCKETS_PER_LAUNCH>(big, grid_tiles, A, B, ldb, C, ldc, N, cfg, st, dests, cleared_by_kernel);
     }
     if (s) return s;
+    cleared_by_kernel = false;   // a further launch follows a product kernel, not the clearing one
   }
   return LF_OK;
 }
@@ -833,8 +875,9 @@ int lf_spmm_hyb_f32_host(const lf_hyb* A, const float* B, float* C, int32_t N, i
                          void* device_workspace, size_t workspace_bytes, void* stream) {
   if (int s = check_hyb(A)) return s;
   LF_REQUIRE(B && C && N >= 1 && device_workspace, "bad arguments");
-  LF_REQUIRE((flags & ~(LF_SPMM_ACCUMULATE | LF_SPMM_NO_SYNC)) == 0, "unknown flags %d", flags);
+  LF_REQUIRE((flags & ~(LF_SPMM_ACCUMULATE | LF_SPMM_NO_SYNC | LF_SPMM_FORMAT_RESIDENT)) == 0, "unknown flags %d", flags);
   const bool accumulate = (flags & LF_SPMM_ACCUMULATE) != 0;
+  const bool upload_format = (flags & LF_SPMM_FORMAT_RESIDENT) == 0;
   size_t off[7];
   if (workspace_bytes < host_ws_layout(A, N, off)) return fail(LF_ERR_WORKSPACE_TOO_SMALL, "host-call workspace too small");
   cudaStream_t st = (cudaStream_t)stream;
@@ -842,12 +885,14 @@ int lf_spmm_hyb_f32_host(const lf_hyb* A, const float* B, float* C, int32_t N, i
   const int nb = A->num_buckets;
   const size_t n_rows = (size_t)A->row_off[nb], n_slots = (size_t)A->slot_off[nb];
   const size_t c_bytes = (size_t)(A->row_end - A->row_begin) * N * 4;
-  if (n_rows) LF_CUDA_CHECK(cudaMemcpyAsync(ws + off[0], A->rows, n_rows * 4, cudaMemcpyHostToDevice, st));
-  if (n_slots) {
-    LF_CUDA_CHECK(cudaMemcpyAsync(ws + off[1], A->cols, n_slots * 4, cudaMemcpyHostToDevice, st));
-    LF_CUDA_CHECK(cudaMemcpyAsync(ws + off[2], A->vals, n_slots * 4, cudaMemcpyHostToDevice, st));
+  if (upload_format) {   // otherwise the workspace still holds this format from an earlier call
+    if (n_rows) LF_CUDA_CHECK(cudaMemcpyAsync(ws + off[0], A->rows, n_rows * 4, cudaMemcpyHostToDevice, st));
+    if (n_slots) {
+      LF_CUDA_CHECK(cudaMemcpyAsync(ws + off[1], A->cols, n_slots * 4, cudaMemcpyHostToDevice, st));
+      LF_CUDA_CHECK(cudaMemcpyAsync(ws + off[2], A->vals, n_slots * 4, cudaMemcpyHostToDevice, st));
+    }
+    if (A->num_zero_rows) LF_CUDA_CHECK(cudaMemcpyAsync(ws + off[3], A->zero_rows, (size_t)A->num_zero_rows * 4, cudaMemcpyHostToDevice, st));
   }
-  if (A->num_zero_rows) LF_CUDA_CHECK(cudaMemcpyAsync(ws + off[3], A->zero_rows, (size_t)A->num_zero_rows * 4, cudaMemcpyHostToDevice, st));
   LF_CUDA_CHECK(cudaMemcpyAsync(ws + off[4], B, (size_t)A->num_cols * N * 4, cudaMemcpyHostToDevice, st));
   if (accumulate && c_bytes) LF_CUDA_CHECK(cudaMemcpyAsync(ws + off[5], C, c_bytes, cudaMemcpyHostToDevice, st));
   lf_hyb dev = *A;
@@ -855,7 +900,6 @@ int lf_spmm_hyb_f32_host(const lf_hyb* A, const float* B, float* C, int32_t N, i
   dev.cols = (const int32_t*)(ws + off[1]);
   dev.vals = (const float*)(ws + off[2]);
   dev.mask = nullptr;
-  dev.hot_bits = nullptr;
   dev.zero_rows = (const int32_t*)(ws + off[3]);
   if (int s = lf_spmm_hyb_f32(&dev, (const float*)(ws + off[4]), N, (float*)(ws + off[5]), N, N,
                               accumulate ? LF_SPMM_ACCUMULATE : LF_SPMM_OVERWRITE, st))
@@ -888,8 +932,10 @@ int lf_spmm_csr_f32(const int64_t* indptr, const int32_t* indices, const float* 
   {
     const int64_t rows = row_end - row_begin, groups = ceil_div64(nnz, spg);
     const int64_t n = rows > groups ? rows : groups;
-    const int64_t want = ceil_div64(n, 256);
-    csr_prepare_kernel<<<(unsigned)(want > 148 * 32 ? 148 * 32 : want), 256, 0, st>>>(indptr, row_begin, row_end, spg, C, ldc, N);
+    const int64_t want = ceil_div64(n, 256 / 32);
+    const unsigned pgrid = (unsigned)(want > 148 * 32 ? 148 * 32 : want);
+    if (cfg.VEC == 4) csr_prepare_kernel<4><<<pgrid, 256, 0, st>>>(indptr, row_begin, row_end, spg, C, ldc, N);
+    else csr_prepare_kernel<1><<<pgrid, 256, 0, st>>>(indptr, row_begin, row_end, spg, C, ldc, N);
     LF_CUDA_CHECK(cudaGetLastError());
   }
   if (nnz == 0) return LF_OK;
@@ -897,8 +943,8 @@ int lf_spmm_csr_f32(const int64_t* indptr, const int32_t* indices, const float* 
   LF_REQUIRE(blocks < (1ll << 31), "too many thread blocks");
   dim3 grid((unsigned)blocks, (unsigned)((N + cfg.pass - 1) / cfg.pass));
 #define LF_LAUNCH(G_, V_, VEC_)                                                                              \
-  spmm_csr_kernel<G_, V_, VEC_><<<grid, kThreads, 0, st>>>(indptr, indices, data, row_begin, row_end, B, (int)ldb, \
-                                                           C, ldc, N, spg)
+  LF_CUDA_CHECK(launch_dep(spmm_csr_kernel<G_, V_, VEC_>, grid, kThreads, st, true, indptr, indices, data, row_begin, \
+                           row_end, B, (int)ldb, C, ldc, N, spg))
   if (cfg.VEC == 4) {
     if (cfg.G == 8) LF_LAUNCH(8, 1, 4);
     else if (cfg.G == 16) LF_LAUNCH(16, 1, 4);
@@ -911,7 +957,6 @@ int lf_spmm_csr_f32(const int64_t* indptr, const int32_t* indices, const float* 
     else LF_LAUNCH(32, 4, 1);
   }
 #undef LF_LAUNCH
-  LF_CUDA_CHECK(cudaGetLastError());
   return LF_OK;
 }
 

@@ -41,12 +41,33 @@ class DeviceCsr:
         return int(self.indices.numel())
 
     @staticmethod
-    def from_host(indptr, indices, data, shape, device="cuda") -> "DeviceCsr":
+    def from_host(indptr, indices, data, shape, device="cuda", validate: bool = True) -> "DeviceCsr":
+        """Upload host arrays.  Column indices that do not fit int32 are refused here (a cast would
+        wrap them); with ``validate`` the uploaded matrix is checked on the device by
+        ``lf_csr_validate`` (row pointers, column range, strictly ascending columns)."""
         torch = _torch()
+        indices = np.asarray(indices)
+        if indices.dtype != np.int32 and indices.size and (int(indices.max()) > 0x7fffffff or int(indices.min()) < 0):
+            raise ValueError("column indices must lie in [0, 2^31)")
         ip = torch.from_numpy(np.ascontiguousarray(indptr, dtype=np.int64)).to(device)
         ix = torch.from_numpy(np.ascontiguousarray(indices, dtype=np.int32)).to(device)
         dv = None if data is None else torch.from_numpy(np.ascontiguousarray(data, dtype=np.float32)).to(device)
-        return DeviceCsr(ip, ix, dv, (int(shape[0]), int(shape[1])))
+        csr = DeviceCsr(ip, ix, dv, (int(shape[0]), int(shape[1])))
+        if validate:
+            csr.validate()
+        return csr
+
+    def validate(self) -> None:
+        """``lf_csr_validate``: raises ``ValueError`` when the matrix is not canonical CSR."""
+        torch = _torch()
+        lib = _cabi.load()
+        assert self.indptr.numel() == self.shape[0] + 1, "indptr must hold one entry per row plus one"
+        with torch.cuda.device(self.indptr.device):
+            st = lib.lf_csr_validate(t_ptr(self.indptr), t_ptr(self.indices), self.shape[0], self.shape[1],
+                                     self.nnz, _stream_ptr(torch))
+        if st == _cabi.LF_ERR_INVALID_ARGUMENT:
+            raise ValueError(lib.lf_last_error().decode("utf-8", "replace"))
+        check(st)
 
 
 def flatten_widths(bucket_widths: Sequence[Sequence[int]]):
@@ -56,21 +77,52 @@ def flatten_widths(bucket_widths: Sequence[Sequence[int]]):
     return pbo, flat
 
 
-def hyb_stats(csr: DeviceCsr, num_parts: int):
+class Workspace:
+    """A device byte buffer that grows on demand and is handed to consecutive builder calls, so that
+    a sequence of builds (statistics, plan, fill) on one stream allocates once instead of per call.
+    Not for concurrent use from several streams."""
+
+    def __init__(self, device):
+        self.device = device
+        self._buf = None
+        self._cursor = 0
+
+    def get(self, nbytes: int, slot: int = 0):
+        """A 256-byte aligned view of ``nbytes`` bytes.  ``slot == 0`` starts over at the beginning
+        of the buffer; views requested with increasing slot numbers after it do not overlap.  A view
+        stays valid when a later request makes the buffer grow (it keeps the old storage alive)."""
+        torch = _torch()
+        if slot == 0:
+            self._cursor = 0
+        start = -(-self._cursor // 256) * 256
+        end = start + max(int(nbytes), 1)
+        if self._buf is None or self._buf.numel() < end:
+            have = 0 if self._buf is None else self._buf.numel()
+            self._buf = torch.empty(max(end, 2 * have), dtype=torch.uint8, device=self.device)
+        self._cursor = end
+        return self._buf[start:end]
+
+
+def hyb_stats(csr: DeviceCsr, num_parts: int, workspace: Optional[Workspace] = None):
     """Run ``lf_hyb_stats``; returns ``(class_stats int64[P,11,3], colmask_hist int64[P,2048])`` on the host."""
     torch = _torch()
     lib = _cabi.load()
     M, K = csr.shape
     dev = csr.indptr.device
+    n_stat, n_hist = num_parts * _cabi.NUM_WIDTH_CLASSES * 3, num_parts * _cabi.COLMASK_BINS
     with torch.cuda.device(dev):
-        stats = torch.empty(num_parts * _cabi.NUM_WIDTH_CLASSES * 3, dtype=torch.int64, device=dev)
-        hist = torch.empty(num_parts * _cabi.COLMASK_BINS, dtype=torch.int64, device=dev)
         ws_bytes = lib.lf_hyb_stats_workspace_bytes(M, K, num_parts)
-        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
-        check(lib.lf_hyb_stats(t_ptr(csr.indptr), t_ptr(csr.indices), M, K, num_parts, t_ptr(stats),
-                               t_ptr(hist), t_ptr(ws), ws_bytes, _stream_ptr(torch)))
-        return (stats.cpu().numpy().reshape(num_parts, _cabi.NUM_WIDTH_CLASSES, 3),
-                hist.cpu().numpy().reshape(num_parts, _cabi.COLMASK_BINS))
+        if workspace is None:
+            out = torch.empty(n_stat + n_hist, dtype=torch.int64, device=dev)
+            ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+        else:
+            out = workspace.get((n_stat + n_hist) * 8, 0).view(torch.int64)
+            ws = workspace.get(ws_bytes, 1)
+        check(lib.lf_hyb_stats(t_ptr(csr.indptr), t_ptr(csr.indices), M, K, num_parts, out.data_ptr(),
+                               out.data_ptr() + n_stat * 8, ws.data_ptr(), ws_bytes, _stream_ptr(torch)))
+        host = out.cpu().numpy()      # one read-back for both tables (synchronises the stream)
+        return (host[:n_stat].reshape(num_parts, _cabi.NUM_WIDTH_CLASSES, 3).copy(),
+                host[n_stat:].reshape(num_parts, _cabi.COLMASK_BINS).copy())
 
 
 class HybFormat:
@@ -92,7 +144,6 @@ class HybFormat:
         self.row_off = np.ascontiguousarray(row_off, dtype=np.int64)
         self.slot_off = np.ascontiguousarray(slot_off, dtype=np.int64)
         self.rows, self.cols, self.vals, self.mask, self.zero_rows = rows, cols, vals, mask, zero_rows
-        self.hot_bits = None     # optional uint32 device tensor, one bit per slot (see struct lf_hyb)
 
     # -- C view ---------------------------------------------------------------------------
     def c_struct(self, host_arrays=None) -> LfHyb:
@@ -118,7 +169,6 @@ class HybFormat:
             s.rows, s.cols, s.vals, s.mask = np_ptr(r), np_ptr(c), np_ptr(v), 0
             s.zero_rows = np_ptr(z) if self.num_zero_rows else 0
         s.num_zero_rows = self.num_zero_rows
-        s.hot_bits = t_ptr(self.hot_bits) if (host_arrays is None and self.hot_bits is not None) else 0
         return s
 
     @property
@@ -209,8 +259,11 @@ class HybFormat:
 
 
 def build_hyb_device(csr: DeviceCsr, bucket_widths: Sequence[Sequence[int]],
-                     row_range: Optional[Tuple[int, int]] = None, with_mask: bool = True) -> HybFormat:
-    """``lf_hyb_plan`` + ``lf_hyb_fill``: CSR in device memory -> composed format in device memory."""
+                     row_range: Optional[Tuple[int, int]] = None, with_mask: bool = True,
+                     workspace: Optional[Workspace] = None) -> HybFormat:
+    """``lf_hyb_plan`` + ``lf_hyb_fill``: CSR in device memory -> composed format in device memory.
+    With a ``Workspace`` the scratch of both calls comes out of it and the call returns without
+    waiting for the fill (stream order protects the scratch for the next call on the same stream)."""
     torch = _torch()
     lib = _cabi.load()
     M, K = csr.shape
@@ -222,14 +275,14 @@ def build_hyb_device(csr: DeviceCsr, bucket_widths: Sequence[Sequence[int]],
     with torch.cuda.device(dev):
         stream = _stream_ptr(torch)
         ws_bytes = lib.lf_hyb_build_workspace_bytes(r0, r1, P, nb)
-        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev) if workspace is None else workspace.get(ws_bytes, 0)
         ell_rows = np.zeros(max(nb, 1), dtype=np.int64)
         row_off = np.zeros(nb + 1, dtype=np.int64)
         slot_off = np.zeros(nb + 1, dtype=np.int64)
         n_zero = C.c_int64(0)
         check(lib.lf_hyb_plan(t_ptr(csr.indptr), t_ptr(csr.indices), M, K, r0, r1, P, np_ptr(pbo),
                               np_ptr(flat_w) if nb else 0, np_ptr(ell_rows), np_ptr(row_off),
-                              np_ptr(slot_off), C.addressof(n_zero), t_ptr(ws), ws_bytes, stream))
+                              np_ptr(slot_off), C.addressof(n_zero), ws.data_ptr(), ws_bytes, stream))
         ell_rows = ell_rows[:nb]
         n_rows_total, n_slots_total = int(row_off[nb]), int(slot_off[nb])
         rows = torch.empty(n_rows_total, dtype=torch.int32, device=dev)
@@ -240,11 +293,12 @@ def build_hyb_device(csr: DeviceCsr, bucket_widths: Sequence[Sequence[int]],
         fmt = HybFormat((M, K), (r0, r1), bucket_widths, ell_rows, row_off, slot_off, rows, cols, vals,
                         mask, zero_rows)
         sc_bytes = lib.lf_hyb_fill_scratch_bytes(n_rows_total)
-        scratch = torch.empty(sc_bytes, dtype=torch.uint8, device=dev)
+        scratch = torch.empty(sc_bytes, dtype=torch.uint8, device=dev) if workspace is None else workspace.get(sc_bytes, 1)
         layout = fmt.c_struct()
         check(lib.lf_hyb_fill(t_ptr(csr.indptr), t_ptr(csr.indices), t_ptr(csr.data), C.byref(layout),
-                              t_ptr(ws), ws_bytes, t_ptr(scratch), sc_bytes, stream))
-        torch.cuda.current_stream().synchronize()   # ws / scratch are released on return
+                              ws.data_ptr(), ws_bytes, scratch.data_ptr(), sc_bytes, stream))
+        if workspace is None:
+            torch.cuda.current_stream().synchronize()   # ws / scratch are released on return
     return fmt
 
 

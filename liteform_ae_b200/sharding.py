@@ -133,7 +133,7 @@ class HostShardedSpmm:
         self.slots = []
         for _ in range(slots):
             f = copy.copy(fmt)
-            f.mask, f.hot_bits = None, None
+            f.mask = None
             for n in names:
                 setattr(f, n, torch.empty_like(getattr(fmt, n)))
             self.slots.append({

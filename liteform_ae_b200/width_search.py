@@ -137,34 +137,3 @@ def search_from_stats(class_stats: np.ndarray, colmask_hist: np.ndarray, feat_si
     for p, pool in enumerate(pools):
         out.append(_choose(pool, _ColumnCounter(colmask_hist[p]), feat_size, num_parts, cost_out) if pool else [])
     return out
-
-
-def stats_from_csr_host(indptr: np.ndarray, indices: np.ndarray, num_cols: int, num_parts: int):
-    """NumPy evaluation of the statistics (host logic for CPU-side tests of this module; the
-    library computes them on the device)."""
-    indptr = np.asarray(indptr, dtype=np.int64)
-    indices = np.asarray(indices, dtype=np.int64)
-    M = len(indptr) - 1
-    psz = (num_cols + num_parts - 1) // num_parts
-    row_of = np.repeat(np.arange(M, dtype=np.int64), np.diff(indptr))
-    part = indices // psz
-    deg = np.bincount(part * M + row_of, minlength=num_parts * M).reshape(num_parts, M)
-    k = np.zeros_like(deg)
-    pos = deg > 0
-    k[pos] = np.ceil(np.log2(deg[pos].astype(np.float64))).astype(np.int64)
-    k[pos] += (np.int64(1) << k[pos]) < deg[pos]
-    kc = np.minimum(k, NUM_CLASSES - 1)
-    reps = np.where(k > NUM_CLASSES - 1, np.int64(1) << np.maximum(k - (NUM_CLASSES - 1), 0), 1)
-    stats = np.zeros((num_parts, NUM_CLASSES, 3), dtype=np.int64)
-    for p in range(num_parts):
-        live = pos[p]
-        stats[p, :, 0] = np.bincount(kc[p][live], weights=reps[p][live], minlength=NUM_CLASSES)
-        stats[p, :, 1] = np.bincount(kc[p][live], weights=deg[p][live], minlength=NUM_CLASSES)
-        stats[p, :, 2] = np.bincount(kc[p][live], minlength=NUM_CLASSES)
-    colmask = np.zeros(num_cols, dtype=np.int64)
-    np.bitwise_or.at(colmask, indices, np.int64(1) << kc[part, row_of])
-    hist = np.zeros((num_parts, BINS), dtype=np.int64)
-    col_part = np.arange(num_cols, dtype=np.int64) // psz
-    touched = colmask > 0
-    np.add.at(hist, (col_part[touched], colmask[touched]), 1)
-    return stats, hist

@@ -107,6 +107,30 @@ def init_buckets(row: np.ndarray, col: np.ndarray, shape: Tuple[int, int], num_p
     return out
 
 
+def bucket_counters(row: np.ndarray, col: np.ndarray, shape: Tuple[int, int], num_parts: int):
+    """The bucket statistics of ``init_buckets`` (format_algos.py:819-900) in the counter form the
+    CUDA library emits: ``class_stats int64[P, 11, 3]`` = (num_rows, nnz, len(row_indices)) per
+    width class ``k`` (width ``2**k``), and ``colmask_hist int64[P, 2048]`` = number of columns of
+    the partition whose set of touching classes is the bin's bit pattern (so that the size of the
+    union of ``col_indices`` over any set of classes is a sum of bins)."""
+    pools = init_buckets(row, col, shape, num_parts)
+    K = shape[1]
+    psz = partition_size(K, num_parts)
+    n_classes = WIDTH_LIMIT.bit_length()          # widths 1 .. 1024
+    stats = np.zeros((num_parts, n_classes, 3), dtype=np.int64)
+    hist = np.zeros((num_parts, 1 << n_classes), dtype=np.int64)
+    for p, pool in enumerate(pools):
+        colmask = np.zeros(K, dtype=np.int64)
+        for w, b in pool.items():
+            k = int(w).bit_length() - 1
+            stats[p, k] = (b.num_rows, b.nnz, len(b.row_ids))
+            colmask[b.cols] |= np.int64(1) << k
+        touched = np.nonzero(colmask)[0]
+        assert touched.size == 0 or (touched // psz == p).all()
+        np.add.at(hist[p], colmask[touched], 1)
+    return stats, hist
+
+
 # --------------------------------------------------------------------------------------
 # the dictionary surgery of the width search
 # --------------------------------------------------------------------------------------

@@ -11,7 +11,8 @@ format side of the path (``search_bucket_config`` format_algos.py:988-1032,
 for the restatement in ``hyb_oracle.py`` and to generate ``tests/golden``.
 
 Nothing in the shipped package imports this file.  It only works where a checkout
-of the reference is present; ``reference_available()`` says whether it is.
+of the reference is present and the environment variable ``LITEFORM_REFERENCE_ROOT`` names it;
+``reference_available()`` says whether that is the case.
 """
 from __future__ import annotations
 
@@ -20,7 +21,8 @@ import sys
 import types
 from unittest.mock import MagicMock
 
-_DEFAULT_ROOT = os.environ.get("LITEFORM_REFERENCE_ROOT", os.path.join(os.sep, "root", "reference"))
+# The checkout's location comes from the environment only; without it the reference is "absent".
+_DEFAULT_ROOT = os.environ.get("LITEFORM_REFERENCE_ROOT", "")
 _SUBDIR = "playground_pipline"
 _ABSENT = ["tvm", "tvm.testing", "tvm.tir", "tvm.script", "tvm.sparse",
            "sparsetir_artifact", "dgl", "dgl.data", "ogb", "ogb.nodeproppred"]
@@ -28,7 +30,7 @@ _cache = {}
 
 
 def reference_available(root: str = _DEFAULT_ROOT) -> bool:
-    return os.path.isfile(os.path.join(root, _SUBDIR, "format_algos.py"))
+    return bool(root) and os.path.isfile(os.path.join(root, _SUBDIR, "format_algos.py"))
 
 
 def load_reference(root: str = _DEFAULT_ROOT):
@@ -36,7 +38,7 @@ def load_reference(root: str = _DEFAULT_ROOT):
     if root in _cache:
         return _cache[root]
     if not reference_available(root):
-        raise FileNotFoundError(f"no LiteForm reference under {root}")
+        raise FileNotFoundError(f"no LiteForm reference under {root!r} (set LITEFORM_REFERENCE_ROOT to the checkout)")
     import numpy as np
 
     saved = {k: sys.modules.get(k) for k in _ABSENT + ["utils", "format_algos", "format_matrix_market"]}

@@ -13,10 +13,11 @@ GENERATORS = {
     "powerlaw_1048576_s1": lambda: synth.power_law_graph(),
     "skew_1048576_s3": lambda: synth.skewed_rows(),
     "uniform32_4194304_s2": lambda: synth.uniform_rows(),
+    "blocks_2097152_s4": lambda: synth.bsr_to_csr(*synth.banded_blocks()),
 }
 SMALL = ["zipf_16384_s0", "zipf_2048_s5", "powerlaw_8192_s1", "uniform32_4096_s2", "skew_8192_s3",
          "blocks_4096_s4"]
-FULL = ["powerlaw_1048576_s1", "skew_1048576_s3", "uniform32_4194304_s2"]
+FULL = ["powerlaw_1048576_s1", "skew_1048576_s3", "uniform32_4194304_s2", "blocks_2097152_s4"]
 
 _cache = {}
 

@@ -1,7 +1,7 @@
 """Generate ``tests/golden/hyb_golden.json`` by running the UNMODIFIED reference.
 
-Needs a checkout of johnpzh/liteform_ae (its location: the loader's default, or the
-environment variable ``LITEFORM_REFERENCE_ROOT``).  For every case it feeds a seeded matrix to the reference's
+Needs a checkout of johnpzh/liteform_ae, named by the environment variable
+``LITEFORM_REFERENCE_ROOT``.  For every case it feeds a seeded matrix to the reference's
 ``search_bucket_config`` (playground_pipline/format_algos.py:988-1032) and ``build_hyb_format``
 (format_algos.py:226-385) and records the chosen widths and a sha256 digest of the int32-cast
 output arrays; tiny hand-made cases also keep the arrays themselves.  The tests then require
@@ -57,6 +57,8 @@ def generator_cases(full: bool):
             "powerlaw_1048576_s1": (lambda: synth.power_law_graph(), [(1, 128), (8, 128)]),
             "skew_1048576_s3": (lambda: synth.skewed_rows(), [(1, 256)]),
             "uniform32_4194304_s2": (lambda: synth.uniform_rows(), [(1, 64)]),
+            # config 5 as element CSR (every row holds 64 entries): the composed format of the block matrix
+            "blocks_2097152_s4": (lambda: synth.bsr_to_csr(*synth.banded_blocks()), [(1, 128)]),
         })
     return cases
 

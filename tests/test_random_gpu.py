@@ -30,7 +30,7 @@ def test_random_shapes(cuda_device, seed):
         rows = np.repeat(np.arange(M, dtype=np.int64), np.diff(csr.indptr))
         d = hyb.DeviceCsr.from_host(csr.indptr, csr.indices, csr.data, csr.shape, cuda_device)
         st, hi = hyb.hyb_stats(d, P)
-        want_st, want_hi = ws.stats_from_csr_host(csr.indptr, csr.indices, K, P)
+        want_st, want_hi = ho.bucket_counters(rows, csr.indices.astype(np.int64), csr.shape, P)
         assert np.array_equal(st, want_st) and np.array_equal(hi, want_hi)
         try:
             widths = ho.search_bucket_config(rows, csr.indices.astype(np.int64), csr.shape, P, max(N, 1))

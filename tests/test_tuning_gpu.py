@@ -20,6 +20,7 @@ def restore_defaults():
     lib.lf_bsr_set_tuning(0, 0, 0)
     lib.lf_set_option(_cabi.LF_OPT_BSR_COPY_ENGINE, 0)
     lib.lf_set_option(_cabi.LF_OPT_BSR_TILE_ORDER, 0)
+    lib.lf_set_option(_cabi.LF_OPT_SPMM_TILE_SEGMENTS, 0)
 
 
 def test_every_spmm_variant_gives_the_same_product(cuda_device, restore_defaults):
@@ -28,22 +29,18 @@ def test_every_spmm_variant_gives_the_same_product(cuda_device, restore_defaults
     csr = synth.skewed_rows(M=4096, seed=5, heavy_rows=6, heavy_len=3000)
     d = hyb.DeviceCsr.from_host(csr.indptr, csr.indices, csr.data, csr.shape, cuda_device)
     fmt = hyb.build_hyb_device(d, [[1, 2, 4, 8, 16]], with_mask=False)
-    # per-slot hint bits for policy 2: mark every other slot; hints must never change values
-    words = (int(fmt.slot_off[-1]) + 31) // 32
-    hot = torch.full((words,), 0x55555555, dtype=torch.int32, device=cuda_device)
     for N in (32, 128, 512):
         B = synth.dense_features(4096, N, 2)
         Bd = torch.from_numpy(B).to(cuda_device)
         want = ho.spmm_scipy_csr(csr.indptr, csr.indices, csr.data.astype(np.float64), csr.shape, B.astype(np.float64))
-        for pol, minb, slots in itertools.product((0, 1, 2), (2, 3, 4), (0, 8, 64, 4096)):
+        for pol, minb, slots, segs in itertools.product((0, 1), (2, 3, 4), (0, 8, 64, 4096), (0, 1, 7, 64)):
             assert lib.lf_set_option(_cabi.LF_OPT_SPMM_CACHE_POLICY, pol) == 0
             assert lib.lf_set_option(_cabi.LF_OPT_SPMM_MIN_BLOCKS, minb) == 0
             assert lib.lf_set_option(_cabi.LF_OPT_SPMM_SLOTS_PER_GROUP, slots) == 0
-            for bits in ((None, hot) if pol == 2 else (None,)):
-                fmt.hot_bits = bits
-                C = hyb.spmm_hyb(fmt, Bd).cpu().numpy()
-                np.testing.assert_allclose(C, want, rtol=1e-5, atol=1e-4, err_msg=f"{N} {pol} {minb} {slots}")
-        fmt.hot_bits = None
+            assert lib.lf_set_option(_cabi.LF_OPT_SPMM_TILE_SEGMENTS, segs) == 0
+            C = hyb.spmm_hyb(fmt, Bd).cpu().numpy()
+            np.testing.assert_allclose(C, want, rtol=1e-5, atol=1e-4, err_msg=f"{N} {pol} {minb} {slots} {segs}")
+    assert lib.lf_set_option(_cabi.LF_OPT_SPMM_CACHE_POLICY, 2) == _cabi.LF_ERR_INVALID_ARGUMENT
     assert lib.lf_set_option(_cabi.LF_OPT_SPMM_MIN_BLOCKS, 7) == _cabi.LF_ERR_INVALID_ARGUMENT
     assert lib.lf_set_option(99, 1) == _cabi.LF_ERR_INVALID_ARGUMENT
 

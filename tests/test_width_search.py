@@ -1,4 +1,5 @@
-"""Host width search on device-style statistics vs the oracle's set-based search."""
+"""Host width search on counter-form statistics (derived from the oracle's ``init_buckets``, which
+is pinned to format_algos.py:819-900) vs the oracle's set-based search."""
 import numpy as np
 import pytest
 
@@ -16,7 +17,7 @@ def test_search_from_stats_equals_oracle(name):
     csr = cases.matrix(name)
     row, col = _coo(csr)
     for P in (1, 2, 7):
-        stats, hist = ws.stats_from_csr_host(csr.indptr, csr.indices, csr.shape[1], P)
+        stats, hist = ho.bucket_counters(row, col, csr.shape, P)
         for N in (32, 512):
             assert ws.search_from_stats(stats, hist, N, P) == ho.search_bucket_config(row, col, csr.shape, P, N)
 
@@ -25,7 +26,7 @@ def test_stats_tables_equal_oracle_buckets():
     csr = synth.skewed_rows(M=4096, seed=8, heavy_rows=4, heavy_len=3000)
     row, col = _coo(csr)
     for P in (1, 3):
-        stats, hist = ws.stats_from_csr_host(csr.indptr, csr.indices, csr.shape[1], P)
+        stats, hist = ho.bucket_counters(row, col, csr.shape, P)
         pools = ho.init_buckets(row, col, csr.shape, P)
         bins = np.arange(ws.BINS)
         for p, pool in enumerate(pools):
@@ -43,7 +44,8 @@ def test_edge_cases_from_golden(golden):
         if rec.get("forced"):
             continue
         csr = cases.edge_csr(rec)
-        stats, hist = ws.stats_from_csr_host(csr.indptr, csr.indices, csr.shape[1], rec["P"])
+        row, col = _coo(csr)
+        stats, hist = ho.bucket_counters(row, col, csr.shape, rec["P"])
         if "error" in rec:
             with pytest.raises(ValueError, match="only having 1 non-zero"):
                 ws.search_from_stats(stats, hist, rec["N"], rec["P"])
