@@ -282,6 +282,33 @@ int lf_bsr8_fill(const int64_t* indptr /*[dev]*/, const int32_t* indices /*[dev]
                  void* blocks /*[dev] out*/, int32_t dtype, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * Coarse blocks -> 8x8 tiles on the device.  The reference hands its block path a SciPy BSR matrix
+ * with 32x32 fp16 blocks (bench_bsrmm(bsr_mat, x, block_size=32), playground_pipline/
+ * format_algos.py:1562-1643, built by MTX.tobsr_with_padding, format_matrix_market.py:116-138).
+ * These two calls cut R x C blocks (multiples of 8; indptr int64[block_rows+1], block columns
+ * sorted inside a block row, data [num_blocks][R][C] in in_dtype) into the 8x8 tiles the product
+ * kernels take and drop the tiles that hold only zeros, so the padding inside coarse blocks costs
+ * nothing.  The result equals scipy.sparse.bsr_matrix(blocksize=(8, 8)) of the same matrix after
+ * eliminate_zeros(): tile (a, c) of a block in block row I, block column J lands in fine block row
+ * I*R/8 + a with block column J*C/8 + c.
+ *   lf_bsr_split8_plan  flags and counts: writes out_indptr int64[block_rows*R/8 + 1], returns
+ *                       *num_tiles on the host (synchronises the stream); `scratch` keeps one
+ *                       byte per candidate tile for the fill.
+ *   lf_bsr_split8_fill  writes out_indices int32[num_tiles] and out_blocks[num_tiles*64] in
+ *                       out_dtype (converted through float32, round to nearest even).
+ * ------------------------------------------------------------------------------------------- */
+size_t lf_bsr_split8_scratch_bytes(int64_t num_blocks, int32_t R, int32_t C);
+int lf_bsr_split8_plan(const int64_t* indptr /*[dev]*/, const void* data /*[dev]*/, int32_t in_dtype,
+                       int64_t block_rows, int64_t num_blocks, int32_t R, int32_t C,
+                       void* scratch /*[dev]*/, size_t scratch_bytes, int64_t* out_indptr /*[dev] out*/,
+                       int64_t* num_tiles /*[host] out*/, void* stream);
+int lf_bsr_split8_fill(const int64_t* indptr /*[dev]*/, const int32_t* indices /*[dev]*/, const void* data /*[dev]*/,
+                       int32_t in_dtype, int64_t block_rows, int64_t num_blocks, int32_t R, int32_t C,
+                       const void* scratch /*[dev] as left by the plan*/, const int64_t* out_indptr /*[dev]*/,
+                       int32_t* out_indices /*[dev] out*/, void* out_blocks /*[dev] out*/, int32_t out_dtype,
+                       void* stream);
+
+/* ---------------------------------------------------------------------------------------------
  * Block-sparse SpMM, 8x8 blocks (BSR): C[block_row_begin*8 : block_row_end*8, 0:N] = A * B.
  * Replaces the kernel of bench_bsrmm (playground_pipline/format_algos.py:1562-1643; arithmetic
  * format_algos.py:1204-1213), which runs 32x32 fp16 blocks through wmma with fp16 accumulators

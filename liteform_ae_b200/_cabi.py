@@ -81,6 +81,11 @@ SIGNATURES = {
     "lf_spmm_csr_f32": (C.c_int, [vp, vp, vp, C.c_int64, C.c_int64, C.c_int64, vp, C.c_int64, vp, C.c_int64, C.c_int32, vp]),
     "lf_bsr8_plan": (C.c_int, [vp, vp, C.c_int64, vp, C.POINTER(C.c_int64), vp]),
     "lf_bsr8_fill": (C.c_int, [vp, vp, vp, C.c_int64, vp, vp, vp, C.c_int32, vp]),
+    "lf_bsr_split8_scratch_bytes": (C.c_size_t, [C.c_int64, C.c_int32, C.c_int32]),
+    "lf_bsr_split8_plan": (C.c_int, [vp, vp, C.c_int32, C.c_int64, C.c_int64, C.c_int32, C.c_int32, vp, C.c_size_t, vp,
+                                     C.POINTER(C.c_int64), vp]),
+    "lf_bsr_split8_fill": (C.c_int, [vp, vp, vp, C.c_int32, C.c_int64, C.c_int64, C.c_int32, C.c_int32, vp, vp, vp, vp,
+                                     C.c_int32, vp]),
     "lf_bsr_set_tuning": (C.c_int, [C.c_int32, C.c_int32, C.c_int32]),
     "lf_bsr_copy_status": (C.c_int, [vp]),
     "lf_spmm_bsr8_f32": (C.c_int, [vp, vp, vp, C.c_int64, C.c_int64, vp, C.c_int64, vp, C.c_int64, C.c_int32, vp]),

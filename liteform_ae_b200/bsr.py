@@ -3,8 +3,8 @@
 The reference converts the graph with SciPy (``MTX.tobsr_with_padding``,
 playground_pipline/format_matrix_market.py:116-138, block size 32, fp16) and times a generated
 wmma kernel (``bench_bsrmm``, playground_pipline/format_algos.py:1562-1643).  Here the format
-stays SciPy's (``indptr``, sorted ``indices``, dense ``data[nb, R, C]``), re-blocked to 8x8 on
-the host when it comes in coarser, and the product runs on ``lf_spmm_bsr8_{f32,bf16,f16}``.
+stays SciPy's (``indptr``, sorted ``indices``, dense ``data[nb, R, C]``), cut into 8x8 tiles on
+the device when it comes in coarser, and the product runs on ``lf_spmm_bsr8_{f32,bf16,f16}``.
 ``DeviceBsr8.from_csr_device`` converts a CSR matrix that already lies in device memory.
 """
 from __future__ import annotations
@@ -79,22 +79,51 @@ class DeviceBsr8:
 
     @staticmethod
     def from_scipy(bsr_mat, dtype: Optional[str] = None, device="cuda") -> "DeviceBsr8":
-        """Accepts a ``scipy.sparse.bsr_matrix`` with square blocks whose size is a multiple of 8
-        (re-blocked to 8x8, all-zero sub-blocks dropped) on a shape that is a multiple of 8."""
-        import scipy.sparse as sp
+        """Accepts a ``scipy.sparse.bsr_matrix`` with blocks whose sides are multiples of 8 on a shape
+        that is a multiple of the block size.  The block arrays are uploaded as they are; blocks
+        coarser than 8x8 (the reference passes 32x32, format_algos.py:1562-1643) are cut into 8x8
+        tiles on the device and all-zero tiles dropped (``lf_bsr_split8_plan`` / ``_fill``) -- the
+        result equals ``scipy.sparse.bsr_matrix(blocksize=(8, 8))`` of the matrix without its
+        explicit zeros."""
+        torch = _torch()
+        lib = _cabi.load()
+        import ctypes
         m = bsr_mat
         if dtype is None:
             dtype = "float16" if m.data.dtype == np.float16 else "float32"
         R, Cb = m.blocksize
         assert R % 8 == 0 and Cb % 8 == 0, "block size must be a multiple of 8"
-        # rebuild in float32 from the raw arrays (SciPy itself has no float16 support)
-        m32 = sp.bsr_matrix((m.data.astype(np.float32), m.indices, m.indptr), shape=m.shape, blocksize=(R, Cb))
-        if (R, Cb) != (8, 8):
-            csr = m32.tocsr()
-            csr.eliminate_zeros()       # the padding inside coarse blocks must not become 8x8 tiles
-            m32 = sp.bsr_matrix(csr, blocksize=(8, 8))
-        m32.sort_indices()
-        return DeviceBsr8.from_arrays(m32.indptr, m32.indices, m32.data, m32.shape, dtype, device)
+        assert m.shape[0] % R == 0 and m.shape[1] % Cb == 0, "shape must be a multiple of the block size"
+        m_indptr, m_indices, m_data = m.indptr, m.indices, m.data
+        row_of = np.repeat(np.arange(len(m_indptr) - 1), np.diff(m_indptr))
+        if m_indices.size and not (np.diff(m_indices)[np.diff(row_of) == 0] > 0).all():
+            # block columns must ascend inside a block row (SciPy's own sort refuses float16 data)
+            order = np.lexsort((m_indices, row_of))
+            m_indices, m_data = m_indices[order], m_data[order]
+        in_np = {np.dtype(np.float16): (np.float16, torch.float16, _cabi.LF_DTYPE_F16)}.get(
+            m_data.dtype, (np.float32, torch.float32, _cabi.LF_DTYPE_F32))
+        tdt, out_code = {"float32": (torch.float32, _cabi.LF_DTYPE_F32), "bfloat16": (torch.bfloat16, _cabi.LF_DTYPE_BF16),
+                         "float16": (torch.float16, _cabi.LF_DTYPE_F16)}[str(dtype)]
+        block_rows, nb = m.shape[0] // R, int(m_indices.shape[0])
+        indptr = torch.from_numpy(np.ascontiguousarray(m_indptr, dtype=np.int64)).to(device)
+        indices = torch.from_numpy(np.ascontiguousarray(m_indices, dtype=np.int32)).to(device)
+        data = torch.from_numpy(np.ascontiguousarray(m_data, dtype=in_np[0])).to(device)
+        dev = indptr.device
+        with torch.cuda.device(dev):
+            stream = torch.cuda.current_stream().cuda_stream
+            sc_bytes = lib.lf_bsr_split8_scratch_bytes(nb, R, Cb)
+            scratch = torch.empty(sc_bytes, dtype=torch.uint8, device=dev)
+            fine_rows = block_rows * (R // 8)
+            indptr8 = torch.empty(fine_rows + 1, dtype=torch.int64, device=dev)
+            n_tiles = ctypes.c_int64(0)
+            check(lib.lf_bsr_split8_plan(t_ptr(indptr), t_ptr(data), in_np[2], block_rows, nb, R, Cb, t_ptr(scratch),
+                                         sc_bytes, t_ptr(indptr8), ctypes.byref(n_tiles), stream))
+            indices8 = torch.empty(n_tiles.value, dtype=torch.int32, device=dev)
+            blocks = torch.empty((n_tiles.value, 8, 8), dtype=tdt, device=dev)
+            check(lib.lf_bsr_split8_fill(t_ptr(indptr), t_ptr(indices), t_ptr(data), in_np[2], block_rows, nb, R, Cb,
+                                         t_ptr(scratch), t_ptr(indptr8), t_ptr(indices8), t_ptr(blocks), out_code, stream))
+            torch.cuda.current_stream().synchronize()      # scratch and the coarse arrays are released on return
+        return DeviceBsr8(indptr8, indices8, blocks, (int(m.shape[0]), int(m.shape[1])))
 
 
 def spmm_bsr8(a: DeviceBsr8, B, out=None, block_row_range=None):

@@ -123,12 +123,207 @@ scan_counts_kernel(int64_t* __restrict__ v, int64_t n) {
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Coarse blocks (R x C, both multiples of 8) -> 8x8 tiles.  The reference's block path hands over
+// 32x32 fp16 blocks (bench_bsrmm(bsr_mat, x, block_size=32), format_algos.py:1562-1643); the
+// product kernels here take 8x8 tiles, and the zero padding inside coarse blocks must not become
+// tiles.  Three launches: flag the candidate tiles that hold a nonzero; count them per fine block
+// row and scan; write block columns and tiles in order (coarse column, then sub-column).
+// A candidate tile is (coarse block b, sub-row a, sub-column c), flag index (b * R/8 + a) * C/8 + c.
+// ---------------------------------------------------------------------------------------------
+template <typename T> __device__ __forceinline__ float to_float(T x);
+template <> __device__ __forceinline__ float to_float<float>(float x) { return x; }
+template <> __device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
+template <> __device__ __forceinline__ float to_float<__half>(__half x) { return __half2float(x); }
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+split8_flag_kernel(const T* __restrict__ data, int64_t candidates, int R, int C, uint8_t* __restrict__ flags) {
+  const int Ra = R / 8, Cc = C / 8;
+  for (int64_t q = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; q < candidates; q += (int64_t)gridDim.x * blockDim.x) {
+    const int c = (int)(q % Cc);
+    const int64_t t = q / Cc;
+    const int a = (int)(t % Ra);
+    const int64_t b = t / Ra;
+    const T* src = data + (b * R + a * 8) * C + c * 8;
+    bool any = false;
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) any |= to_float<T>(src[i * C + j]) != 0.f;
+    flags[q] = any ? 1 : 0;
+  }
+}
+
+// counts[f + 1] = tiles of fine block row f = I * R/8 + a
+__global__ void __launch_bounds__(256)
+split8_count_kernel(const int64_t* __restrict__ indptr, const uint8_t* __restrict__ flags, int64_t fine_rows, int Ra,
+                    int Cc, int64_t* __restrict__ out_indptr) {
+  const int64_t f = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (f >= fine_rows) return;
+  const int64_t I = f / Ra;
+  const int a = (int)(f % Ra);
+  int64_t n = 0;
+  for (int64_t b = indptr[I]; b < indptr[I + 1]; ++b) {
+    const uint8_t* fl = flags + (b * Ra + a) * Cc;
+    for (int c = 0; c < Cc; ++c) n += fl[c];
+  }
+  out_indptr[f + 1] = n;
+}
+
+// One warp per fine block row: walks its candidate tiles in order, 32 at a time; the kept ones get
+// consecutive output positions (ballot prefix) and are copied by the whole warp, two elements per
+// lane, converted to the output type.  Zeros are written as +0 (what a rebuild from the nonzero
+// entries produces).
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(256)
+split8_fill_kernel(const int64_t* __restrict__ indptr, const int32_t* __restrict__ indices, const TI* __restrict__ data,
+                   const uint8_t* __restrict__ flags, int64_t fine_rows, int R, int C,
+                   const int64_t* __restrict__ out_indptr, int32_t* __restrict__ out_indices, TO* __restrict__ out_blocks) {
+  const int Ra = R / 8, Cc = C / 8;
+  const int lane = threadIdx.x & 31;
+  const int64_t f = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (f >= fine_rows) return;
+  const int64_t I = f / Ra;
+  const int a = (int)(f % Ra);
+  const int64_t b0 = indptr[I];
+  const int64_t cand = (indptr[I + 1] - b0) * Cc;
+  int64_t out = out_indptr[f];
+  for (int64_t q0 = 0; q0 < cand; q0 += 32) {
+    const int64_t q = q0 + lane;
+    int64_t b = 0;
+    int c = 0;
+    bool keep = false;
+    if (q < cand) {
+      b = b0 + q / Cc;
+      c = (int)(q % Cc);
+      keep = flags[(b * Ra + a) * Cc + c] != 0;
+    }
+    const unsigned kept = __ballot_sync(0xffffffffu, keep);
+    if (keep) out_indices[out + __popc(kept & ((1u << lane) - 1u))] = indices[b] * Cc + c;
+    int k = 0;
+    for (unsigned todo = kept; todo; todo &= todo - 1, ++k) {
+      const int src_lane = __ffs(todo) - 1;
+      const int64_t sb = __shfl_sync(0xffffffffu, b, src_lane);
+      const int sc = __shfl_sync(0xffffffffu, c, src_lane);
+      const TI* src = data + (sb * R + a * 8) * C + sc * 8;
+      TO* dst = out_blocks + (out + k) * 64;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int e = lane + 32 * h;           // element of the tile: row e / 8, column e % 8
+        const float x = to_float<TI>(src[(e >> 3) * C + (e & 7)]);
+        dst[e] = from_float<TO>(x == 0.f ? 0.f : x);
+      }
+    }
+    out += __popc(kept);
+  }
+}
+
+template <typename TI>
+int split8_fill_launch(int out_dtype, const int64_t* indptr, const int32_t* indices, const TI* data, const uint8_t* flags,
+                       int64_t fine_rows, int R, int C, const int64_t* out_indptr, int32_t* out_indices, void* out_blocks,
+                       cudaStream_t st) {
+  const int64_t grid = ceil_div64(fine_rows, 8);
+  LF_REQUIRE(grid < (1ll << 31), "too many thread blocks");
+  switch (out_dtype) {
+    case LF_DTYPE_F32:
+      split8_fill_kernel<TI, float><<<(unsigned)grid, 256, 0, st>>>(indptr, indices, data, flags, fine_rows, R, C,
+                                                                    out_indptr, out_indices, (float*)out_blocks);
+      break;
+    case LF_DTYPE_BF16:
+      split8_fill_kernel<TI, __nv_bfloat16><<<(unsigned)grid, 256, 0, st>>>(indptr, indices, data, flags, fine_rows, R, C,
+                                                                            out_indptr, out_indices, (__nv_bfloat16*)out_blocks);
+      break;
+    default:
+      split8_fill_kernel<TI, __half><<<(unsigned)grid, 256, 0, st>>>(indptr, indices, data, flags, fine_rows, R, C,
+                                                                     out_indptr, out_indices, (__half*)out_blocks);
+      break;
+  }
+  LF_CUDA_CHECK(cudaGetLastError());
+  return LF_OK;
+}
+
+int check_split8(const void* indptr, const void* data, int64_t block_rows, int64_t num_blocks, int R, int C, int in_dtype) {
+  LF_REQUIRE(indptr && block_rows >= 0 && num_blocks >= 0, "bad arguments");
+  LF_REQUIRE(R >= 8 && C >= 8 && R % 8 == 0 && C % 8 == 0 && R <= 1024 && C <= 1024,
+             "block shape %d x %d is not a multiple of 8 (or exceeds 1024)", R, C);
+  LF_REQUIRE(in_dtype >= LF_DTYPE_F32 && in_dtype <= LF_DTYPE_F16, "unknown dtype %d", in_dtype);
+  LF_REQUIRE(num_blocks == 0 || data, "block data missing");
+  LF_REQUIRE(num_blocks * (int64_t)(R / 8) * (C / 8) < (1ll << 31), "more than 2^31-1 candidate tiles are not supported");
+  return LF_OK;
+}
+
 }  // namespace
 }  // namespace lf
 
 using namespace lf;
 
 extern "C" {
+
+size_t lf_bsr_split8_scratch_bytes(int64_t num_blocks, int32_t R, int32_t C) {
+  if (num_blocks < 0 || R < 8 || C < 8) return 0;
+  return align_up((size_t)num_blocks * (size_t)(R / 8) * (size_t)(C / 8) + 1, 256);
+}
+
+int lf_bsr_split8_plan(const int64_t* indptr, const void* data, int32_t in_dtype, int64_t block_rows,
+                       int64_t num_blocks, int32_t R, int32_t C, void* scratch, size_t scratch_bytes,
+                       int64_t* out_indptr, int64_t* num_tiles, void* stream) {
+  if (int s = check_split8(indptr, data, block_rows, num_blocks, R, C, in_dtype)) return s;
+  LF_REQUIRE(scratch && out_indptr && num_tiles, "null pointer argument");
+  if (scratch_bytes < lf_bsr_split8_scratch_bytes(num_blocks, R, C)) return fail(LF_ERR_WORKSPACE_TOO_SMALL, "split scratch too small");
+  cudaStream_t st = (cudaStream_t)stream;
+  const int Ra = R / 8, Cc = C / 8;
+  const int64_t fine_rows = block_rows * Ra;
+  const int64_t candidates = num_blocks * Ra * Cc;
+  uint8_t* flags = (uint8_t*)scratch;
+  *num_tiles = 0;
+  if (candidates > 0) {
+    const int64_t want = ceil_div64(candidates, 256);
+    const unsigned grid = (unsigned)(want > 148 * 64 ? 148 * 64 : want);
+    if (in_dtype == LF_DTYPE_F32) split8_flag_kernel<float><<<grid, 256, 0, st>>>((const float*)data, candidates, R, C, flags);
+    else if (in_dtype == LF_DTYPE_BF16) split8_flag_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)data, candidates, R, C, flags);
+    else split8_flag_kernel<__half><<<grid, 256, 0, st>>>((const __half*)data, candidates, R, C, flags);
+    LF_CUDA_CHECK(cudaGetLastError());
+  }
+  if (fine_rows == 0) {
+    LF_CUDA_CHECK(cudaMemsetAsync(out_indptr, 0, sizeof(int64_t), st));
+    LF_CUDA_CHECK(cudaStreamSynchronize(st));
+    return LF_OK;
+  }
+  LF_REQUIRE(ceil_div64(fine_rows, 256) < (1ll << 31), "too many block rows");
+  split8_count_kernel<<<(unsigned)ceil_div64(fine_rows, 256), 256, 0, st>>>(indptr, flags, fine_rows, Ra, Cc, out_indptr);
+  LF_CUDA_CHECK(cudaGetLastError());
+  scan_counts_kernel<<<1, kScanThreads, 0, st>>>(out_indptr, fine_rows);
+  LF_CUDA_CHECK(cudaGetLastError());
+  LF_CUDA_CHECK(cudaMemcpyAsync(num_tiles, out_indptr + fine_rows, sizeof(int64_t), cudaMemcpyDeviceToHost, st));
+  LF_CUDA_CHECK(cudaStreamSynchronize(st));
+  return LF_OK;
+}
+
+int lf_bsr_split8_fill(const int64_t* indptr, const int32_t* indices, const void* data, int32_t in_dtype,
+                       int64_t block_rows, int64_t num_blocks, int32_t R, int32_t C, const void* scratch,
+                       const int64_t* out_indptr, int32_t* out_indices, void* out_blocks, int32_t out_dtype,
+                       void* stream) {
+  if (int s = check_split8(indptr, data, block_rows, num_blocks, R, C, in_dtype)) return s;
+  LF_REQUIRE(out_dtype >= LF_DTYPE_F32 && out_dtype <= LF_DTYPE_F16, "unknown dtype %d", out_dtype);
+  LF_REQUIRE(scratch && out_indptr, "null pointer argument");
+  const int64_t fine_rows = block_rows * (R / 8);
+  if (fine_rows == 0 || num_blocks == 0) return LF_OK;
+  LF_REQUIRE(indices, "block columns missing");
+  if (!out_indices || !out_blocks) {   // legal only when the plan found no tile; the kernel then writes nothing
+    LF_REQUIRE(!out_indices && !out_blocks, "output arrays missing");
+  }
+  cudaStream_t st = (cudaStream_t)stream;
+  const uint8_t* flags = (const uint8_t*)scratch;
+  if (in_dtype == LF_DTYPE_F32)
+    return split8_fill_launch<float>(out_dtype, indptr, indices, (const float*)data, flags, fine_rows, R, C, out_indptr,
+                                     out_indices, out_blocks, st);
+  if (in_dtype == LF_DTYPE_BF16)
+    return split8_fill_launch<__nv_bfloat16>(out_dtype, indptr, indices, (const __nv_bfloat16*)data, flags, fine_rows, R,
+                                             C, out_indptr, out_indices, out_blocks, st);
+  return split8_fill_launch<__half>(out_dtype, indptr, indices, (const __half*)data, flags, fine_rows, R, C, out_indptr,
+                                    out_indices, out_blocks, st);
+}
 
 int lf_bsr8_plan(const int64_t* indptr, const int32_t* indices, int64_t M, int64_t* bsr_indptr,
                  int64_t* num_blocks, void* stream) {

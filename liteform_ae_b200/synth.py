@@ -40,6 +40,27 @@ class Csr:
         return sp.csr_matrix((self.data, self.indices, self.indptr), shape=self.shape)
 
 
+def _sorted_unique(a: np.ndarray) -> np.ndarray:
+    """``np.unique(a)`` for an integer array by sort + neighbour compare (sorts ``a`` in place)."""
+    a.sort()
+    if a.size == 0:
+        return a
+    keep = np.ones(a.size, dtype=bool)
+    np.not_equal(a[1:], a[:-1], out=keep[1:])
+    return a[keep]
+
+
+def _merge_unique(keys: np.ndarray, new: np.ndarray) -> np.ndarray:
+    """``np.unique(np.concatenate([keys, new]))`` when ``keys`` is already sorted and distinct and
+    ``new`` is much shorter: insert instead of sorting everything again."""
+    new = _sorted_unique(new)
+    if keys.size == 0:
+        return new
+    pos = np.searchsorted(keys, new)
+    dup = keys[np.minimum(pos, keys.size - 1)] == new
+    return np.insert(keys, pos[~dup], new[~dup])
+
+
 def _distinct_uniform_columns(rng, lens: np.ndarray, K: int):
     """For every row r draw ``lens[r]`` distinct uniform columns; returns flat sorted keys
     ``row * K + col`` (so rows come out contiguous and columns ascending)."""
@@ -57,7 +78,7 @@ def _distinct_uniform_columns(rng, lens: np.ndarray, K: int):
             break
         r = np.repeat(np.arange(M, dtype=np.int64), need)
         c = rng.integers(0, K, size=total, dtype=np.int64)
-        keys = np.unique(np.concatenate([keys, r * K + c]))
+        keys = _merge_unique(keys, r * K + c) if keys.size else _sorted_unique(r * K + c)
         have = np.bincount(keys // K, minlength=M)
         need = lens - have
     return keys
@@ -105,7 +126,7 @@ def power_law_graph(M: int = 1 << 20, seed: int = 1, mean: float = 14.0, cap: in
     r = np.repeat(np.arange(M, dtype=np.int64), deg)
     c = np.searchsorted(weight, rng.random(total) * weight[-1], side="right").astype(np.int64)
     np.minimum(c, M - 1, out=c)
-    keys = np.unique(r * M + c)            # in-row duplicates dropped
+    keys = _sorted_unique(r * M + c)       # in-row duplicates dropped
     indptr, indices = _csr_from_keys(keys, M, M)
     lens = np.diff(indptr)
     data = np.repeat((1.0 / np.maximum(lens, 1)).astype(np.float32), lens)

@@ -100,3 +100,52 @@ def test_full_size_block_matrix_round_trip(cuda_device):
     np.testing.assert_array_equal(a.indptr.cpu().numpy(), np.asarray(indptr, dtype=np.int64))
     np.testing.assert_array_equal(a.indices.cpu().numpy(), np.asarray(indices, dtype=np.int32))
     np.testing.assert_array_equal(a.blocks.cpu().numpy(), blocks)
+
+
+def _scipy_split8(m):
+    """The host route the device split replaces: float32 copy -> CSR -> explicit zeros dropped -> 8x8 blocks."""
+    R, Cb = m.blocksize
+    m32 = sp.bsr_matrix((m.data.astype(np.float32), m.indices, m.indptr), shape=m.shape, blocksize=(R, Cb))
+    csr = m32.tocsr()
+    csr.eliminate_zeros()
+    out = sp.bsr_matrix(csr, blocksize=(8, 8))
+    out.sort_indices()
+    return out
+
+
+@pytest.mark.parametrize("blocksize", [(32, 32), (16, 24), (8, 8)])
+@pytest.mark.parametrize("in_dtype", [np.float32, np.float16])
+def test_coarse_blocks_are_cut_into_tiles_on_the_device(cuda_device, blocksize, in_dtype):
+    """lf_bsr_split8_plan / lf_bsr_split8_fill vs SciPy: tiles that hold only zeros (padding inside
+    coarse blocks, explicit zeros, -0.0) are dropped, block columns come out sorted, values are
+    copied bit for bit."""
+    R, Cb = blocksize
+    rng = np.random.default_rng(R * 100 + Cb)
+    Mb, Kb, per_row = 37, 29, 5
+    indptr = np.arange(Mb + 1, dtype=np.int32) * per_row
+    cols = np.stack([rng.permutation(Kb)[:per_row] for _ in range(Mb)])        # NOT sorted inside a block row
+    data = rng.uniform(-1, 1, size=(Mb * per_row, R, Cb)).astype(np.float32)
+    data[rng.random(data.shape) < 0.93] = 0.0                                   # most 8x8 tiles end up empty
+    data[0, :8, :8] = 0.0
+    data[0, 0, 0] = -0.0                                                        # a tile of zeros only (one negative)
+    data[1, 8 % R:8 % R + 8, :8] = 0.0
+    m = sp.bsr_matrix((data, cols.reshape(-1), indptr), shape=(Mb * R, Kb * Cb), blocksize=(R, Cb))
+    if in_dtype != np.float32:       # SciPy builds no float16 matrix; narrow the block array afterwards
+        m.data = m.data.astype(in_dtype)
+    want = _scipy_split8(m)
+    for out_dtype in ("float32", "float16", "bfloat16"):
+        a = bsr.DeviceBsr8.from_scipy(m, dtype=out_dtype, device=cuda_device)
+        assert a.shape == m.shape
+        np.testing.assert_array_equal(a.indptr.cpu().numpy(), want.indptr.astype(np.int64))
+        np.testing.assert_array_equal(a.indices.cpu().numpy(), want.indices.astype(np.int32))
+        import torch
+        ref = torch.from_numpy(want.data.astype(np.float32)).to(getattr(torch, out_dtype))
+        assert torch.equal(a.blocks.cpu().view(torch.int16 if out_dtype != "float32" else torch.int32),
+                           ref.view(torch.int16 if out_dtype != "float32" else torch.int32))
+
+
+def test_coarse_block_matrix_without_blocks(cuda_device):
+    m = sp.bsr_matrix((np.zeros((0, 32, 32), dtype=np.float32), np.zeros(0, dtype=np.int32), np.zeros(5, dtype=np.int32)),
+                      shape=(128, 96), blocksize=(32, 32))
+    a = bsr.DeviceBsr8.from_scipy(m, device=cuda_device)
+    assert a.num_blocks == 0 and a.indptr.numel() == 17 and not a.indptr.any()

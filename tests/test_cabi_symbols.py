@@ -27,8 +27,8 @@ def test_library_builds_and_exports_all_symbols():
 
 
 def test_struct_layout_matches_header():
-    # 4 int64 + 2 int32 + 10 pointers + 1 int64 + 1 pointer
-    assert ctypes.sizeof(_cabi.LfHyb) == 4 * 8 + 2 * 4 + 10 * 8 + 8 + 8
+    # 4 int64 + 2 int32 + 10 pointers + 1 int64
+    assert ctypes.sizeof(_cabi.LfHyb) == 4 * 8 + 2 * 4 + 10 * 8 + 8
 
 
 def test_workspace_queries_are_pure():
