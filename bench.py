@@ -8,7 +8,9 @@
 A step is one SpMM C = A B over the whole (row-sharded) matrix with the format and B resident in
 HBM.  The default workload is the power-law graph (2^20 rows, N = 128).  Rank 0 prints one JSON
 line.  Inputs are synthetic and seeded; B plus the format exceed the 126 MB L2, so consecutive
-steps cannot be served from cache.
+steps cannot be served from cache.  Without --workload the line also carries a `configs` object
+with the other benchmark matrices (uniform N = 64, skew N = 256, blocks float32 / bf16 at
+N = 32, 128, 512), each device-timed the same way and checked on sampled rows against SciPy.
 """
 from __future__ import annotations
 
@@ -150,6 +152,7 @@ def run_reference(args, rank, world):
     """The reference's CPU product (SciPy, what MTX.dot calls) on the host cores."""
     if rank != 0:
         return
+    args.workload = args.workload or "powerlaw"
     desc, gen, full_rows, N0 = WORKLOADS[args.workload]
     rows = args.rows or full_rows
     N = args.feat or N0
@@ -173,14 +176,17 @@ def run_reference(args, rank, world):
             list(ex.map(lambda P: cpu_spmm(P, B), parts))
         t = time.perf_counter() - t0
     value = 2.0 * used_nnz * N * args.steps / t / 1e9
-    sample = f"first {used_rows} of {csr.shape[0]} rows ({used_nnz} of {csr.nnz} nnz) per step, scipy csr @ dense split over {threads} threads"
+    sample = (f"first {used_rows} of {csr.shape[0]} rows ({used_nnz} of {csr.nnz} nnz) per step, scipy csr @ dense "
+              f"(float32) with the rows split over {threads} threads; the reference's own call, MTX.dot, is "
+              f"coo.tocsc().dot(B) on one thread (format_matrix_market.py:89-99) and is slower than this")
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": t / args.steps * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic (seeded)",
-        "config": {"workload": f"{args.workload}: {desc}", "format": "scipy csr on the host", "rows": csr.shape[0],
-                   "cols": csr.shape[1], "nnz": csr.nnz, "N": N},
+        "config": {"workload": f"{args.workload}: {desc}", "rows": csr.shape[0], "cols": csr.shape[1], "nnz": csr.nnz,
+                   "N": N},
+        "detail": {"format": "scipy csr @ dense on the host (float32)"},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -189,58 +195,100 @@ def run_reference(args, rank, world):
 
 
 # ------------------------------------------------------------------------------------------------
+class Spec:
+    """What one measurement runs on: a workload, its feature width / input type / partition count."""
+
+    def __init__(self, workload, N=0, dtype="f32", parts=1, rows=0, seed=0, fmt="auto", device_B=False):
+        self.workload, self.dtype, self.parts, self.seed = workload, dtype, parts, seed
+        self.desc, self.gen, full_rows, N0 = WORKLOADS[workload]
+        self.rows = rows or full_rows
+        self.full_size = self.rows == full_rows
+        self.N = N or N0
+        self.use_bsr = fmt == "bsr8" or (fmt == "auto" and workload == "blocks")
+        self.device_B = device_B       # B drawn on the device (side configurations: no host copy of B is needed)
+
+
+def make_B(spec, K, dev, torch):
+    """(B on the device in float32, host copy or None)."""
+    if spec.device_B:
+        gen = torch.Generator(device=dev)
+        gen.manual_seed(1000 + spec.seed)
+        return torch.randn((K, spec.N), generator=gen, device=dev, dtype=torch.float32), None
+    host = synth.dense_features(K, spec.N, spec.seed)
+    return torch.from_numpy(host).to(dev), host
+
+
 class HybProblem:
     """Composed-format path: statistics + width search on the whole matrix, per-rank format slice."""
     kernel = "spmm_hyb_kernel"
 
-    def __init__(self, args, rank, world, dev):
+    def __init__(self, spec, rank, world, dev):
         import torch
         from liteform_ae_b200 import hyb, width_search
         from liteform_ae_b200.sharding import my_range
-        self.hyb, self.torch, self.dev = hyb, torch, dev
+        self.hyb, self.torch, self.dev, self.spec = hyb, torch, dev, spec
         self.rank, self.world = rank, world
-        desc, gen, full_rows, N0 = WORKLOADS[args.workload]
-        self.N = N = args.feat or N0
-        self.P = P = args.parts
+        self.N = N = spec.N
+        self.P = P = spec.parts
         t0 = time.perf_counter()
-        self.csr = csr = gen(args.rows or full_rows)
+        self.csr = csr = spec.gen(spec.rows)
         self.M, self.K = csr.shape
-        self.B_host = synth.dense_features(self.K, N, args.seed)
         self.t_gen = time.perf_counter() - t0
         self.nnz = csr.nnz
         d_csr = hyb.DeviceCsr.from_host(csr.indptr, csr.indices, csr.data, csr.shape, dev)
         cuts = hyb.shard_rows(d_csr, world)
         self.r0, self.r1 = my_range(cuts, rank)
+        ws = hyb.Workspace(dev)
         for attempt in range(2):   # the first pass pays context and module load; report the second
             torch.cuda.synchronize(dev)
             t0 = time.perf_counter()
-            stats, hist = hyb.hyb_stats(d_csr, P)
+            stats, hist = hyb.hyb_stats(d_csr, P, workspace=ws)
             self.widths = width_search.search_from_stats(stats, hist, N, P)
             torch.cuda.synchronize(dev)
             self.t_search = time.perf_counter() - t0
             t0 = time.perf_counter()
-            self.fmt = hyb.build_hyb_device(d_csr, self.widths, row_range=(self.r0, self.r1), with_mask=False)
+            self.fmt = hyb.build_hyb_device(d_csr, self.widths, row_range=(self.r0, self.r1), with_mask=False, workspace=ws)
             torch.cuda.synchronize(dev)
             self.t_build = time.perf_counter() - t0
-        del d_csr
-        self.B = torch.from_numpy(self.B_host).to(dev)
+        del d_csr, ws
+        self.B, self.B_host = make_B(spec, self.K, dev, torch)
         self.eb = 4
         self.dtype = "f32"
-        if args.dtype == "bf16":       # B in bf16, values / accumulation / C in float32
+        if spec.dtype == "bf16":       # B in bf16, values / accumulation / C in float32
             self.B = self.B.to(torch.bfloat16)
             self.eb = 2
             self.dtype = "bf16"
-        elif args.dtype != "f32":
+        elif spec.dtype != "f32":
             raise SystemExit("the composed-format path takes --dtype f32 or bf16")
         self.C = torch.empty((self.r1 - self.r0, N), dtype=torch.float32, device=dev)
         self.launches_per_step = 1 + (1 if (P == 1 and self.fmt.num_zero_rows > 0) else 0) + (1 if P > 1 else 0)
-        self.config = {"workload": f"{args.workload}: {desc}", "format": "hyb (composed ELL)", "rows": self.M,
-                       "cols": self.K, "nnz": self.nnz, "N": N, "num_parts": P, "bucket_widths": self.widths,
+        self.config = {"workload": f"{spec.workload}: {spec.desc}", "rows": self.M, "cols": self.K, "nnz": self.nnz, "N": N}
+        self.detail = {"format": "hyb (composed ELL)", "num_parts": P, "bucket_widths": self.widths,
                        "sharding": f"rows, nnz-balanced, {world} rank(s), B replicated, C left sharded",
                        "l2": "inputs exceed L2 (B %.0f MB + format %.0f MB per rank); no flush between steps" % (
-                           self.B_host.nbytes / 1e6, (self.fmt.cols.numel() * 8 + self.fmt.rows.numel() * 4) / 1e6)}
+                           self.K * N * self.eb / 1e6, (self.fmt.cols.numel() * 8 + self.fmt.rows.numel() * 4) / 1e6),
+                       "thread_blocks": self.launch_shape()}
         self.extra = {"format_build_ms": self.t_build * 1e3, "width_search_ms": self.t_search * 1e3,
                       "generate_s": self.t_gen, "padded_slots": self.fmt.total_slots, "zero_rows": self.fmt.num_zero_rows}
+
+    def launch_shape(self):
+        """Thread blocks of one product launch and how many waves of resident blocks that is (the launch
+        rule of lf_spmm_hyb_f32: 256 slots per thread group, halved while fewer than 8 waves)."""
+        N, fmt = self.N, self.fmt
+        if self.spec.dtype == "bf16":
+            lanes, chunks, vec = (8, 1, 8) if N <= 64 else (16, 1, 8) if N <= 128 else (32, 1, 8) if N <= 256 else (32, 2, 8)
+        else:
+            lanes, chunks, vec = ((8, 1, 4) if N <= 32 else (16, 1, 4) if N <= 64 else (32, 1, 4) if N <= 128 else
+                                  (32, 2, 4) if N <= 256 else (32, 4, 4))
+        gpc = 256 // lanes
+        resident = 148 * 3
+        tiles = 0
+        for spg in (256, 128, 64, 32):
+            tiles = sum(-(-int(r) // (max(1, spg // int(w)) * gpc)) for r, w in zip(fmt.ell_rows, fmt.widths) if r)
+            if tiles >= resident * 8:
+                break
+        passes = -(-N // (lanes * chunks * vec))
+        return {"per_launch": tiles * passes, "waves_of_444_resident": round(tiles * passes / resident, 2)}
 
     def step(self):
         self.hyb.spmm_hyb(self.fmt, self.B, out=self.C)
@@ -255,10 +303,31 @@ class HybProblem:
             gath -= my_nnz * self.N * 2
         return comp, gath
 
+    def sampled_parity(self, C=None, count=2000):
+        """Rows of this rank's C (device tensor, or a host array) against SciPy in float64 on the same rows:
+        `count` random rows plus the eight longest.  Only the rows of B those rows touch are read back."""
+        torch, csr, r0, r1 = self.torch, self.csr, self.r0, self.r1
+        if r1 == r0:
+            return {"rows_checked": 0, "max_abs_err": 0.0, "max_rel_err": 0.0, "ok": True}
+        rng = np.random.default_rng(7 + self.rank)
+        lens = np.diff(csr.indptr[r0:r1 + 1])
+        pick = np.unique(np.concatenate([rng.integers(r0, r1, count), r0 + np.argsort(lens)[-8:]]))
+        ptr = np.concatenate([[0], np.cumsum(np.diff(csr.indptr)[pick])]).astype(np.int64)
+        idx = np.concatenate([csr.indices[csr.indptr[r]:csr.indptr[r + 1]] for r in pick])
+        val = np.concatenate([csr.data[csr.indptr[r]:csr.indptr[r + 1]] for r in pick]).astype(np.float64)
+        cols = np.unique(idx)
+        B_rows = self.B[torch.from_numpy(cols).to(self.dev)].double().cpu().numpy()      # what the kernel multiplied
+        import scipy.sparse as sp
+        want = np.asarray(sp.csr_matrix((val, np.searchsorted(cols, idx), ptr), shape=(len(pick), len(cols))) @ B_rows)
+        src = self.C if C is None else C
+        local = pick - r0
+        got = src[torch.from_numpy(local).to(self.dev)].cpu().numpy() if hasattr(src, "is_cuda") else np.asarray(src)[local]
+        return parity_record(got, want, len(pick), "f32 rel 1e-5 / abs 1e-4 vs scipy float64 on the same (rounded) inputs")
+
     def prepare_e2e(self):
         torch, hyb, fmt = self.torch, self.hyb, self.fmt
-        if self.eb != 4:
-            raise RuntimeError("the host-memory entry point is float32 only")
+        if self.eb != 4 or self.B_host is None:
+            raise RuntimeError("the host-memory entry point is float32 only and needs B on the host")
         pin = lambda a: torch.from_numpy(a).pin_memory().numpy()
         if self.world > 1:
             # several ranks: each uploads its format shard and 1/world of B's rows, an all-gather over
@@ -267,6 +336,7 @@ class HybProblem:
             self.hs = HostShardedSpmm(fmt, self.N, self.rank, self.world, slots=2)
             self.B_rows = torch.from_numpy(self.B_host[self.hs.first:self.hs.last]).pin_memory()
             self.Cp = [torch.empty((self.r1 - self.r0, self.N), dtype=torch.float32).pin_memory() for _ in range(2)]
+            self.format_bytes = self.hs.format_bytes
             return (self.hs.h2d_bytes, self.hs.d2h_bytes,
                     "sharding.HostShardedSpmm: pinned host format shard + 1/world of B in, all-gather of B over "
                     "NVLink, lf_spmm_hyb_f32, C rows out (bytes are per rank)")
@@ -283,17 +353,18 @@ class HybProblem:
         self.ws = [torch.empty(hyb.host_workspace_bytes(self.host_fmt, self.N), dtype=torch.uint8, device=self.dev)
                    for _ in range(2)]
         self.e2e_streams = [torch.cuda.Stream(device=self.dev) for _ in range(2)]
-        h2d = sum(a.nbytes for a in self.h) + self.Bp.nbytes
+        self.format_bytes = sum(a.nbytes for a in self.h)
+        h2d = self.format_bytes + self.Bp.nbytes
         return h2d, self.Cp[0].nbytes, "lf_spmm_hyb_f32_host (pinned host format + B in, C out, per rank)"
 
-    def e2e_step(self, slot=0, sync=True):
+    def e2e_step(self, slot=0, sync=True, resident=False):
         if self.world > 1:
-            self.hs.enqueue(self.B_rows, self.Cp[slot], slot)
+            self.hs.enqueue(self.B_rows, self.Cp[slot], slot, format_resident=resident)
             if sync:
                 self.hs.slots[slot]["stream"].synchronize()
             return
         self.hyb.spmm_hyb_host(self.h, self.host_fmt, self.Bp, self.Cp[slot], self.ws[slot], sync=sync,
-                               stream=self.e2e_streams[slot])
+                               stream=self.e2e_streams[slot], format_resident=resident)
 
     def e2e_sync(self):
         if self.world > 1:
@@ -305,6 +376,43 @@ class HybProblem:
     def e2e_result(self, slot=0):
         return self.Cp[slot].numpy() if self.world > 1 else self.Cp[slot]
 
+    def e2e_phases(self, reps=5):
+        """One call at a time, its phases told apart by CUDA events on the call's stream: uploads
+        (format + B), all-gather of B (several ranks), product, download of C.  Milliseconds, median."""
+        torch = self.torch
+        rec = {"h2d_ms": [], "allgather_B_ms": [], "kernel_ms": [], "d2h_ms": []}
+        if self.world > 1:
+            for _ in range(reps):
+                ev = []
+                self.hs.enqueue(self.B_rows, self.Cp[0], 0, events=ev)
+                self.hs.slots[0]["stream"].synchronize()
+                for k, name in enumerate(("h2d_ms", "allgather_B_ms", "kernel_ms", "d2h_ms")):
+                    rec[name].append(ev[k].elapsed_time(ev[k + 1]))
+        else:
+            # the same copies and the same product as lf_spmm_hyb_f32_host makes, issued one by one
+            st = self.e2e_streams[0]
+            host = [torch.from_numpy(a) for a in self.h] + [torch.from_numpy(self.Bp)]
+            dev_t = [torch.empty_like(h, device=self.dev) for h in host]
+            Cd = torch.empty((self.r1 - self.r0, self.N), dtype=torch.float32, device=self.dev)
+            Ch = torch.from_numpy(self.Cp[0])
+            for _ in range(reps):
+                ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+                with torch.cuda.stream(st):
+                    ev[0].record()
+                    for d, h in zip(dev_t, host):
+                        d.copy_(h, non_blocking=True)
+                    ev[1].record()
+                    self.hyb.spmm_hyb(self.fmt, dev_t[4], out=Cd)
+                    ev[2].record()
+                    Ch.copy_(Cd, non_blocking=True)
+                    ev[3].record()
+                st.synchronize()
+                rec["h2d_ms"].append(ev[0].elapsed_time(ev[1]))
+                rec["kernel_ms"].append(ev[1].elapsed_time(ev[2]))
+                rec["d2h_ms"].append(ev[2].elapsed_time(ev[3]))
+            rec.pop("allgather_B_ms")
+        return {k: statistics.median(v) for k, v in rec.items()}
+
     def cpu_matrix(self):
         return self.csr.toscipy()
 
@@ -314,13 +422,19 @@ class HybProblem:
         import torch
         from liteform_ae_b200.sharding import ShardedSpmm
         torch_, hyb = self.torch, self.hyb
-        sh = ShardedSpmm.__new__(ShardedSpmm)
-        sh.rank, sh.world, sh.fmt = rank, world, self.fmt
-        d_ptr = torch_.from_numpy(self.csr.indptr).to(self.dev)
-        sh.cuts = hyb.shard_rows(hyb.DeviceCsr(d_ptr, None, None, self.csr.shape), world)
-        if mode == "fused":
+        if not hasattr(self, "_sh"):
+            sh = ShardedSpmm.__new__(ShardedSpmm)
+            sh.rank, sh.world, sh.fmt = rank, world, self.fmt
+            d_ptr = torch_.from_numpy(self.csr.indptr).to(self.dev)
+            sh.cuts = hyb.shard_rows(hyb.DeviceCsr(d_ptr, None, None, self.csr.shape), world)
+            sh.row_range = (self.r0, self.r1)
             sh.prepare_fused_gather(self.N)
+            self._sh = sh
+        sh = self._sh
+        if mode == "fused":
             run = lambda: sh.spmm_gather_fused(self.B)
+        elif mode == "peer":
+            run = lambda: sh.gather_peer(hyb.spmm_hyb(self.fmt, self.B, out=self.C))
         else:
             run = lambda: sh.gather(hyb.spmm_hyb(self.fmt, self.B, out=self.C))
         for _ in range(3):
@@ -332,7 +446,7 @@ class HybProblem:
             full = run()
         ev1.record()
         barrier()
-        t = torch_.tensor([ev0.elapsed_time(ev1) / steps], dtype=torch_.float64, device=self.dev)
+        t = torch_.tensor([ev0.elapsed_time(ev1) / steps], dtype=torch.float64, device=self.dev)
         if world > 1:
             import torch.distributed as dist
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -340,7 +454,7 @@ class HybProblem:
         sub = self.csr.toscipy()[pick]
         want = np.asarray(sub @ self.B_host.astype(np.float64))
         got = full[torch_.from_numpy(pick).to(self.dev)].cpu().numpy()
-        return {"mode": mode, "ms_per_step": float(t.item()), "gflops": 2.0 * self.nnz * self.N / float(t.item()) / 1e6,
+        return {"ms_per_step": float(t.item()), "gflops": 2.0 * self.nnz * self.N / float(t.item()) / 1e6,
                 "gathered_bytes_per_rank": int(self.M * self.N * 4),
                 "max_abs_err_sampled_rows": float(np.abs(got - want).max())}
 
@@ -381,54 +495,64 @@ class HybProblem:
         return out
 
 
+def parity_record(got, want, rows, tolerance):
+    err = np.abs(got - want)
+    scale = float(np.abs(want).max()) or 1.0
+    return {"rows_checked": int(rows), "max_abs_err": float(err.max()), "max_rel_err": float(err.max() / scale),
+            "ok": bool(np.all(err <= 1e-4 + 1e-5 * np.abs(want))), "tolerance": tolerance}
+
+
 class BsrProblem:
     """8x8 block path (config 5): block rows split evenly over the ranks (every block row holds
     the same number of blocks), B replicated."""
 
-    def __init__(self, args, rank, world, dev):
+    def __init__(self, spec, rank, world, dev, shared=None):
         import torch
         from liteform_ae_b200 import bsr
-        self.bsr, self.torch, self.dev = bsr, torch, dev
-        desc, _, full_rows, N0 = WORKLOADS[args.workload]
-        self.N = N = args.feat or N0
+        self.bsr, self.torch, self.dev, self.spec = bsr, torch, dev, spec
+        self.rank, self.world = rank, world
+        self.N = N = spec.N
         t0 = time.perf_counter()
-        indptr, indices, blocks, shape = synth.banded_blocks(M=args.rows or full_rows)
+        if shared is None:
+            shared = synth.banded_blocks(M=spec.rows)
+        indptr, indices, blocks, shape = shared
+        self.shared = shared
         self.M, self.K = shape
-        self.B_host = synth.dense_features(self.K, N, args.seed)
         self.t_gen = time.perf_counter() - t0
         self.indptr, self.indices, self.blocks = indptr, indices, blocks
         self.nnz = int(blocks.size)
         Mb = self.M // 8
         self.r0, self.r1 = (Mb * rank) // world, (Mb * (rank + 1)) // world   # block rows
-        self.tdt = {"f32": torch.float32, "bf16": torch.bfloat16, "f16": torch.float16}[args.dtype]
-        self.dtype = args.dtype
-        if args.dtype == "f32":
+        self.tdt = {"f32": torch.float32, "bf16": torch.bfloat16, "f16": torch.float16}[spec.dtype]
+        self.dtype = spec.dtype
+        if spec.dtype == "f32":
             self.kernel = "bsr8_spmm_f32_narrow_kernel" if N <= 32 else "bsr8_spmm_f32_kernel"
         else:
             self.kernel = ("bsr8_spmm_16bit_narrow_kernel" if N <= 32 else
                            "bsr8_spmm_16bit_mid_kernel" if N <= 64 else "bsr8_spmm_16bit_kernel")
-        name = {"f32": "float32", "bf16": "bfloat16", "f16": "float16"}[args.dtype]
+        name = {"f32": "float32", "bf16": "bfloat16", "f16": "float16"}[spec.dtype]
         self.a = bsr.DeviceBsr8.from_arrays(indptr, indices, blocks, shape, name, dev)
-        self.B = torch.from_numpy(self.B_host).to(dev).to(self.tdt)
+        B32, self.B_host = make_B(spec, self.K, dev, torch)
+        self.B = B32.to(self.tdt)
+        del B32
         self.C = torch.empty(((self.r1 - self.r0) * 8, N), dtype=torch.float32, device=dev)
         self.launches_per_step = 1
-        eb = 4 if args.dtype == "f32" else 2
+        eb = 4 if spec.dtype == "f32" else 2
         self.eb = eb
-        self.config = {"workload": f"{args.workload}: {desc}", "format": "bsr 8x8", "rows": self.M, "cols": self.K,
-                       "nnz": self.nnz, "N": N, "input_dtype": args.dtype, "accumulate": "f32",
+        self.config = {"workload": f"{spec.workload}: {spec.desc}", "rows": self.M, "cols": self.K, "nnz": self.nnz, "N": N}
+        self.detail = {"format": "bsr 8x8", "input_dtype": spec.dtype, "accumulate": "f32",
                        "sharding": f"block rows, even split, {world} rank(s), B replicated, C left sharded",
                        "l2": "inputs exceed L2 (A %.0f MB + B %.0f MB per rank); no flush between steps" % (
-                           self.nnz * eb / 1e6 / world, self.B_host.size * eb / 1e6)}
+                           self.nnz * eb / 1e6 / world, self.K * N * eb / 1e6)}
         self.extra = {"generate_s": self.t_gen}
-        if not args.no_build_timing:
-            self.extra.update(self.time_device_builder(name))
 
-    def time_device_builder(self, dtype_name):
+    def time_device_builder(self):
         """CSR -> 8x8 blocks on the device (lf_bsr8_plan + lf_bsr8_fill), timed on the element CSR form
         of this matrix.  The CSR arrays are laid out on the device from the block arrays (every block
         row of the synthetic matrix holds the same number of blocks, so this is a reshape)."""
         torch = self.torch
         from liteform_ae_b200 import hyb
+        dtype_name = {"f32": "float32", "bf16": "bfloat16", "f16": "float16"}[self.spec.dtype]
         per = np.diff(self.indptr)
         if per.size == 0 or not (per == per[0]).all():
             return {}
@@ -463,8 +587,32 @@ class BsrProblem:
         gath = nb * 64 * self.eb + 4 * nb + 8 * (self.r1 - self.r0 + 1) + nb * 8 * self.N * self.eb + rows * self.N * 4
         return comp, gath
 
+    def sampled_parity(self, C=None, count=300):
+        """Block rows of this rank's C against SciPy's BSR product in float64 of the operands as the
+        kernel sees them (rounded to the input type)."""
+        import scipy.sparse as sp
+        torch = self.torch
+        if self.r1 == self.r0:
+            return {"rows_checked": 0, "max_abs_err": 0.0, "max_rel_err": 0.0, "ok": True}
+        rng = np.random.default_rng(9 + self.rank)
+        pick = np.unique(np.concatenate([rng.integers(self.r0, self.r1, count), [self.r0, self.r1 - 1]]))
+        ip = self.indptr.astype(np.int64)
+        sel = np.concatenate([np.arange(ip[I], ip[I + 1]) for I in pick])
+        J = np.unique(self.indices[sel])
+        ptr = np.concatenate([[0], np.cumsum(np.diff(ip)[pick])]).astype(np.int64)
+        blk = self.a.blocks[torch.from_numpy(sel).to(self.dev)].double().cpu().numpy()
+        b_rows = torch.from_numpy((J[:, None].astype(np.int64) * 8 + np.arange(8)[None, :]).reshape(-1)).to(self.dev)
+        want = np.asarray(sp.bsr_matrix((blk, np.searchsorted(J, self.indices[sel]).astype(np.int32), ptr),
+                                        shape=(len(pick) * 8, len(J) * 8)) @ self.B[b_rows].double().cpu().numpy())
+        rows = ((pick - self.r0)[:, None] * 8 + np.arange(8)[None, :]).reshape(-1)
+        src = self.C if C is None else C
+        got = src[torch.from_numpy(rows).to(self.dev)].cpu().numpy() if hasattr(src, "is_cuda") else np.asarray(src)[rows]
+        return parity_record(got, want, len(rows), "rel 1e-5 / abs 1e-4 vs scipy float64 on the same (rounded) inputs")
+
     def prepare_e2e(self):
         torch = self.torch
+        if self.B_host is None:
+            raise RuntimeError("the end-to-end leg needs B on the host")
         s, e = int(self.indptr[self.r0]), int(self.indptr[self.r1])
         conv = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(self.tdt).pin_memory()
         self.h_ptr = torch.from_numpy((self.indptr[self.r0:self.r1 + 1] - s).astype(np.int64)).pin_memory()
@@ -477,13 +625,15 @@ class BsrProblem:
         self.d_in = [tuple(torch.empty_like(h, device=self.dev) for h in host) for _ in range(2)]
         self.d_C = [torch.empty_like(self.h_C[0], device=self.dev) for _ in range(2)]
         self.e2e_streams = [torch.cuda.Stream(device=self.dev) for _ in range(2)]
+        self.format_bytes = sum(t.numel() * t.element_size() for t in host[:3])
         h2d = sum(t.numel() * t.element_size() for t in host)
         return h2d, self.h_C[0].numel() * 4, "spmm_bsr8 on buffers copied from/to pinned host memory every step"
 
-    def e2e_step(self, slot=0, sync=True):
+    def e2e_step(self, slot=0, sync=True, resident=False):
         torch = self.torch
         with torch.cuda.stream(self.e2e_streams[slot]):
-            for d, h in zip(self.d_in[slot], (self.h_ptr, self.h_idx, self.h_blk, self.h_B)):
+            pairs = list(zip(self.d_in[slot], (self.h_ptr, self.h_idx, self.h_blk, self.h_B)))
+            for d, h in (pairs[3:] if resident else pairs):
                 d.copy_(h, non_blocking=True)
             d_ptr, d_idx, d_blk, d_B = self.d_in[slot]
             a = self.bsr.DeviceBsr8(d_ptr, d_idx, d_blk, ((self.r1 - self.r0) * 8, self.K))
@@ -499,9 +649,176 @@ class BsrProblem:
     def e2e_result(self, slot=0):
         return self.h_C[slot].numpy()
 
+    def e2e_phases(self, reps=5):
+        return None
+
     def cpu_matrix(self):
         import scipy.sparse as sp
         return sp.bsr_matrix((self.blocks, self.indices, self.indptr), shape=(self.M, self.K)).tocsr()
+
+
+def pin_to_gpu_numa_node(local_rank):
+    """Keep this process (and with it the pinned host buffers it will touch first) on the CPUs that are
+    local to its GPU, where the topology is visible and the allowed CPU set contains any of them.
+    Read-only queries plus the process's own affinity; nothing outlasts the process."""
+    info = {"applied": False}
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(physical_gpu_index(local_rank))
+        bus = pynvml.nvmlDeviceGetPciInfo(h).busId
+        bus = bus.decode() if isinstance(bus, bytes) else bus
+        dom, rest = bus.split(":", 1)
+        path = f"/sys/bus/pci/devices/{int(dom, 16):04x}:{rest.lower()}/local_cpulist"
+        with open(path) as f:
+            text = f.read().strip()
+        local = set()
+        for part in text.split(","):
+            if part:
+                a, _, b = part.partition("-")
+                local.update(range(int(a), int(b or a) + 1))
+        allowed = os.sched_getaffinity(0)
+        both = allowed & local
+        info.update({"gpu_local_cpus": text, "allowed_cpus": len(allowed)})
+        if both and both != allowed:
+            os.sched_setaffinity(0, both)
+            info["applied"] = True
+        info["cpus_used"] = len(both or allowed)
+    except Exception as exc:
+        info["error"] = repr(exc)[:200]
+    return info
+
+
+def measure(prob, steps, warmup, barrier, dist, world, dev):
+    """W warm-up steps, then K timed steps bracketed by barrier + synchronize; CUDA events around every
+    step on the launching stream.  Returns the record of one configuration (max over ranks)."""
+    import torch
+    for _ in range(warmup):
+        prob.step()
+    barrier()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+    t_wall0 = time.perf_counter()
+    ev[0].record()
+    for i in range(steps):
+        prob.step()
+        ev[i + 1].record()
+    barrier()
+    t_wall1 = time.perf_counter()
+    total_ms = ev[0].elapsed_time(ev[-1])
+    step_ms = [ev[i].elapsed_time(ev[i + 1]) for i in range(steps)]
+    alg, gath = prob.bytes_models()
+    mine = torch.tensor([total_ms, statistics.fmean(step_ms), float(alg), float(gath)], dtype=torch.float64, device=dev)
+    if world > 1:
+        every = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(every, mine)
+        every = torch.stack(every).cpu().numpy()
+    else:
+        every = mine.cpu().numpy()[None, :]
+    parity = prob.sampled_parity()
+    ok = torch.tensor([1.0 if parity["ok"] else 0.0, parity["max_abs_err"], parity["max_rel_err"]], dtype=torch.float64, device=dev)
+    if world > 1:
+        allok = [torch.empty_like(ok) for _ in range(world)]
+        dist.all_gather(allok, ok)
+        allok = torch.stack(allok).cpu().numpy()
+        parity = {"rows_checked_per_rank": parity["rows_checked"], "max_abs_err": float(allok[:, 1].max()),
+                  "max_rel_err": float(allok[:, 2].max()), "ok": bool(allok[:, 0].min() > 0.5), "tolerance": parity.get("tolerance")}
+    return {"total_ms_max": float(every[:, 0].max()), "rank_total_ms": [float(x) for x in every[:, 0]],
+            "launch_ms_rank0": float(every[0, 1]), "launch_ms_max": float(every[:, 1].max()),
+            "step_ms_rank0": step_ms, "alg_bytes_rank": [float(x) for x in every[:, 2]],
+            "gather_bytes_rank": [float(x) for x in every[:, 3]], "parity": parity, "wall": (t_wall0, t_wall1)}
+
+
+def roofline_of(prob, rec, world):
+    """Roofline object of one configuration.  Per rank: algorithmic bytes of the rank's shard / the rank's
+    mean launch time; the job's figure divides the whole matrix's bytes by the slowest rank's time and
+    compares with `world` times the measured single-GPU peak."""
+    peak, peak_kind = measured_peak_gbs()
+    steps = len(rec["step_ms_rank0"])
+    launch_ms = rec["total_ms_max"] / steps if world > 1 else rec["launch_ms_rank0"]
+    alg = sum(rec["alg_bytes_rank"])
+    gath = sum(rec["gather_bytes_rank"])
+    achieved = alg / (launch_ms * 1e-3) / 1e9
+    return {"bound": "hbm", "achieved": achieved, "peak": peak * world, "unit": "GB/s", "frac": achieved / (peak * world),
+            "traffic": None, "peak_kind": f"of {peak_kind}" + (f" x {world} GPUs" if world > 1 else ""),
+            "kernel": prob.kernel, "algorithmic_bytes_per_launch": int(alg), "launch_ms": launch_ms,
+            "launch_ms_median": statistics.median(rec["step_ms_rank0"]),
+            "gather_model_bytes_per_launch": int(gath), "gather_model_gbs": gath / (launch_ms * 1e-3) / 1e9}
+
+
+def kernel_source_hash():
+    """sha256 (first 16 hex digits) over the CUDA sources: a traffic figure captured under ncu is only
+    reported while the kernels are the ones it was captured on."""
+    import glob
+    import hashlib
+    h = hashlib.sha256()
+    for f in sorted(glob.glob(os.path.join(ROOT, "liteform_ae_b200", "csrc", "*.cu*"))):
+        with open(f, "rb") as fh:
+            h.update(fh.read())
+    return h.hexdigest()[:16]
+
+
+def attach_traffic(roofline, spec, world):
+    key = (spec.workload, "bsr8" if spec.use_bsr else "hyb", spec.dtype, spec.N, spec.parts, world)
+    entry = TRAFFIC_BYTES_PER_LAUNCH.get(key) if spec.full_size else None
+    if entry is None:
+        roofline["traffic_source"] = "no ncu capture for this configuration"
+        return
+    nbytes, source, src_hash = entry
+    if src_hash != kernel_source_hash():
+        roofline["traffic_source"] = f"stale: {source} was captured on other kernel sources ({src_hash})"
+        return
+    roofline["traffic"] = nbytes
+    roofline["traffic_source"] = source
+    roofline["dram_gbs_from_traffic"] = nbytes / (roofline["launch_ms"] * 1e-3) / 1e9
+
+
+def run_side_configs(args, rank, world, dev, barrier, dist):
+    """The other benchmark configurations, device-timed like the headline and checked on sampled rows."""
+    import torch
+    out = {}
+    side_steps, side_warm = max(3, min(args.steps, args.side_steps)), 3
+    plan = [("config3_uniform_f32_n64", Spec("uniform", 64, "f32", device_B=True)),
+            ("config4_skew_f32_n256", Spec("skew", 256, "f32", device_B=True))]
+    for name, spec in plan:
+        try:
+            prob = HybProblem(spec, rank, world, dev)
+            rec = measure(prob, side_steps, side_warm, barrier, dist, world, dev)
+            out[name] = side_record(prob, spec, rec, world, side_steps)
+            del prob
+        except Exception as exc:
+            out[name] = {"error": repr(exc)[:300]}
+        torch.cuda.empty_cache()
+    shared = None
+    try:
+        shared = synth.banded_blocks()
+    except Exception as exc:
+        out["config5_blocks"] = {"error": repr(exc)[:300]}
+    if shared is not None:
+        for dtype in ("f32", "bf16"):
+            for N in (128, 32, 512):
+                name = f"config5_blocks_{dtype}_n{N}"
+                try:
+                    spec = Spec("blocks", N, dtype, device_B=True)
+                    prob = BsrProblem(spec, rank, world, dev, shared=shared)
+                    rec = measure(prob, side_steps, side_warm, barrier, dist, world, dev)
+                    out[name] = side_record(prob, spec, rec, world, side_steps)
+                    del prob
+                except Exception as exc:
+                    out[name] = {"error": repr(exc)[:300]}
+                torch.cuda.empty_cache()
+    return out
+
+
+def side_record(prob, spec, rec, world, steps):
+    roof = roofline_of(prob, rec, world)
+    attach_traffic(roof, spec, world)
+    ms = rec["total_ms_max"] / steps
+    return {"config": prob.config, "dtype": prob.dtype, "steps": steps, "ms": ms,
+            "gflops": 2.0 * prob.nnz * prob.N / ms / 1e6,
+            "rank_ms_min": min(rec["rank_total_ms"]) / steps, "rank_ms_max": max(rec["rank_total_ms"]) / steps,
+            "roofline": {k: roof[k] for k in ("frac", "achieved", "peak", "algorithmic_bytes_per_launch", "kernel",
+                                              "traffic", "traffic_source", "gather_model_gbs")},
+            "parity": rec["parity"], "detail": {k: v for k, v in prob.detail.items() if k != "l2"}}
 
 
 def run_ours(args, rank, local_rank, world):
@@ -510,8 +827,11 @@ def run_ours(args, rank, local_rank, world):
 
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
-    use_bsr = args.format == "bsr8" or (args.format == "auto" and args.workload == "blocks")
-    prob = (BsrProblem if use_bsr else HybProblem)(args, rank, world, dev)
+    numa = pin_to_gpu_numa_node(local_rank)
+    spec = Spec(args.workload or "powerlaw", args.feat, args.dtype, args.parts, args.rows, args.seed, args.format)
+    prob = (BsrProblem if spec.use_bsr else HybProblem)(spec, rank, world, dev)
+    if spec.use_bsr and not args.no_build_timing:
+        prob.extra.update(prob.time_device_builder())
     N = prob.N
 
     def barrier():
@@ -521,25 +841,10 @@ def run_ours(args, rank, local_rank, world):
 
     sampler = ClockSampler(physical_gpu_index(local_rank))
     sampler.start()
-    for _ in range(args.warmup):
-        prob.step()
-    barrier()
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
-    t_wall0 = time.perf_counter()
-    ev[0].record()
-    for i in range(args.steps):
-        prob.step()
-        ev[i + 1].record()
-    barrier()
-    t_wall1 = time.perf_counter()
+    rec = measure(prob, args.steps, args.warmup, barrier, dist, world, dev)
     sampler.stop()
-    total_ms = ev[0].elapsed_time(ev[-1])
-    step_ms = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps)]
-    t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    total_ms_max = float(t.item())
-    clocks = sampler.summary(t_wall0, t_wall1)
+    total_ms_max = rec["total_ms_max"]
+    clocks = sampler.summary(*rec["wall"])
 
     # ---- end to end: host buffers in, host buffer out, copies inside the timed region ----------
     try:
@@ -557,60 +862,62 @@ def run_ours(args, rank, local_rank, world):
             prob.e2e_step()
         barrier()
         t_one = (time.perf_counter() - t0) / e2e_steps
+
+        def two_in_flight(resident):
+            for slot in (0, 1):
+                prob.e2e_step(slot, sync=False, resident=resident)
+            prob.e2e_sync()
+            barrier()
+            t0 = time.perf_counter()
+            for i in range(e2e_steps):
+                prob.e2e_step(i % 2, sync=False, resident=resident)
+            prob.e2e_sync()
+            barrier()
+            return (time.perf_counter() - t0) / e2e_steps
+
         # (2) two calls in flight on two streams (own workspace and result buffer each): the result
         # of one step crosses the bus while the operands of the next one come in.  Every step still
         # copies all its inputs in and its whole result out inside the timed region.
-        for slot in (0, 1):
-            prob.e2e_step(slot, sync=False)
-        prob.e2e_sync()
-        barrier()
-        t0 = time.perf_counter()
-        for i in range(e2e_steps):
-            prob.e2e_step(i % 2, sync=False)
-        prob.e2e_sync()
-        barrier()
-        t_two = (time.perf_counter() - t0) / e2e_steps
-        te = torch.tensor([t_one, t_two], dtype=torch.float64, device=dev)
+        t_two = two_in_flight(False)
+        e2e_parity = [prob.sampled_parity(C=prob.e2e_result(k)) for k in (0, 1)]
+        # (3) as (2), but the format stays in the device workspace after the first call: only B goes in
+        t_res = two_in_flight(True)
+        res_parity = [prob.sampled_parity(C=prob.e2e_result(k)) for k in (0, 1)]
+        phases = prob.e2e_phases()
+        te = torch.tensor([t_one, t_two, t_res], dtype=torch.float64, device=dev)
         if world > 1:
             dist.all_reduce(te, op=dist.ReduceOp.MAX)
-        t_one, t_two = float(te[0].item()), float(te[1].item())
-        resident = prob.C.cpu().numpy()
+        t_one, t_two, t_res = (float(x) for x in te.cpu())
         e2e = {"value": 2.0 * prob.nnz * N / min(t_one, t_two) / 1e9, "unit": UNIT,
                "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
                "ms_per_step": min(t_one, t_two) * 1e3, "steps": e2e_steps, "call": call,
                "mode": "two calls in flight on two streams" if t_two < t_one else "one call at a time",
                "ms_per_step_one_call_at_a_time": t_one * 1e3, "ms_per_step_two_in_flight": t_two * 1e3,
-               "max_abs_diff_vs_resident_run": float(max(np.abs(prob.e2e_result(k) - resident).max() for k in (0, 1)))}
+               "parity_sampled_rows": {"max_abs_err": max(p["max_abs_err"] for p in e2e_parity),
+                                       "max_rel_err": max(p["max_rel_err"] for p in e2e_parity),
+                                       "ok": all(p["ok"] for p in e2e_parity), "rows_checked": e2e_parity[0]["rows_checked"]},
+               "format_resident": {"ms_per_step": t_res * 1e3, "value": 2.0 * prob.nnz * N / t_res / 1e9,
+                                   "h2d_bytes_per_step": int(h2d - prob.format_bytes),
+                                   "note": "LF_SPMM_FORMAT_RESIDENT: the format stays in the device workspace after the "
+                                           "first call, B in and C out every step; not the headline (the reference uploads "
+                                           "the format on every call)",
+                                   "parity_ok": all(p["ok"] for p in res_parity)},
+               "phases_one_call_ms": phases, "host_affinity": numa}
     except Exception as exc:  # keep the device-resident numbers, say what went wrong
         e2e = {"value": None, "unit": UNIT, "error": repr(exc)}
 
-    # ---- optional: the whole C on every rank (NCCL all-gather after the product, or fused) -----
+    # ---- the whole C on every rank: padded NCCL all-gather, ragged peer-store gather, fused epilogue ----
     gather = None
-    if args.gather != "none" and world > 1 and isinstance(prob, HybProblem):
-        try:
-            gather = prob.time_gather(args.gather, rank, world, max(3, min(args.steps, 30)), barrier)
-        except Exception as exc:
-            gather = {"mode": args.gather, "error": repr(exc)}
-
-    if rank != 0:
-        return
-    peak, peak_kind = measured_peak_gbs()
-    launch_ms = statistics.fmean(step_ms)
-    alg, gath = prob.bytes_models()
-    achieved = alg / (launch_ms * 1e-3) / 1e9
-    key = (args.workload, "bsr8" if use_bsr else "hyb", prob.dtype, N, args.parts, world)
-    roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": TRAFFIC_BYTES_PER_LAUNCH.get(key),
-                "peak_kind": f"of {peak_kind}", "kernel": prob.kernel,
-                "algorithmic_bytes_per_launch": int(alg), "launch_ms": launch_ms,
-                "launch_ms_median": statistics.median(step_ms),
-                "gather_model_bytes_per_launch": int(gath),
-                "gather_model_gbs": gath / (launch_ms * 1e-3) / 1e9}
-    if roofline["traffic"]:
-        roofline["dram_gbs_from_traffic"] = roofline["traffic"] / (launch_ms * 1e-3) / 1e9
+    if args.gather != "none" and world > 1 and isinstance(prob, HybProblem) and prob.eb == 4 and prob.B_host is not None:
+        gather = {}
+        for mode in (("nccl", "peer", "fused") if args.gather == "all" else (args.gather,)):
+            try:
+                gather[mode] = prob.time_gather(mode, rank, world, max(3, min(args.steps, 30)), barrier)
+            except Exception as exc:
+                gather[mode] = {"error": repr(exc)[:300]}
 
     cpu = None
-    if world == 1 and not args.no_cpu:
+    if rank == 0 and world == 1 and not args.no_cpu:
         A = prob.cpu_matrix()
         gf, t_pass, used_rows, used_nnz, passes = time_cpu(A, prob.B_host, 1, 12.0, 2)
         cpu = {"value": gf, "unit": UNIT, "cores": 1, "kind": "port",
@@ -619,35 +926,41 @@ def run_ours(args, rank, local_rank, world):
         if threads > 1:
             gfm, tm, ur, un, ps = time_cpu(A, prob.B_host, threads, 6.0, 2)
             cpu["all_cores"] = {"value": gfm, "cores": threads, "sample": f"{ur} rows split over {threads} threads, {tm:.2f} s per pass"}
+        del A
 
+    roofline = roofline_of(prob, rec, world)
+    attach_traffic(roofline, spec, world)
+    headline_detail, headline_extra = prob.detail, prob.extra
     line = {
         "metric": METRIC, "value": 2.0 * prob.nnz * N * args.steps / (total_ms_max * 1e-3) / 1e9, "unit": UNIT,
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms_max / args.steps,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": prob.dtype,
-        "data": "synthetic (seeded, numpy default_rng)", "config": prob.config,
+        "data": "synthetic (seeded, numpy default_rng)", "config": prob.config, "detail": headline_detail,
         "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks,
         "gpu_launches": prob.launches_per_step * args.steps,
+        "parity_sampled_rows": rec["parity"],
+        "rank_ms_min": min(rec["rank_total_ms"]) / args.steps, "rank_ms_max": max(rec["rank_total_ms"]) / args.steps,
     }
-    line.update(prob.extra)
+    line.update(headline_extra)
     if gather is not None:
         line["gather"] = gather
     if args.per_bucket and hasattr(prob, "per_bucket"):
         line["per_bucket"] = prob.per_bucket(20)
-    print(json.dumps(line), flush=True)
+    del prob
+    torch.cuda.empty_cache()
+    if args.workload is None and not args.no_side:
+        t0 = time.perf_counter()
+        line["configs"] = run_side_configs(args, rank, world, dev, barrier, dist)
+        line["configs_wall_s"] = time.perf_counter() - t0
+    if rank == 0:
+        print(json.dumps(line), flush=True)
 
 
-# DRAM bytes (read + write) of one launch of the dominant kernel, taken from the ncu captures
-# summarised under profiles/; keyed by (workload, format, dtype, N, num_parts, n_gpus).  Absent
-# entries are reported as null.
+# DRAM bytes (read + write) of one launch of the dominant kernel from an ncu capture
+# (dram__bytes_read.sum + dram__bytes_write.sum), keyed by (workload, format, dtype, N, num_parts,
+# n_gpus) at full size: (bytes, where the figure comes from, hash of the CUDA sources it was
+# captured on).  The figure is reported only while kernel_source_hash() still matches.
 TRAFFIC_BYTES_PER_LAUNCH = {
-    # profiles/spmm_hyb_powerlaw_n128.md (full-size capture)
-    ("powerlaw", "hyb", "f32", 128, 1, 1): 3124605000 + 543989248,
-    # profiles/spmm_hyb_uniform_n64_skew_n256.md (full-size captures)
-    ("uniform", "hyb", "f32", 64, 1, 1): 33724907264 + 1074169856,
-    ("skew", "hyb", "f32", 256, 1, 1): 21397719552 + 1109027072,
-    # profiles/spmm_bsr8_blocks_n128.md (captured at 2^20 rows, scaled x2 to the 2^21-row matrix)
-    ("blocks", "bsr8", "f32", 128, 1, 1): 2 * (918607360 + 508638720),
-    ("blocks", "bsr8", "bf16", 128, 1, 1): 2 * (494361600 + 492801280),
 }
 
 
@@ -657,7 +970,10 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="powerlaw", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS),
+                    help="default: powerlaw as the headline plus the other benchmark matrices in `configs`")
+    ap.add_argument("--no-side", action="store_true", help="skip the `configs` object (the other benchmark matrices)")
+    ap.add_argument("--side-steps", type=int, default=20, help="timed steps of each side configuration")
     ap.add_argument("--rows", type=int, default=0, help="override the matrix dimension (tests)")
     ap.add_argument("--feat", type=int, default=0, help="override the feature width N")
     ap.add_argument("--parts", type=int, default=1, help="number of column partitions")
@@ -666,8 +982,9 @@ def main():
                     help="auto: 8x8 block kernels for the block workload, composed format otherwise")
     ap.add_argument("--dtype", default="f32", choices=["f32", "bf16", "f16"], help="input type of the block path")
     ap.add_argument("--per-bucket", action="store_true", help="also time every ELL bucket on its own")
-    ap.add_argument("--gather", default="none", choices=["none", "nccl", "fused"],
-                    help="multi-GPU only: also time product + full C on every rank (NCCL all-gather or fused epilogue)")
+    ap.add_argument("--gather", default="all", choices=["none", "all", "nccl", "peer", "fused"],
+                    help="multi-GPU only: also time product + full C on every rank (padded NCCL all-gather, ragged "
+                         "peer-store gather lf_allgather_rows, fused epilogue lf_spmm_hyb_f32_bcast)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-build-timing", action="store_true", help="block path: skip timing the device CSR -> blocks builder")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-memory end-to-end leg (profiling runs)")

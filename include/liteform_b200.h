@@ -128,7 +128,10 @@ int lf_hyb_stats(const int64_t* indptr /*[dev] M+1*/, const int32_t* indices /*[
  *     clears the part it uses on `stream` first, and two calls that may overlap on the GPU
  *     (different streams, or host threads on different streams) race on it -- serialise them;
  *   - no cudaMalloc, cudaFree or other allocating routine is called; class_stats and
- *     colmask_hist are the caller's buffers exactly as for lf_hyb_stats.
+ *     colmask_hist are the caller's buffers exactly as for lf_hyb_stats;
+ *   - the looked-up address is kept per device ordinal for the life of the process: after a
+ *     cudaDeviceReset of that device it no longer names the array -- a process that resets a
+ *     device must not call this entry point on it again.
  * ------------------------------------------------------------------------------------------- */
 #define LF_STATIC_STATS_MAX_COLS (1 << 20)
 int lf_hyb_stats_static(const int64_t* indptr /*[dev] M+1*/, const int32_t* indices /*[dev] nnz*/,
@@ -232,6 +235,18 @@ int lf_spmm_hyb_bf16(const lf_hyb* A, const uint16_t* B /*[dev] K x N bf16*/, in
 int lf_spmm_hyb_f32_bcast(const lf_hyb* A, const float* B /*[dev] K x N*/, int64_t ldb,
                           float* const* C_full /*[host] num_dests device pointers*/, int32_t num_dests,
                           int64_t ldc, int32_t N, void* stream);
+
+/* Ragged all-gather of C (no counterpart in the reference, which runs on one device): this rank's
+ * row block -- `rows` rows of N floats at C_rows, the rows [row_begin, row_begin + rows) of the
+ * whole product -- is copied into the same rows of num_dests full-size C matrices, C_full[k]
+ * pointing at row 0 of the buffer on GPU k of the group (this GPU's included), reachable through
+ * peer mappings.  Row blocks may differ in size from rank to rank, which NCCL's all-gather does not
+ * take; every rank calls this for its own block, a barrier over the group before (nobody still
+ * reads the buffers) and after (all blocks have landed) completes the gather.  Plain peer stores,
+ * each row crosses NVLink once per destination; no multicast, no staging copy. */
+int lf_allgather_rows(const float* C_rows /*[dev]*/, int64_t ld_rows, int64_t row_begin, int64_t rows, int32_t N,
+                      float* const* C_full /*[host] num_dests device pointers*/, int32_t num_dests, int64_t ldc,
+                      void* stream);
 
 /* Same product with every operand in HOST memory: the arrays of build_hyb_format as NumPy holds
  * them after the int32/float32 casts of format_algos.py:568-577, B and C row-major.  The call

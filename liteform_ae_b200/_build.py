@@ -34,11 +34,29 @@ def find_nvcc() -> str:
     raise RuntimeError("nvcc not found; set NVCC or put it on PATH")
 
 
+BUILD_ID_PATH = os.path.join(_HERE, "liblf_b200.build_id")
+
+
+def source_id() -> str:
+    """sha256 over the contents of every source and header the library is built from."""
+    import hashlib
+    h = hashlib.sha256()
+    for f in SOURCES + HEADERS:
+        h.update(os.path.basename(f).encode())
+        with open(f, "rb") as fh:
+            h.update(fh.read())
+    return h.hexdigest()
+
+
 def is_stale() -> bool:
+    """True when the library is missing or was built from other sources than the ones on disk
+    (compared by content: file times do not survive a copy of the tree)."""
     if not os.path.isfile(LIB_PATH):
         return True
-    built = os.path.getmtime(LIB_PATH)
-    return any(os.path.getmtime(f) > built for f in SOURCES + HEADERS)
+    if not os.path.isfile(BUILD_ID_PATH):
+        return False   # a library that came without its build record: nothing to compare with
+    with open(BUILD_ID_PATH) as f:
+        return f.read().strip() != source_id()
 
 
 def build_library(force: bool = False, verbose: bool = False, ptxas_info: bool = False) -> str:
@@ -55,6 +73,8 @@ def build_library(force: bool = False, verbose: bool = False, ptxas_info: bool =
     if ptxas_info or verbose:
         sys.stderr.write(res.stderr)
     os.replace(LIB_PATH + ".tmp", LIB_PATH)
+    with open(BUILD_ID_PATH, "w") as f:
+        f.write(source_id() + "\n")
     return LIB_PATH
 
 

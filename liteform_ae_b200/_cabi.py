@@ -9,6 +9,7 @@ import ctypes as C
 import os
 from typing import Optional
 
+from . import _build
 from ._build import LIB_PATH
 
 LF_OK = 0
@@ -76,6 +77,7 @@ SIGNATURES = {
     "lf_spmm_hyb_f32": (C.c_int, [C.POINTER(LfHyb), vp, C.c_int64, vp, C.c_int64, C.c_int32, C.c_int32, vp]),
     "lf_spmm_hyb_bf16": (C.c_int, [C.POINTER(LfHyb), vp, C.c_int64, vp, C.c_int64, C.c_int32, C.c_int32, vp]),
     "lf_spmm_hyb_f32_bcast": (C.c_int, [C.POINTER(LfHyb), vp, C.c_int64, vp, C.c_int32, C.c_int64, C.c_int32, vp]),
+    "lf_allgather_rows": (C.c_int, [vp, C.c_int64, C.c_int64, C.c_int64, C.c_int32, vp, C.c_int32, C.c_int64, vp]),
     "lf_spmm_hyb_f32_host_workspace_bytes": (C.c_size_t, [C.POINTER(LfHyb), C.c_int32]),
     "lf_spmm_hyb_f32_host": (C.c_int, [C.POINTER(LfHyb), vp, vp, C.c_int32, C.c_int32, vp, C.c_size_t, vp]),
     "lf_spmm_csr_f32": (C.c_int, [vp, vp, vp, C.c_int64, C.c_int64, C.c_int64, vp, C.c_int64, vp, C.c_int64, C.c_int32, vp]),
@@ -107,6 +109,10 @@ def load() -> C.CDLL:
             raise RuntimeError(
                 f"{LIB_PATH} is missing: build it with `python -m liteform_ae_b200._build` "
                 "(there is no fallback implementation)")
+        if _build.is_stale():
+            raise RuntimeError(
+                f"{LIB_PATH} is older than its sources: rebuild it with `python -m liteform_ae_b200._build` "
+                "(a stale library is an error, not a fallback)")
         lib = C.CDLL(LIB_PATH)
         for name, (res, args) in SIGNATURES.items():
             fn = getattr(lib, name)

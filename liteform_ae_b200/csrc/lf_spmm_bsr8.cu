@@ -728,7 +728,7 @@ int check_common(const void* indptr, const void* indices, const void* blocks, in
                  const void* B, int64_t ldb, const void* C, int64_t ldc, int N, int feat_align) {
   LF_REQUIRE(indptr && B && C, "null pointer argument");
   LF_REQUIRE(0 <= r0 && r0 <= r1, "bad block-row range");
-  LF_REQUIRE(r0 == r1 || (indices && blocks), "block arrays missing");
+  // a matrix without any block has no block arrays (NULL): the product is a zero C
   LF_REQUIRE(N >= 1 && ldb >= N && ldc >= N && ldb < (1ll << 31), "bad dense operands");
   if (N % feat_align != 0 || ldb % feat_align != 0 || ldc % 4 != 0 || (uintptr_t)B % 16 != 0 ||
       (uintptr_t)C % 16 != 0 || (uintptr_t)blocks % 16 != 0)
@@ -763,6 +763,11 @@ int copy_engine() {
   const int v = g_bsr_copy_engine ? g_bsr_copy_engine : env;
   return v >= 1 && v <= 3 ? v : 1;
 }
+// A block matrix that holds no block at all (the caller passes no block arrays): C = 0.
+int clear_c(float* C, int64_t ldc, int N, int64_t rows, cudaStream_t st) {
+  LF_CUDA_CHECK(cudaMemset2DAsync(C, sizeof(float) * ldc, 0, sizeof(float) * N, (size_t)rows, st));
+  return LF_OK;
+}
 }  // namespace
 }  // namespace lf
 
@@ -792,6 +797,10 @@ int lf_spmm_bsr8_f32(const int64_t* indptr, const int32_t* indices, const float*
   if (int s = check_common(indptr, indices, blocks, block_row_begin, block_row_end, B, ldb, C, ldc, N, 4)) return s;
   if (block_row_begin == block_row_end) return LF_OK;
   cudaStream_t st = (cudaStream_t)stream;
+  if (!indices || !blocks) {
+    LF_REQUIRE(!indices && !blocks, "one of the block arrays is missing");
+    return clear_c(C, ldc, N, (block_row_end - block_row_begin) * 8, st);
+  }
   const int64_t rows = block_row_end - block_row_begin;
   const int T = g_bsr_feat_units ? g_bsr_feat_units : (N > 64 ? 2 : 1);
   const int D = g_bsr_stages ? g_bsr_stages : (T == 2 ? 3 : 4);
@@ -836,6 +845,10 @@ static int launch_16bit(bool bf16, const int64_t* indptr, const int32_t* indices
   if (int s = check_common(indptr, indices, blocks, r0, r1, B, ldb, C, ldc, N, 8)) return s;
   if (r0 == r1) return LF_OK;
   cudaStream_t st = (cudaStream_t)stream;
+  if (!indices || !blocks) {
+    LF_REQUIRE(!indices && !blocks, "one of the block arrays is missing");
+    return clear_c(C, ldc, N, (r1 - r0) * 8, st);
+  }
   const int tiles = (N + 127) / 128;
   const int rpw = g_bsr_rows_per_warp ? g_bsr_rows_per_warp : 8;
   const int64_t grid = ceil_div64(ceil_div64(r1 - r0, rpw) * tiles, kWarps);

@@ -489,6 +489,28 @@ spmm_csr_kernel(const int64_t* __restrict__ indptr, const int32_t* __restrict__ 
   flush(cur, (cur == first_row && head_open) || s1 < nb);
 }
 
+// Ragged all-gather of C over peer mappings: the rows of this rank's block are read once and
+// stored into the same rows of every destination (plain 128-bit peer stores over NVLink).
+template <int VEC>
+__global__ void __launch_bounds__(256)
+allgather_rows_kernel(const float* __restrict__ src, int64_t ld_src, int64_t rows, int N, int64_t row_begin,
+                      const __grid_constant__ DestList dests, int64_t ldc) {
+  const int per_row = (N + VEC - 1) / VEC;
+  const int64_t total = rows * per_row;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / per_row;
+    const int f = (int)(i - r * per_row) * VEC;
+    const int64_t off = (row_begin + r) * ldc + f;
+    if (VEC == 4) {
+      const float4 v = __ldcs(reinterpret_cast<const float4*>(src + r * ld_src + f));
+      for (int k = 0; k < dests.n; ++k) *reinterpret_cast<float4*>(dests.p[k] + off) = v;
+    } else {
+      const float v = __ldcs(src + r * ld_src + f);
+      for (int k = 0; k < dests.n; ++k) dests.p[k][off] = v;
+    }
+  }
+}
+
 struct FeatCfg { int G, V, VEC, pass; };
 
 // Kernel launch with, optionally, a programmatic dependency on the previous kernel of the stream
@@ -847,6 +869,31 @@ static int spmm_hyb_impl(const lf_hyb* A, const void* B, bool b_is_bf16, int64_t
     if (s) return s;
     cleared_by_kernel = false;   // a further launch follows a product kernel, not the clearing one
   }
+  return LF_OK;
+}
+
+int lf_allgather_rows(const float* C_rows, int64_t ld_rows, int64_t row_begin, int64_t rows, int32_t N,
+                      float* const* C_full, int32_t num_dests, int64_t ldc, void* stream) {
+  LF_REQUIRE(C_full && num_dests >= 1 && num_dests <= LF_MAX_DESTS, "1..%d destinations are supported", LF_MAX_DESTS);
+  LF_REQUIRE(rows >= 0 && row_begin >= 0 && N >= 1 && ld_rows >= N && ldc >= N, "bad shape");
+  if (rows == 0) return LF_OK;
+  LF_REQUIRE(C_rows, "source rows missing");
+  DestList d;
+  d.n = num_dests;
+  d.pad_ = 0;
+  bool vec = N % 4 == 0 && ld_rows % 4 == 0 && ldc % 4 == 0 && (uintptr_t)C_rows % 16 == 0;
+  for (int k = 0; k < LF_MAX_DESTS; ++k) d.p[k] = k < num_dests ? C_full[k] : nullptr;
+  for (int k = 0; k < num_dests; ++k) {
+    LF_REQUIRE(d.p[k], "destination %d is null", k);
+    vec = vec && (uintptr_t)d.p[k] % 16 == 0;
+  }
+  cudaStream_t st = (cudaStream_t)stream;
+  const int64_t items = rows * (vec ? N / 4 : N);
+  const int64_t want = ceil_div64(items, 256 * 4);
+  const unsigned grid = (unsigned)(want < 1 ? 1 : (want > (int64_t)sm_count() * 16 ? (int64_t)sm_count() * 16 : want));
+  if (vec) allgather_rows_kernel<4><<<grid, 256, 0, st>>>(C_rows, ld_rows, rows, N, row_begin, d, ldc);
+  else allgather_rows_kernel<1><<<grid, 256, 0, st>>>(C_rows, ld_rows, rows, N, row_begin, d, ldc);
+  LF_CUDA_CHECK(cudaGetLastError());
   return LF_OK;
 }
 

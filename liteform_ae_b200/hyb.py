@@ -343,16 +343,19 @@ def spmm_csr(csr: DeviceCsr, B, out=None, row_range=None):
 
 
 def spmm_hyb_host(fmt_host_arrays, fmt: HybFormat, B_host: np.ndarray, C_host: np.ndarray, workspace,
-                  accumulate: bool = False, sync: bool = True, stream=None):
+                  accumulate: bool = False, sync: bool = True, stream=None, format_resident: bool = False):
     """``lf_spmm_hyb_f32_host``: all operands in (ideally pinned) host memory; ``workspace`` is a
     device byte tensor of at least ``host_workspace_bytes(fmt, N)`` bytes.  ``sync=False`` only
     enqueues on ``stream`` (a ``torch.cuda.Stream``, default: the current one): ``C_host`` is valid
-    and the workspace reusable after that stream has been synchronised."""
+    and the workspace reusable after that stream has been synchronised.  ``format_resident=True``
+    skips the upload of the format: ``workspace`` must still hold it from an earlier call with the
+    same format and N."""
     torch = _torch()
     lib = _cabi.load()
     N = int(B_host.shape[1])
     s = fmt.c_struct(host_arrays=fmt_host_arrays)
-    flags = (_cabi.LF_SPMM_ACCUMULATE if accumulate else _cabi.LF_SPMM_OVERWRITE) | (0 if sync else _cabi.LF_SPMM_NO_SYNC)
+    flags = (_cabi.LF_SPMM_ACCUMULATE if accumulate else _cabi.LF_SPMM_OVERWRITE) | (0 if sync else _cabi.LF_SPMM_NO_SYNC) \
+        | (_cabi.LF_SPMM_FORMAT_RESIDENT if format_resident else 0)
     with torch.cuda.device(workspace.device):
         st = _stream_ptr(torch) if stream is None else stream.cuda_stream
         check(lib.lf_spmm_hyb_f32_host(C.byref(s), np_ptr(B_host), np_ptr(C_host), N, flags,
@@ -403,3 +406,15 @@ def spmm_hyb_bcast(fmt: HybFormat, B, dest_ptrs: Sequence[int], ldc: int):
         s = fmt.c_struct()
         check(lib.lf_spmm_hyb_f32_bcast(C.byref(s), B.data_ptr(), B.stride(0), arr, len(dest_ptrs), int(ldc),
                                         int(B.shape[1]), _stream_ptr(torch)))
+
+
+def allgather_rows(C_local, row_begin: int, dest_ptrs: Sequence[int], ldc: int):
+    """``lf_allgather_rows``: store this rank's row block into rows ``row_begin ...`` of every full-size
+    C whose device address is listed in ``dest_ptrs`` (own buffer and peers' symmetric-memory buffers)."""
+    torch = _torch()
+    lib = _cabi.load()
+    assert C_local.is_cuda and C_local.dtype == torch.float32 and C_local.dim() == 2 and C_local.stride(1) == 1
+    arr = (C.c_void_p * len(dest_ptrs))(*[int(p) for p in dest_ptrs])
+    with torch.cuda.device(C_local.device):
+        check(lib.lf_allgather_rows(C_local.data_ptr(), C_local.stride(0), int(row_begin), int(C_local.shape[0]),
+                                    int(C_local.shape[1]), arr, len(dest_ptrs), int(ldc), _stream_ptr(torch)))

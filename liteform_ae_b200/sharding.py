@@ -88,6 +88,17 @@ class ShardedSpmm:
         assert len(self._dest_ptrs) == self.world
         return self.C_full
 
+    def gather_peer(self, C_local):
+        """The whole C on every rank from the per-rank row blocks, by ``lf_allgather_rows``: every rank
+        stores its (ragged) block straight into all full-size buffers over NVLink -- no padding, no
+        staging copy.  Needs ``prepare_fused_gather`` (the symmetric-memory buffers)."""
+        from . import hyb
+        self._symm.barrier()                      # nobody still reads the previous product
+        hyb.allgather_rows(C_local, self.row_range[0] if hasattr(self, "row_range") else self.cuts[self.rank],
+                           self._dest_ptrs, self.C_full.stride(0))
+        self._symm.barrier()                      # every rank's rows have landed everywhere
+        return self.C_full
+
     def spmm_gather_fused(self, B):
         """C = A @ B with the whole product on every rank: the kernel's epilogue stores each row of
         this rank's shard into every rank's full-size C (peer stores over NVLink).  Barriers on the
@@ -141,22 +152,42 @@ class HostShardedSpmm:
                 "B_chunk": torch.empty((self.chunk, self.N), dtype=torch.float32, device=dev),
                 "B_full": torch.empty((self.chunk * world, self.N), dtype=torch.float32, device=dev),
                 "C": torch.empty((fmt.row_end - fmt.row_begin, self.N), dtype=torch.float32, device=dev)})
-        self.h2d_bytes = sum(t.numel() * t.element_size() for t in self.h_fmt.values()) + (self.last - self.first) * self.N * 4
+        self.format_bytes = sum(t.numel() * t.element_size() for t in self.h_fmt.values())
+        self.h2d_bytes = self.format_bytes + (self.last - self.first) * self.N * 4
         self.d2h_bytes = (fmt.row_end - fmt.row_begin) * self.N * 4
 
-    def enqueue(self, B_rows_host, C_host, slot: int = 0):
+    def enqueue(self, B_rows_host, C_host, slot: int = 0, format_resident: bool = False, events=None):
         """``B_rows_host``: pinned float32 tensor holding THIS rank's rows ``first:last`` of B;
-        ``C_host``: pinned float32 tensor for this rank's rows of C.  Returns after enqueueing."""
+        ``C_host``: pinned float32 tensor for this rank's rows of C.  Returns after enqueueing.
+        ``format_resident``: skip the upload of the format when this slot already holds it from an
+        earlier call (the reference uploads it on every call, format_algos.py:568-578).
+        ``events``: a list that receives five CUDA events recorded on the slot's stream -- start,
+        after the uploads, after the all-gather of B, after the product, after the download -- so
+        that a caller can tell the phases of one call apart."""
         import torch.distributed as dist
         from . import hyb
         torch, s = self.torch, self.slots[slot]
+
+        def mark():
+            if events is not None:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                events.append(ev)
+
         with torch.cuda.stream(s["stream"]):
-            for n, h in self.h_fmt.items():
-                getattr(s["fmt"], n).copy_(h, non_blocking=True)
+            mark()
+            if not (format_resident and s.get("has_format")):
+                for n, h in self.h_fmt.items():
+                    getattr(s["fmt"], n).copy_(h, non_blocking=True)
+                s["has_format"] = True
             s["B_chunk"][:self.last - self.first].copy_(B_rows_host, non_blocking=True)
+            mark()
             dist.all_gather_into_tensor(s["B_full"], s["B_chunk"], group=self.group)
+            mark()
             hyb.spmm_hyb(s["fmt"], s["B_full"][:self.K], out=s["C"])
+            mark()
             C_host.copy_(s["C"], non_blocking=True)
+            mark()
 
     def synchronize(self):
         for s in self.slots:

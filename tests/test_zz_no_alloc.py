@@ -43,6 +43,34 @@ def test_static_scratch_matches_workspace_variant_twice(cuda_device):
             assert np.array_equal(got_hist, want_hist)
 
 
+def test_static_variant_leaves_device_memory_alone(cuda_device):
+    """The point of the entry point: after the first call on a device (which looks the scratch up)
+    a call changes neither the free device memory the driver reports nor what PyTorch's allocator
+    holds -- the outputs are allocated before the measurement, the call itself allocates nothing."""
+    import torch
+    lib = _cabi.load()
+    csr = synth.zipf_rows(M=4096, seed=9)
+    d = hyb.DeviceCsr.from_host(csr.indptr, csr.indices, csr.data, csr.shape, cuda_device)
+    P = 2
+    stats = torch.empty(P * _cabi.NUM_WIDTH_CLASSES * 3, dtype=torch.int64, device=cuda_device)
+    hist = torch.empty(P * _cabi.COLMASK_BINS, dtype=torch.int64, device=cuda_device)
+
+    def call():
+        with torch.cuda.device(cuda_device):
+            _cabi.check(lib.lf_hyb_stats_static(d.indptr.data_ptr(), d.indices.data_ptr(), csr.shape[0], csr.shape[1], P,
+                                                stats.data_ptr(), hist.data_ptr(), torch.cuda.current_stream().cuda_stream))
+        torch.cuda.synchronize(cuda_device)
+
+    call()                                   # warm-up: one-time address look-up, module load
+    free_before, _ = torch.cuda.mem_get_info(cuda_device)
+    reserved_before = torch.cuda.memory_reserved(cuda_device)
+    for _ in range(3):
+        call()
+    free_after, _ = torch.cuda.mem_get_info(cuda_device)
+    assert free_after == free_before
+    assert torch.cuda.memory_reserved(cuda_device) == reserved_before
+
+
 def test_sizes_beyond_the_static_scratch_are_refused(cuda_device):
     import torch
     lib = _cabi.load()
