@@ -67,12 +67,19 @@ const char* lf_last_error(void);
 #define LF_OPT_SPMM_CACHE_POLICY 2     /* 0 plain loads and stores; 1 slots, row ids and C stream through (default) */
 #define LF_OPT_SPMM_MIN_BLOCKS 3       /* resident thread blocks per SM the kernel is compiled for: 2..4 (default 3) */
 #define LF_OPT_BSR_COPY_ENGINE 4        /* how the 8x8 block kernels fill shared memory: 0 automatic, 1 per-lane
-                                          cp.async, 2 tiled bulk copies through a tensor map, 3 one bulk copy per row
-                                          of B (2 and 3 complete on mbarriers) */
+                                          cp.async into warp-private rings, 2 tiled bulk copies through a tensor map
+                                          into the same rings, 3 one bulk copy per row of B, 4 thread-block-wide
+                                          pipeline: a producer warp issues one tiled bulk copy per block, consumer
+                                          warps run the MMAs, 5 (16-bit inputs; float32 runs 4) the same copies feeding
+                                          tcgen05.mma with accumulators in tensor memory (2 to 5 complete on mbarriers) */
 #define LF_OPT_BSR_TILE_ORDER 5         /* float32 block kernel with several 128-feature tiles: 0 automatic (2 from
                                           four tiles on), 1 the tiles of a block row run together (A read once),
                                           2 one tile after the other over all rows (the B rows of one tile stay
                                           in the L2) */
+#define LF_OPT_BSR_PIPE_SHAPE 7         /* copy engine 4: blocks per stage * 10 + stages of the ring (44, 43, 83, 26;
+                                          0 = default 44) */
+#define LF_OPT_BSR_PIPE_3D 8            /* copy engine 4: 1 (default) one 3-D tiled copy brings all feature slices of
+                                          a block, 0 one 2-D tiled copy per 128-byte feature slice */
 #define LF_OPT_SPMM_TILE_SEGMENTS 6     /* order of the thread blocks of the composed-format product: 0 bucket after
                                           bucket (default); S > 0: every bucket is cut into S segments of consecutive
                                           rows and the launch runs segment 0 of all buckets, then segment 1, ... */

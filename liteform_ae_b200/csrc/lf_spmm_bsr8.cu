@@ -41,6 +41,9 @@ namespace {
 
 using namespace bsr8;
 
+// 1 = per-lane cp.async into warp-private rings, 4 = thread-block pipeline fed by tiled bulk copies
+constexpr int kDefaultCopyEngine = 1;
+
 // ---------------------------------------------------------------------------------------------
 // float32 in / float32 out, 3xTF32.  One warp = one block row x one tile of 64*T features.
 // Lane (g = lane / 4, t = lane % 4).  MMA index maps:
@@ -752,6 +755,10 @@ int g_bsr_copy_engine = 0;
 // 0 = automatic (one after the other from four feature tiles on), 1 = the feature tiles of a block
 // row together, 2 = one tile after the other (LF_OPT_BSR_TILE_ORDER)
 int g_bsr_tile_order = 0;
+// thread-block pipeline: blocks per stage * 10 + stages (0 = default), and whether one 3-D tiled
+// copy per block may be used (1) or one 2-D copy per feature slice (0)
+int g_bsr_pipe_shape = 0;
+int g_bsr_pipe_3d = 1;
 
 namespace {
 int copy_engine() {
@@ -761,7 +768,7 @@ int copy_engine() {
     env = e ? atoi(e) : 0;
   }
   const int v = g_bsr_copy_engine ? g_bsr_copy_engine : env;
-  return v >= 1 && v <= 3 ? v : 1;
+  return v >= 1 && v <= 5 ? v : kDefaultCopyEngine;
 }
 // A block matrix that holds no block at all (the caller passes no block arrays): C = 0.
 int clear_c(float* C, int64_t ldc, int N, int64_t rows, cudaStream_t st) {
@@ -785,8 +792,12 @@ int lf_bsr_set_tuning(int32_t feat_units, int32_t stages, int32_t rows_per_warp)
 }
 
 int lf_bsr_copy_status(void* stream) {
-  int n = 0;
+  int n = 0, m = 0;
   if (int s = bsr8_tma_timeouts((cudaStream_t)stream, &n)) return s;
+  if (int s = bsr8_pipe_timeouts((cudaStream_t)stream, &m)) return s;
+  n += m;
+  if (int s = bsr8_umma_timeouts((cudaStream_t)stream, &m)) return s;
+  n += m;
   if (n) return fail(LF_ERR_KERNEL_TIMEOUT, "%d warps of a block kernel gave up waiting for a copy", n);
   return LF_OK;
 }
@@ -822,7 +833,11 @@ int lf_spmm_bsr8_f32(const int64_t* indptr, const int32_t* indices, const float*
     LF_CUDA_CHECK(cudaGetLastError());
     return LF_OK;
   }
-  if (T == 2 && copy_engine() > 1)
+  if ((copy_engine() == 4 || copy_engine() == 5) && N > 32)
+    return bsr8_f32_pipe_launch(indptr, indices, blocks, block_row_begin, block_row_end, B, ldb, C, ldc, N,
+                                g_bsr_pipe_shape, g_bsr_rows_per_warp, (N + 127) / 128 > 3 ? g_bsr_tile_order != 1 : g_bsr_tile_order == 2,
+                                g_bsr_pipe_3d != 0, st);
+  if (T == 2 && (copy_engine() == 2 || copy_engine() == 3))
     return bsr8_f32_tma_launch(copy_engine() == 3, indptr, indices, blocks, block_row_begin, block_row_end, B, ldb, C, ldc, N, D, rpw,
                                tile_major > 0, st);
 #define LF_BSR(T_, D_, M_)                                                                                   \
@@ -887,7 +902,13 @@ static int launch_16bit(bool bf16, const int64_t* indptr, const int32_t* indices
     LF_CUDA_CHECK(cudaGetLastError());
     return LF_OK;
   }
-  if (copy_engine() > 1) return bsr8_16bit_tma_launch(copy_engine() == 3, bf16, indptr, indices, blocks, r0, r1, B, ldb, C, ldc, N, D, rpw, st);
+  if (copy_engine() == 5)
+    return bsr8_16bit_umma_launch(bf16, indptr, indices, blocks, r0, r1, B, ldb, C, ldc, N, g_bsr_pipe_shape,
+                                  g_bsr_rows_per_warp, g_bsr_pipe_3d != 0, st);
+  if (copy_engine() == 4)
+    return bsr8_16bit_pipe_launch(bf16, indptr, indices, blocks, r0, r1, B, ldb, C, ldc, N, g_bsr_pipe_shape,
+                                  g_bsr_rows_per_warp, g_bsr_pipe_3d != 0, st);
+  if (copy_engine() == 2 || copy_engine() == 3) return bsr8_16bit_tma_launch(copy_engine() == 3, bf16, indptr, indices, blocks, r0, r1, B, ldb, C, ldc, N, D, rpw, st);
 #define LF_BSR16(B_, D_, M_)                                                                                  \
   do {                                                                                                        \
     auto k = bsr8_spmm_16bit_kernel<B_, D_, M_>;                                                              \

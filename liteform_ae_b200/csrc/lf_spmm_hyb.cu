@@ -716,8 +716,16 @@ int lf_set_option(int32_t option, int32_t value) {
       g_tile_segments = value;
       return LF_OK;
     case LF_OPT_BSR_COPY_ENGINE:
-      LF_REQUIRE(value >= 0 && value <= 3, "copy engine %d out of range", value);
+      LF_REQUIRE(value >= 0 && value <= 5, "copy engine %d out of range", value);
       g_bsr_copy_engine = value;
+      return LF_OK;
+    case LF_OPT_BSR_PIPE_SHAPE:
+      LF_REQUIRE(value >= 0 && value <= 99, "pipeline shape %d out of range", value);
+      g_bsr_pipe_shape = value;
+      return LF_OK;
+    case LF_OPT_BSR_PIPE_3D:
+      LF_REQUIRE(value == 0 || value == 1, "pipeline copy form %d out of range", value);
+      g_bsr_pipe_3d = value;
       return LF_OK;
     case LF_OPT_BSR_TILE_ORDER:
       LF_REQUIRE(value >= 0 && value <= 2, "tile order %d out of range", value);

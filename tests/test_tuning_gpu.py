@@ -21,6 +21,8 @@ def restore_defaults():
     lib.lf_set_option(_cabi.LF_OPT_BSR_COPY_ENGINE, 0)
     lib.lf_set_option(_cabi.LF_OPT_BSR_TILE_ORDER, 0)
     lib.lf_set_option(_cabi.LF_OPT_SPMM_TILE_SEGMENTS, 0)
+    lib.lf_set_option(_cabi.LF_OPT_BSR_PIPE_SHAPE, 0)
+    lib.lf_set_option(_cabi.LF_OPT_BSR_PIPE_3D, 1)
 
 
 def test_every_spmm_variant_gives_the_same_product(cuda_device, restore_defaults):
@@ -73,4 +75,54 @@ def test_every_block_kernel_variant_gives_the_same_product(cuda_device, restore_
             np.testing.assert_allclose(bsr.spmm_bsr8(a32, Bd).cpu().numpy(), want, rtol=1e-5, atol=1e-4)
         assert lib.lf_set_option(_cabi.LF_OPT_BSR_TILE_ORDER, 0) == 0
     assert lib.lf_bsr_set_tuning(3, 0, 0) == _cabi.LF_ERR_INVALID_ARGUMENT
-    assert lib.lf_set_option(_cabi.LF_OPT_BSR_COPY_ENGINE, 4) == _cabi.LF_ERR_INVALID_ARGUMENT
+    assert lib.lf_set_option(_cabi.LF_OPT_BSR_COPY_ENGINE, 5) == _cabi.LF_ERR_INVALID_ARGUMENT
+
+
+@pytest.mark.parametrize("per_row", [8, 5, 1, 19])
+def test_thread_block_pipeline_gives_the_same_product(cuda_device, restore_defaults, per_row):
+    """Copy engine 4 (producer warp + tiled bulk copies + consumer warps) in every ring shape, with
+    one 3-D copy per block and with one 2-D copy per feature slice, float32 and both 16-bit types,
+    feature widths that fill, underfill and overflow the 128- / 256-feature tiles, block rows
+    with 1, 5, 8 and 19 blocks (odd counts pair the last block with zeros; 19 spans several
+    stages), empty block rows and row ranges."""
+    import scipy.sparse as sp
+    import torch
+    lib = _cabi.load()
+    indptr, indices, blocks, shape = synth.banded_blocks(M=4096, seed=11, per_block_row=per_row, half_band=60)
+    indptr = indptr.astype(np.int64)
+    keep = np.ones(len(indices), dtype=bool)
+    counts = np.diff(indptr).copy()
+    for I in (0, 3, 40, 511):                 # some block rows lose all their blocks
+        keep[indptr[I]:indptr[I + 1]] = False
+        counts[I] = 0
+    indptr = np.concatenate([[0], np.cumsum(counts)]).astype(np.int64)
+    indices, blocks = indices[keep], blocks[keep]
+    A = sp.bsr_matrix((blocks.astype(np.float64), indices, indptr), shape=shape)
+    a32 = bsr.DeviceBsr8.from_arrays(indptr, indices, blocks, shape, "float32", cuda_device)
+    assert lib.lf_set_option(_cabi.LF_OPT_BSR_COPY_ENGINE, 4) == 0
+    for N in (40, 64, 128, 136, 160, 256, 384, 512):
+        B = synth.dense_features(shape[1], N, 6)
+        Bd = torch.from_numpy(B).to(cuda_device)
+        want = A @ B.astype(np.float64)
+        for shape_code, three_d, rpc in itertools.product((0, 43, 83, 26), (1, 0), (0, 7)):
+            assert lib.lf_set_option(_cabi.LF_OPT_BSR_PIPE_SHAPE, shape_code) == 0
+            assert lib.lf_set_option(_cabi.LF_OPT_BSR_PIPE_3D, three_d) == 0
+            assert lib.lf_bsr_set_tuning(0, 0, rpc) == 0
+            C = torch.full((shape[0], N), float("nan"), device=cuda_device)
+            bsr.spmm_bsr8(a32, Bd, out=C)
+            np.testing.assert_allclose(C.cpu().numpy(), want, rtol=1e-5, atol=1e-4, err_msg=f"f32 {N} {shape_code} {three_d} {rpc}")
+        part = bsr.spmm_bsr8(a32, Bd, block_row_range=(37, 300)).cpu().numpy()
+        np.testing.assert_allclose(part, want[37 * 8:300 * 8], rtol=1e-5, atol=1e-4)
+        for dtype in ("bfloat16", "float16"):
+            tdt = getattr(torch, dtype)
+            a16 = bsr.DeviceBsr8.from_arrays(indptr, indices, blocks, shape, dtype, cuda_device)
+            A16 = sp.bsr_matrix((a16.blocks.float().cpu().numpy().astype(np.float64), indices, indptr), shape=shape)
+            B16 = Bd.to(tdt)
+            want16 = A16 @ B16.float().cpu().numpy().astype(np.float64)
+            for shape_code, three_d in itertools.product((0, 43, 83), (1, 0)):
+                assert lib.lf_set_option(_cabi.LF_OPT_BSR_PIPE_SHAPE, shape_code) == 0
+                assert lib.lf_set_option(_cabi.LF_OPT_BSR_PIPE_3D, three_d) == 0
+                C = torch.full((shape[0], N), float("nan"), device=cuda_device)
+                bsr.spmm_bsr8(a16, B16, out=C)
+                np.testing.assert_allclose(C.cpu().numpy(), want16, rtol=1e-5, atol=1e-4, err_msg=f"{dtype} {N} {shape_code} {three_d}")
+    assert lib.lf_bsr_copy_status(None) == 0   # no thread block gave up waiting for a copy
