@@ -43,10 +43,25 @@ class MTX:
             self.name = None
             self.coo_mtx = None
         elif filename in _DGL_NAMES:
-            raise RuntimeError(
-                f"dataset '{filename}' is downloaded through DGL/OGB by the reference "
-                "(format_matrix_market.py:47-56); there is no network here. Build the matrix with "
-                "MTX.from_csr / MTX.from_coo or load a .mtx file.")
+            # The reference fetches these seven graphs through DGL/OGB (format_matrix_market.py:47-56).
+            # Here they are read from local files: <LITEFORM_DATA_DIR>/<name>.npz (scipy.sparse.save_npz
+            # of the adjacency matrix) or <name>.mtx; data is set to ones as the reference does (:53).
+            import os
+            root = os.environ.get("LITEFORM_DATA_DIR", "")
+            self.name = filename
+            npz, mtx = os.path.join(root, filename + ".npz"), os.path.join(root, filename + ".mtx")
+            if root and os.path.isfile(npz):
+                self.coo_mtx = sp.coo_matrix(sp.load_npz(npz))
+            elif root and os.path.isfile(mtx):
+                from scipy.io import mmread
+                self.coo_mtx = sp.coo_matrix(mmread(mtx))
+            else:
+                raise RuntimeError(
+                    f"dataset '{filename}' is downloaded through DGL/OGB by the reference "
+                    "(format_matrix_market.py:47-56); there is no network here. Put <name>.npz or <name>.mtx "
+                    "into the directory named by LITEFORM_DATA_DIR, build the matrix with MTX.from_csr / "
+                    "MTX.from_coo, or load a .mtx file by path.")
+            self.coo_mtx.data = np.ones(len(self.coo_mtx.data))
         else:
             from scipy.io import mmread
             self.name = splitext(basename(filename))[0]

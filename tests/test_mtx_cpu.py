@@ -53,3 +53,22 @@ def test_bsr_with_padding_is_fp16_and_sorted():
     back = sp.bsr_matrix((b.data.astype(np.float32), b.indices, b.indptr), shape=b.shape).toarray()
     assert np.array_equal(back, dense)
     assert str(Bucket(4, 2, 7, [1, 2], {3})).startswith("Bucket(bucket_width=4")
+
+
+def test_named_graphs_load_from_local_files(tmp_path, monkeypatch):
+    """The seven graph names of the reference (format_matrix_market.py:43) resolve to files in
+    LITEFORM_DATA_DIR instead of a download; data becomes ones; without a file the error says what to do."""
+    import pytest
+    import scipy.sparse as sp
+    from scipy.io import mmwrite
+    from liteform_ae_b200.format_matrix_market import MTX
+    a = sp.random(30, 30, density=0.1, format="coo", random_state=3)
+    sp.save_npz(tmp_path / "cora.npz", a.tocsr())
+    mmwrite(str(tmp_path / "pubmed.mtx"), a)
+    monkeypatch.setenv("LITEFORM_DATA_DIR", str(tmp_path))
+    for name in ("cora", "pubmed"):
+        g = MTX(name)
+        assert g.name == name and g.num_edges() == a.nnz and (g.coo_mtx.data == 1).all()
+        assert (g.coo_mtx.tocsr() != (a.tocsr() != 0).astype(float)).nnz == 0
+    with pytest.raises(RuntimeError, match="LITEFORM_DATA_DIR"):
+        MTX("reddit")
