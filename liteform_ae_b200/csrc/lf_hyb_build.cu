@@ -772,7 +772,6 @@ int lf_hyb_stats(const int64_t* indptr, const int32_t* indices, int64_t num_rows
   LF_REQUIRE(num_parts >= 1 && num_parts <= num_cols, "num_parts %d out of range", num_parts);
   LF_REQUIRE(num_parts <= 65535, "num_parts %d exceeds the grid limit", num_parts);
   LF_REQUIRE(num_cols < (1ll << 31), "column indices are 32-bit: %lld columns are not supported", (long long)num_cols);
-  LF_REQUIRE(num_rows == 0 || indices, "indices missing");
   if (workspace_bytes < lf_hyb_stats_workspace_bytes(num_rows, num_cols, num_parts))
     return fail(LF_ERR_WORKSPACE_TOO_SMALL, "stats workspace too small");
   cudaStream_t st = (cudaStream_t)stream;

@@ -375,3 +375,15 @@ def digest_hyb(bucket_widths, rows, cols, mask) -> str:
                 h.update(np.asarray(a.shape, dtype=np.int64).tobytes())
                 h.update(a.tobytes())
     return h.hexdigest()
+
+
+def fp32_product_tolerance(want: np.ndarray, row_nnz: np.ndarray) -> np.ndarray:
+    """Allowed |got - want| per element of a float32-accumulated product row: abs 1e-4 + rel 1e-5 (the
+    benchmark's float32 tolerance) for rows of up to 4096 stored entries; beyond that the absolute
+    part grows with the square root of the row length, as the rounding error of ANY float32
+    summation of n terms does (a 100 000-entry row of U(-1,1) x N(0,1) products has partial sums
+    near 200, one ulp of which is 1.5e-5: 1e-4 absolute is seven ulps of the running sum and not
+    attainable by float32 accumulation in any order -- SciPy's own float32 product misses it too)."""
+    n = np.asarray(row_nnz, dtype=np.float64).reshape(-1, 1)
+    return 1e-4 * np.maximum(1.0, np.sqrt(n / 4096.0)) + 1e-5 * np.abs(want)
+

@@ -5,11 +5,15 @@ A full CPU product of these matrices takes minutes, so each case checks (1) the 
 for the skewed matrix all 64 heavy rows -- against the float64 product of exactly those rows.
 float32: rel 1e-5 / abs 1e-4; bf16 inputs with fp32 accumulation: rel 1e-2 of the largest
 magnitude against the unrounded product, 1e-5 / 1e-4 against the product of the rounded inputs.
+Rows with more than 4096 stored entries (the 64 rows of 100 000 entries of the skewed matrix) get
+the absolute part scaled by sqrt(entries / 4096) -- oracle.hyb_oracle.fp32_product_tolerance says
+why -- and the test also shows that SciPy's float32 product of those rows is no closer.
 """
 import numpy as np
 import pytest
 import scipy.sparse as sp
 
+from oracle import hyb_oracle as ho
 from liteform_ae_b200 import bsr, hyb, synth, width_search as ws
 from tests import cases
 
@@ -46,8 +50,22 @@ def _check_hyb(csr, N, cuda_device, must_include=()):
     assert np.abs(got - colsum_A @ B64).max() <= 1e-6 * scale
     rng = np.random.default_rng(3)
     pick = np.unique(np.concatenate([rng.integers(0, csr.shape[0], 3000), np.asarray(must_include, dtype=np.int64)]))
-    np.testing.assert_allclose(C[torch.from_numpy(pick).to(cuda_device)].cpu().numpy(), _rows_product(csr, pick, B64),
-                               rtol=RTOL, atol=ATOL)
+    got = C[torch.from_numpy(pick).to(cuda_device)].cpu().numpy()
+    want = _rows_product(csr, pick, B64)
+    lens = np.diff(csr.indptr)[pick]
+    err = np.abs(got - want)
+    allowed = ho.fp32_product_tolerance(want, lens)
+    assert (err <= allowed).all(), f"max excess {(err - allowed).max():.3e} at row length {lens[np.argmax((err - allowed).max(axis=1))]}"
+    short = lens <= 4096                       # the benchmark's plain tolerance wherever it is attainable
+    np.testing.assert_allclose(got[short], want[short], rtol=RTOL, atol=ATOL)
+    if (~short).any():                         # long rows: SciPy accumulating in float32 is no closer to float64
+        rows = pick[~short]
+        lens_l = np.diff(csr.indptr)[rows]
+        ptr = np.concatenate([[0], np.cumsum(lens_l)]).astype(np.int64)
+        idx = np.concatenate([csr.indices[csr.indptr[r]:csr.indptr[r + 1]] for r in rows])
+        val = np.concatenate([csr.data[csr.indptr[r]:csr.indptr[r + 1]] for r in rows])
+        scipy32 = np.asarray(sp.csr_matrix((val, idx, ptr), shape=(len(rows), csr.shape[1])) @ B)
+        assert err[~short].max() <= 2.0 * np.abs(scipy32 - want[~short]).max()
     return fmt
 
 

@@ -75,12 +75,13 @@ def test_every_block_kernel_variant_gives_the_same_product(cuda_device, restore_
             np.testing.assert_allclose(bsr.spmm_bsr8(a32, Bd).cpu().numpy(), want, rtol=1e-5, atol=1e-4)
         assert lib.lf_set_option(_cabi.LF_OPT_BSR_TILE_ORDER, 0) == 0
     assert lib.lf_bsr_set_tuning(3, 0, 0) == _cabi.LF_ERR_INVALID_ARGUMENT
-    assert lib.lf_set_option(_cabi.LF_OPT_BSR_COPY_ENGINE, 5) == _cabi.LF_ERR_INVALID_ARGUMENT
+    assert lib.lf_set_option(_cabi.LF_OPT_BSR_COPY_ENGINE, 6) == _cabi.LF_ERR_INVALID_ARGUMENT
 
 
 @pytest.mark.parametrize("per_row", [8, 5, 1, 19])
 def test_thread_block_pipeline_gives_the_same_product(cuda_device, restore_defaults, per_row):
-    """Copy engine 4 (producer warp + tiled bulk copies + consumer warps) in every ring shape, with
+    """Copy engines 4 (producer warp + tiled bulk copies + consumer warps with mma.sync) and 5 (the
+    same copies feeding tcgen05.mma, accumulators in tensor memory; 16-bit inputs) in every ring shape, with
     one 3-D copy per block and with one 2-D copy per feature slice, float32 and both 16-bit types,
     feature widths that fill, underfill and overflow the 128- / 256-feature tiles, block rows
     with 1, 5, 8 and 19 blocks (odd counts pair the last block with zeros; 19 spans several
@@ -119,10 +120,13 @@ def test_thread_block_pipeline_gives_the_same_product(cuda_device, restore_defau
             A16 = sp.bsr_matrix((a16.blocks.float().cpu().numpy().astype(np.float64), indices, indptr), shape=shape)
             B16 = Bd.to(tdt)
             want16 = A16 @ B16.float().cpu().numpy().astype(np.float64)
-            for shape_code, three_d in itertools.product((0, 43, 83), (1, 0)):
+            for engine, shape_code, three_d in itertools.product((4, 5), (0, 43, 83, 46, 86), (1, 0)):
+                assert lib.lf_set_option(_cabi.LF_OPT_BSR_COPY_ENGINE, engine) == 0
                 assert lib.lf_set_option(_cabi.LF_OPT_BSR_PIPE_SHAPE, shape_code) == 0
                 assert lib.lf_set_option(_cabi.LF_OPT_BSR_PIPE_3D, three_d) == 0
                 C = torch.full((shape[0], N), float("nan"), device=cuda_device)
                 bsr.spmm_bsr8(a16, B16, out=C)
-                np.testing.assert_allclose(C.cpu().numpy(), want16, rtol=1e-5, atol=1e-4, err_msg=f"{dtype} {N} {shape_code} {three_d}")
+                np.testing.assert_allclose(C.cpu().numpy(), want16, rtol=1e-5, atol=1e-4,
+                                           err_msg=f"{dtype} {N} engine {engine} {shape_code} {three_d}")
+            assert lib.lf_set_option(_cabi.LF_OPT_BSR_COPY_ENGINE, 4) == 0
     assert lib.lf_bsr_copy_status(None) == 0   # no thread block gave up waiting for a copy
