@@ -834,7 +834,8 @@ def side_record(prob, spec, rec, world, steps):
             "roofline": {k: roof.get(k) for k in ("frac", "achieved", "peak", "algorithmic_bytes_per_launch", "kernel",
                                                   "traffic", "traffic_source", "dram_gbs_from_traffic", "gather_model_gbs",
                                                   "gather_model_bytes_per_clk_per_sm")},
-            "parity": rec["parity"], "detail": {k: v for k, v in prob.detail.items() if k != "l2"}}
+            "parity": rec["parity"], "detail": {k: v for k, v in prob.detail.items() if k != "l2"},
+            "build": {k: prob.extra[k] for k in ("format_build_ms", "width_search_ms", "generate_s") if k in prob.extra}}
 
 
 def run_ours(args, rank, local_rank, world):

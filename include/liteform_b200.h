@@ -80,6 +80,8 @@ const char* lf_last_error(void);
                                           0 = default 44) */
 #define LF_OPT_BSR_PIPE_3D 8            /* copy engine 4: 1 (default) one 3-D tiled copy brings all feature slices of
                                           a block, 0 one 2-D tiled copy per 128-byte feature slice */
+#define LF_OPT_BSR_UMMA_PRODUCER 9      /* copy engine 5: who fills shared memory: 0 (default) one warp issuing tiled bulk
+                                          copies, 2 or 4 = that many warps issuing per-lane cp.async */
 #define LF_OPT_SPMM_TILE_SEGMENTS 6     /* order of the thread blocks of the composed-format product: 0 bucket after
                                           bucket (default); S > 0: every bucket is cut into S segments of consecutive
                                           rows and the launch runs segment 0 of all buckets, then segment 1, ... */

@@ -38,9 +38,11 @@ int bsr8_make_b_map(CUtensorMap* map, int* boxes_per_block, const void* B, int64
 
 // 16-bit inputs on the 5th-generation tensor cores (lf_spmm_bsr8_umma.cu): tcgen05.mma with the
 // accumulators in tensor memory, fed by the same tiled copies.  shape as above.
+// producer: 0 = one warp issuing tiled bulk copies, 2 / 4 = that many warps issuing per-lane cp.async
 int bsr8_16bit_umma_launch(bool bf16, const int64_t* indptr, const int32_t* indices, const uint16_t* blocks, int64_t r0,
                            int64_t r1, const uint16_t* B, int64_t ldb, float* C, int64_t ldc, int N, int shape,
-                           int rows_per_cta, bool allow_3d, cudaStream_t st);
+                           int rows_per_cta, bool allow_3d, int producer, cudaStream_t st);
+extern int g_bsr_umma_producer;   // LF_OPT_BSR_UMMA_PRODUCER
 int bsr8_umma_timeouts(cudaStream_t st, int* count);
 
 extern int g_bsr_pipe_shape;    // LF_OPT_BSR_PIPE_SHAPE

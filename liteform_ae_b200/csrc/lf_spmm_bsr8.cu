@@ -759,6 +759,8 @@ int g_bsr_tile_order = 0;
 // copy per block may be used (1) or one 2-D copy per feature slice (0)
 int g_bsr_pipe_shape = 0;
 int g_bsr_pipe_3d = 1;
+// tcgen05 path: who fills shared memory: 0 one warp issuing tiled bulk copies, 2 / 4 that many warps issuing cp.async
+int g_bsr_umma_producer = 0;
 
 namespace {
 int copy_engine() {
@@ -904,7 +906,7 @@ static int launch_16bit(bool bf16, const int64_t* indptr, const int32_t* indices
   }
   if (copy_engine() == 5)
     return bsr8_16bit_umma_launch(bf16, indptr, indices, blocks, r0, r1, B, ldb, C, ldc, N, g_bsr_pipe_shape,
-                                  g_bsr_rows_per_warp, g_bsr_pipe_3d != 0, st);
+                                  g_bsr_rows_per_warp, g_bsr_pipe_3d != 0, g_bsr_umma_producer, st);
   if (copy_engine() == 4)
     return bsr8_16bit_pipe_launch(bf16, indptr, indices, blocks, r0, r1, B, ldb, C, ldc, N, g_bsr_pipe_shape,
                                   g_bsr_rows_per_warp, g_bsr_pipe_3d != 0, st);

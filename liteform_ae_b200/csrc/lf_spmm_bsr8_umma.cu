@@ -27,6 +27,15 @@
 //
 // An odd block at the end of a stage is paired with a zero tile (written by the producer, made
 // visible to the tensor core with a proxy fence) and a duplicate of its own B rows.
+//
+// Two producers, chosen at launch.  (a) One warp issuing tiled bulk copies (TMA) as described.
+// (b) NP warps copying the same bytes with per-lane 16-byte cp.async into the same swizzled
+// layout (chunk c of row r at c ^ r, written by hand): the tiled copies deliver scattered 128-byte
+// rows at about 22-26 bytes per clock and SM whatever the ring looks like, 32 lanes issuing the
+// same rows with one instruction get more.  cp.async writes through the generic proxy, the tensor
+// core reads through the async proxy: a producer warp waits for its own copies of a stage
+// (cp.async.wait_group), issues fence.proxy.async, then arrives on the stage's mbarrier; padding
+// (a missing pair partner, features beyond N) is zero-filled by the copy itself.
 // Every wait is bounded; a thread block that gives up raises a flag, drains its copies, frees its
 // tensor memory and returns; the host reads the count through lf_bsr_copy_status.  No copy and no
 // commit uses cluster multicast; the tensor map covers memory of this GPU only.
@@ -171,12 +180,17 @@ struct RowPtrs {
   __device__ __forceinline__ int64_t at(int r) const { return __shfl_sync(0xffffffffu, mine, r); }
 };
 
-template <bool BF16, int NS, int SB, int D, int AS, int MINB>
-__global__ void __launch_bounds__(192, MINB)
+// NP = 0: one producer warp issuing tiled bulk copies; NP > 0: NP producer warps issuing cp.async.
+// Warps 0-3 epilogue, then the producer warp(s), then the MMA warp.
+template <bool BF16, int NS, int SB, int D, int AS, int MINB, int NP>
+__global__ void __launch_bounds__((5 + (NP > 0 ? NP : 1)) * 32, MINB)
 bsr8_spmm_umma_kernel(const __grid_constant__ CUtensorMap mapB, const int64_t* __restrict__ indptr,
                       const int32_t* __restrict__ indices, const uint8_t* __restrict__ blocks,
+                      const uint16_t* __restrict__ Bmat, int ldb,
                       int64_t block_row_begin, int64_t block_row_end, float* __restrict__ C, int64_t ldc, int N,
                       int tiles, int rows_per_cta, int boxes_per_block) {
+  constexpr int kProducers = NP > 0 ? NP : 1;
+  constexpr int kMmaWarp = 4 + kProducers;
   using Cfg = UmmaCfg<NS, SB, D, AS>;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -200,7 +214,7 @@ bsr8_spmm_umma_kernel(const __grid_constant__ CUtensorMap mapB, const int64_t* _
     *abort_flag = 0;
 #pragma unroll
     for (int s = 0; s < D; ++s) {
-      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_full + 8 * s, kProducers);   // one arrival per producer warp (the TMA producer adds its byte count)
       mbar_init(bar_empty + 8 * s, 1);
     }
 #pragma unroll
@@ -219,7 +233,69 @@ bsr8_spmm_umma_kernel(const __grid_constant__ CUtensorMap mapB, const int64_t* _
   RowPtrs ptrs;
   ptrs.mine = indptr[I0 + min(lane, R)];
 
-  if (warp == 4) {
+  if (NP > 0 && warp >= 4 && warp < kMmaWarp) {
+    // ---- producers (cp.async): NP warps copy every stage together, 16 bytes per lane and instruction --
+    constexpr int LAG = 2;                      // stages a producer warp keeps in flight before it waits
+    static_assert(D >= LAG + 2, "the ring must hold the stages in flight plus one being multiplied");
+    constexpr int PL = (NP > 0 ? NP : 1) * 32;  // producer lanes
+    const int pl = (warp - 4) * 32 + lane;
+    const int64_t stream_end = ptrs.at(R);
+    int64_t win = ptrs.at(0);
+    int idx_cur = (win + lane < stream_end) ? indices[win + lane] : 0;
+    int q = 0;
+    bool ok = true;
+    auto publish = [&](int stage) {             // this warp's copies of `stage` have landed: hand them over
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_full + 8 * (stage % D));
+    };
+    for (int r = 0; r < R && ok; ++r) {
+      int64_t b = ptrs.at(r);
+      const int64_t be = ptrs.at(r + 1);
+      while (b < be) {
+        const int n = (int)min((int64_t)SB, be - b);
+        const int n_pad = (n + 1) & ~1;
+        const int slot = q % D;
+        const uint32_t round = (uint32_t)(q / D);
+        if (round > 0) {
+          ok = mbar_wait(bar_empty + 8 * slot, (round - 1) & 1u, abort_flag);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+        }
+        if (b + SB > win + 32) {   // keep the block columns of the whole stage inside the window
+          win = b;
+          idx_cur = (win + lane < stream_end) ? indices[win + lane] : 0;
+        }
+        const uint32_t dstB = base_u32 + slot * Cfg::kStageB;
+        // B rows: 16-byte chunk c of the stage = (block k, slice s, row r8, chunk j)
+        for (int c = pl; c < n_pad * NS * 64; c += PL) {
+          const int k = c / (NS * 64), w = c % (NS * 64);
+          const int sl = w >> 6, r8 = (w >> 3) & 7, j = w & 7;
+          const int J = __shfl_sync(0xffffffffu, idx_cur, (int)(b - win) + (k < n ? k : n - 1));
+          const int f = (tile * NS + sl) * 64 + j * 8;
+          const bool live = k < n && f < N;
+          const uint16_t* src = Bmat + ((int64_t)J * 8 + r8) * ldb + (live ? f : 0);
+          cp_async16(dstB + k * Cfg::kBlockB + sl * 1024 + r8 * 128 + ((j ^ r8) << 4), src, live ? 16 : 0);
+        }
+        // A tiles: 8 chunks per block, contiguous in memory
+        if (pl < n_pad * 8) {
+          const int k = pl >> 3;
+          cp_async16(base_u32 + Cfg::kOffA + slot * Cfg::kStageA + pl * 16, blocks + (b + (k < n ? k : 0)) * 128 + (pl & 7) * 16,
+                     k < n ? 16 : 0);
+        }
+        cp_async_commit();
+        if (q >= LAG) {
+          cp_async_wait<LAG>();
+          publish(q - LAG);
+        }
+        ++q;
+        b += n;
+      }
+    }
+    cp_async_wait<0>();                         // also on the way out after giving up: nothing stays in flight
+    if (ok)
+      for (int stage = q >= LAG ? q - LAG : 0; stage < q; ++stage) publish(stage);
+  } else if (NP == 0 && warp == 4) {
     // ---- producer: one tiled copy per block, one bulk copy for the tiles of a stage ------------
     const int64_t stream_end = ptrs.at(R);
     int64_t win = ptrs.at(0);
@@ -247,7 +323,7 @@ bsr8_spmm_umma_kernel(const __grid_constant__ CUtensorMap mapB, const int64_t* _
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           __syncwarp();
         }
-        if (lane == 0) mbar_expect_tx(full, (uint32_t)n_pad * Cfg::kBlockB + (uint32_t)n * 128);
+        if (lane == 0) mbar_expect_tx(full, (uint32_t)n_pad * Cfg::kBlockB + (uint32_t)n * 128);   // the one arrival + bytes
         ++q;
         const uint32_t dstB = base_u32 + slot * Cfg::kStageB;
         for (int k = 0; k < n_pad; ++k) {
@@ -278,7 +354,7 @@ bsr8_spmm_umma_kernel(const __grid_constant__ CUtensorMap mapB, const int64_t* _
         while (!mbar_try_wait(bar_full + 8 * (p % D), (uint32_t)(p / D) & 1u) && clock64() - t0 < kWaitCycles) {}
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == kMmaWarp) {
     // ---- MMA issuer -------------------------------------------------------------------------------
     constexpr uint32_t idesc = instr_desc(BF16, 64, 8);
     int q = 0;      // stages consumed so far
@@ -382,48 +458,56 @@ bsr8_spmm_umma_kernel(const __grid_constant__ CUtensorMap mapB, const int64_t* _
   }
 }
 
-template <bool BF16, int NS, int SB, int D, int AS, int MINB>
-int launch(const CUtensorMap& map, int boxes, const int64_t* indptr, const int32_t* indices, const void* blocks, int64_t r0,
-           int64_t r1, float* C, int64_t ldc, int N, int rows_per_cta, cudaStream_t st) {
+template <bool BF16, int NS, int SB, int D, int AS, int MINB, int NP>
+int launch(const CUtensorMap& map, int boxes, const int64_t* indptr, const int32_t* indices, const void* blocks,
+           const uint16_t* B, int64_t ldb, int64_t r0, int64_t r1, float* C, int64_t ldc, int N, int rows_per_cta,
+           cudaStream_t st) {
   using Cfg = UmmaCfg<NS, SB, D, AS>;
   const int tiles = (N + NS * 64 - 1) / (NS * 64);
   const int64_t grid = ceil_div64(r1 - r0, rows_per_cta) * tiles;
   LF_REQUIRE(grid < (1ll << 31), "too many thread blocks");
-  auto k = bsr8_spmm_umma_kernel<BF16, NS, SB, D, AS, MINB>;
+  auto k = bsr8_spmm_umma_kernel<BF16, NS, SB, D, AS, MINB, NP>;
   LF_CUDA_CHECK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
-  k<<<(unsigned)grid, 192, Cfg::kSmem, st>>>(map, indptr, indices, (const uint8_t*)blocks, r0, r1, C, ldc, N, tiles,
-                                            rows_per_cta, boxes);
+  k<<<(unsigned)grid, (5 + (NP > 0 ? NP : 1)) * 32, Cfg::kSmem, st>>>(map, indptr, indices, (const uint8_t*)blocks, B, (int)ldb,
+                                                                     r0, r1, C, ldc, N, tiles, rows_per_cta, boxes);
   LF_CUDA_CHECK(cudaGetLastError());
   return LF_OK;
 }
 
 }  // namespace
 
-// shape: blocks per stage * 10 + stages (44 default, 83, 46, 86)
+// shape: blocks per stage * 10 + stages (44 default, 83, 46, 86); producer: 0 tiled bulk copies, 2 or 4 = that many
+// warps issuing cp.async
 int bsr8_16bit_umma_launch(bool bf16, const int64_t* indptr, const int32_t* indices, const uint16_t* blocks, int64_t r0,
                            int64_t r1, const uint16_t* B, int64_t ldb, float* C, int64_t ldc, int N, int shape,
-                           int rows_per_cta, bool allow_3d, cudaStream_t st) {
+                           int rows_per_cta, bool allow_3d, int producer, cudaStream_t st) {
   CUtensorMap map = {};
   int boxes = 0;
   const int ns = N > 128 ? 4 : 2;   // 256 features per thread block when there are that many, else 128
-  if (int s = bsr8_make_b_map(&map, &boxes, B, ldb, N, 2, ns, allow_3d)) return s;
+  if (producer == 0)
+    if (int s = bsr8_make_b_map(&map, &boxes, B, ldb, N, 2, ns, allow_3d)) return s;
   const int rpc = rows_per_cta >= 1 && rows_per_cta <= 31 ? rows_per_cta : 31;
-#define LF_UMMA(NS_, SB_, D_, AS_, M_)                                                                            \
-  (bf16 ? launch<true, NS_, SB_, D_, AS_, M_>(map, boxes, indptr, indices, blocks, r0, r1, C, ldc, N, rpc, st)    \
-        : launch<false, NS_, SB_, D_, AS_, M_>(map, boxes, indptr, indices, blocks, r0, r1, C, ldc, N, rpc, st))
+#define LF_UMMA(NS_, SB_, D_, AS_, M_, NP_)                                                                              \
+  (bf16 ? launch<true, NS_, SB_, D_, AS_, M_, NP_>(map, boxes, indptr, indices, blocks, B, ldb, r0, r1, C, ldc, N, rpc, st)    \
+        : launch<false, NS_, SB_, D_, AS_, M_, NP_>(map, boxes, indptr, indices, blocks, B, ldb, r0, r1, C, ldc, N, rpc, st))
+#define LF_UMMA_P(NS_, SB_, D_, AS_, M_) \
+  (producer == 0 ? LF_UMMA(NS_, SB_, D_, AS_, M_, 0) : producer == 4 ? LF_UMMA(NS_, SB_, D_, AS_, M_, 4) : LF_UMMA(NS_, SB_, D_, AS_, M_, 2))
   if (ns == 4) {
     switch (shape) {
-      case 83: return LF_UMMA(4, 8, 3, 2, 2);
-      case 46: return LF_UMMA(4, 4, 6, 2, 2);
-      default: return LF_UMMA(4, 4, 4, 2, 3);
+      case 83: return LF_UMMA_P(4, 8, 4, 2, 1);
+      case 46: return LF_UMMA_P(4, 4, 6, 2, 2);
+      case 24: return LF_UMMA_P(4, 2, 4, 2, 3);
+      default: return LF_UMMA_P(4, 4, 4, 2, 3);
     }
   }
   switch (shape) {
-    case 83: return LF_UMMA(2, 8, 3, 4, 4);
-    case 46: return LF_UMMA(2, 4, 6, 4, 4);
-    case 86: return LF_UMMA(2, 8, 6, 4, 2);
-    default: return LF_UMMA(2, 4, 4, 4, 6);
+    case 83: return LF_UMMA_P(2, 8, 4, 4, 3);
+    case 46: return LF_UMMA_P(2, 4, 6, 4, 4);
+    case 86: return LF_UMMA_P(2, 8, 6, 4, 2);
+    case 24: return LF_UMMA_P(2, 2, 4, 4, 6);
+    default: return LF_UMMA_P(2, 4, 4, 4, 6);
   }
+#undef LF_UMMA_P
 #undef LF_UMMA
 }
 

@@ -723,6 +723,10 @@ int lf_set_option(int32_t option, int32_t value) {
       LF_REQUIRE(value >= 0 && value <= 99, "pipeline shape %d out of range", value);
       g_bsr_pipe_shape = value;
       return LF_OK;
+    case LF_OPT_BSR_UMMA_PRODUCER:
+      LF_REQUIRE(value == 0 || value == 2 || value == 4, "producer %d is not one of 0, 2, 4", value);
+      g_bsr_umma_producer = value;
+      return LF_OK;
     case LF_OPT_BSR_PIPE_3D:
       LF_REQUIRE(value == 0 || value == 1, "pipeline copy form %d out of range", value);
       g_bsr_pipe_3d = value;

@@ -23,6 +23,7 @@ def restore_defaults():
     lib.lf_set_option(_cabi.LF_OPT_SPMM_TILE_SEGMENTS, 0)
     lib.lf_set_option(_cabi.LF_OPT_BSR_PIPE_SHAPE, 0)
     lib.lf_set_option(_cabi.LF_OPT_BSR_PIPE_3D, 1)
+    lib.lf_set_option(_cabi.LF_OPT_BSR_UMMA_PRODUCER, 0)
 
 
 def test_every_spmm_variant_gives_the_same_product(cuda_device, restore_defaults):
@@ -120,10 +121,14 @@ def test_thread_block_pipeline_gives_the_same_product(cuda_device, restore_defau
             A16 = sp.bsr_matrix((a16.blocks.float().cpu().numpy().astype(np.float64), indices, indptr), shape=shape)
             B16 = Bd.to(tdt)
             want16 = A16 @ B16.float().cpu().numpy().astype(np.float64)
-            for engine, shape_code, three_d in itertools.product((4, 5), (0, 43, 83, 46, 86), (1, 0)):
+            for engine, shape_code, three_d in itertools.product((4, 5), (0, 43, 83, 46, 86, 24), (1, 0, 2, 4)):
+                # engine 5: three_d doubles as the producer choice (1 / 0: tiled copies, 3-D / 2-D; 2 / 4: cp.async warps)
+                if engine == 4 and three_d > 1:
+                    continue
                 assert lib.lf_set_option(_cabi.LF_OPT_BSR_COPY_ENGINE, engine) == 0
                 assert lib.lf_set_option(_cabi.LF_OPT_BSR_PIPE_SHAPE, shape_code) == 0
-                assert lib.lf_set_option(_cabi.LF_OPT_BSR_PIPE_3D, three_d) == 0
+                assert lib.lf_set_option(_cabi.LF_OPT_BSR_PIPE_3D, min(three_d, 1)) == 0
+                assert lib.lf_set_option(_cabi.LF_OPT_BSR_UMMA_PRODUCER, three_d if three_d > 1 else 0) == 0
                 C = torch.full((shape[0], N), float("nan"), device=cuda_device)
                 bsr.spmm_bsr8(a16, B16, out=C)
                 np.testing.assert_allclose(C.cpu().numpy(), want16, rtol=1e-5, atol=1e-4,
