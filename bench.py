@@ -983,16 +983,16 @@ def run_ours(args, rank, local_rank, world):
 # captured on).  The figure is reported only while kernel_source_hash() still matches.
 _NCU = "ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum -c 2 on `bench.py --workload %s --steps 2 --warmup 3 --no-cpu --no-e2e`"
 TRAFFIC_BYTES_PER_LAUNCH = {
-    ("powerlaw", "hyb", "f32", 128, 1, 1): (3124600000 + 543500000, _NCU % "powerlaw" + ", full size", "298d6cab5c915bd3"),
-    ("powerlaw", "hyb", "f32", 128, 2, 1): (3398000000 + 973500000, _NCU % "powerlaw --parts 2" + ", full size", "298d6cab5c915bd3"),
-    ("powerlaw", "hyb", "f32", 128, 4, 1): (3214500000 + 1479000000, _NCU % "powerlaw --parts 4" + ", full size", "298d6cab5c915bd3"),
-    ("powerlaw", "hyb", "f32", 128, 8, 1): (3289000000 + 2004500000, _NCU % "powerlaw --parts 8" + ", full size", "298d6cab5c915bd3"),
-    ("uniform", "hyb", "f32", 64, 1, 1): (33724000000 + 1074000000, _NCU % "uniform" + ", full size", "298d6cab5c915bd3"),
-    ("skew", "hyb", "f32", 256, 1, 1): (21398000000 + 1109000000, _NCU % "skew" + ", full size", "298d6cab5c915bd3"),
-    ("blocks", "bsr8", "f32", 128, 1, 1): (2 * 1438900000, "ncu section capture on `bench.py --workload blocks --rows 1048576`: DRAM "
-                                           "throughput x duration at 2^20 rows, doubled (traffic is proportional to the rows at a fixed band)", "30d5a8c797082986"),
-    ("blocks", "bsr8", "bf16", 128, 1, 1): (2 * 990800000, "ncu section capture on `bench.py --workload blocks --dtype bf16 --rows 1048576`: DRAM "
-                                            "throughput x duration at 2^20 rows, doubled (traffic is proportional to the rows at a fixed band)", "30d5a8c797082986"),
+    ("powerlaw", "hyb", "f32", 128, 1, 1): (3124457472 + 543653248, _NCU % "powerlaw" + ", full size", "1fc5331b3d83c58c"),
+    ("powerlaw", "hyb", "f32", 128, 2, 1): (3398000000 + 973500000, _NCU % "powerlaw --parts 2" + ", full size", "1fc5331b3d83c58c"),
+    ("powerlaw", "hyb", "f32", 128, 4, 1): (3214500000 + 1479000000, _NCU % "powerlaw --parts 4" + ", full size", "1fc5331b3d83c58c"),
+    ("powerlaw", "hyb", "f32", 128, 8, 1): (3289000000 + 2004500000, _NCU % "powerlaw --parts 8" + ", full size", "1fc5331b3d83c58c"),
+    ("uniform", "hyb", "f32", 64, 1, 1): (33723961600 + 1074016000, _NCU % "uniform" + ", full size", "1fc5331b3d83c58c"),
+    ("skew", "hyb", "f32", 256, 1, 1): (21397954944 + 1109411456, _NCU % "skew" + ", full size", "1fc5331b3d83c58c"),
+    ("blocks", "bsr8", "f32", 128, 1, 1): (2 * 1433762688, "ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum -c 2 on `bench.py --workload blocks --rows 1048576 --steps 2 --warmup 3 --no-cpu --no-e2e --no-build-timing`: "
+                                           "captured at 2^20 rows, doubled (traffic is proportional to the rows at a fixed band)", "b233a3695787bdd6"),
+    ("blocks", "bsr8", "bf16", 128, 1, 1): (2 * 989854976, "ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum -c 2 on `bench.py --workload blocks --dtype bf16 --rows 1048576 --steps 2 --warmup 3 --no-cpu --no-e2e --no-build-timing`: "
+                                            "captured at 2^20 rows, doubled (traffic is proportional to the rows at a fixed band)", "b233a3695787bdd6"),
 }
 
 

@@ -140,3 +140,23 @@ def test_full_size_golden_digest(cuda_device, golden, name):
         rows, cols, mask = fmt.to_nested_numpy()
         assert ho.digest_hyb(widths, rows, cols, mask) == run["digest"]
         del fmt
+
+
+def test_reusable_workspace_gives_the_same_format(cuda_device):
+    """hyb.Workspace: statistics, plan and fill of several matrices out of one growing scratch buffer,
+    without the per-call allocation and the final synchronisation -- same counters, same arrays."""
+    import torch
+    wsp = hyb.Workspace(cuda_device)
+    for name, P in (("zipf_2048_s5", 1), ("skew_8192_s3", 3), ("powerlaw_8192_s1", 2), ("zipf_2048_s5", 4)):
+        csr = cases.matrix(name)
+        d = _dev(csr, cuda_device)
+        stats, hist = hyb.hyb_stats(d, P)
+        stats_w, hist_w = hyb.hyb_stats(d, P, workspace=wsp)
+        assert np.array_equal(stats, stats_w) and np.array_equal(hist, hist_w)
+        widths = ws.search_from_stats(stats, hist, 64, P)
+        a = hyb.build_hyb_device(d, widths)
+        b = hyb.build_hyb_device(d, widths, workspace=wsp)
+        torch.cuda.synchronize(cuda_device)
+        for x, y in ((a.rows, b.rows), (a.cols, b.cols), (a.vals, b.vals), (a.mask, b.mask), (a.zero_rows, b.zero_rows)):
+            assert torch.equal(x, y)
+        assert np.array_equal(a.ell_rows, b.ell_rows) and np.array_equal(a.slot_off, b.slot_off)
