@@ -333,10 +333,14 @@ class HybProblem:
         if self.world > 1:
             # several ranks: each uploads its format shard and 1/world of B's rows, an all-gather over
             # NVLink completes B on every GPU (sharding.HostShardedSpmm)
-            from liteform_ae_b200.sharding import HostShardedSpmm
-            self.hs = HostShardedSpmm(fmt, self.N, self.rank, self.world, slots=2)
-            self.B_rows = torch.from_numpy(self.B_host[self.hs.first:self.hs.last]).pin_memory()
-            self.Cp = [torch.empty((self.r1 - self.r0, self.N), dtype=torch.float32).pin_memory() for _ in range(2)]
+            from liteform_ae_b200.sharding import HostShardedSpmm, gpu_numa_node, pinned_empty
+            # every rank keeps its host buffers on the NUMA node of its own GPU where the host allows it
+            node = gpu_numa_node(self.dev.index)
+            self.hs = HostShardedSpmm(fmt, self.N, self.rank, self.world, slots=2, numa_node=node)
+            self.B_rows, placed = pinned_empty((self.hs.last - self.hs.first, self.N), torch.float32, node)
+            self.B_rows.copy_(torch.from_numpy(self.B_host[self.hs.first:self.hs.last]))
+            self.Cp = [pinned_empty((self.r1 - self.r0, self.N), torch.float32, node)[0] for _ in range(2)]
+            self.numa = {"gpu_numa_node": node, "host_buffers_bound_to_it": bool(placed)}
             self.format_bytes = self.hs.format_bytes
             return (self.hs.h2d_bytes, self.hs.d2h_bytes,
                     "sharding.HostShardedSpmm: pinned host format shard + 1/world of B in, all-gather of B over "
@@ -923,7 +927,7 @@ def run_ours(args, rank, local_rank, world):
                                            "first call, B in and C out every step; not the headline (the reference uploads "
                                            "the format on every call)",
                                    "parity_ok": all(p["ok"] for p in res_parity)},
-               "phases_one_call_ms": phases, "host_affinity": numa}
+               "phases_one_call_ms": phases, "host_affinity": dict(numa, **getattr(prob, "numa", {}))}
     except Exception as exc:  # keep the device-resident numbers, say what went wrong
         e2e = {"value": None, "unit": UNIT, "error": repr(exc)}
 

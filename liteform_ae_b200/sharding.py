@@ -110,6 +110,56 @@ class ShardedSpmm:
         return self.C_full
 
 
+def gpu_numa_node(device_index: int) -> int:
+    """NUMA node the GPU hangs off (from the PCI device's sysfs entry), or -1 when it cannot be told."""
+    try:
+        import torch
+        bus = torch.cuda.get_device_properties(device_index).pci_bus_id
+        dom = torch.cuda.get_device_properties(device_index).pci_domain_id
+        dev = torch.cuda.get_device_properties(device_index).pci_device_id
+        with open(f"/sys/bus/pci/devices/{dom:04x}:{bus:02x}:{dev:02x}.0/numa_node") as f:
+            return int(f.read().strip())
+    except Exception:
+        return -1
+
+
+def pinned_empty(shape, dtype, numa_node: int = -1):
+    """A pinned (page-locked) host tensor.  With ``numa_node >= 0`` its pages are placed on that NUMA
+    node first (anonymous mapping, ``mbind``, first touch) and then registered with the CUDA driver:
+    on a two-socket host every GPU then exchanges data with the memory of its own socket instead of
+    all GPUs sharing one socket's memory path.  Any failure on that route (no such node, policy not
+    permitted in this container) falls back to an ordinary pinned allocation.  Returns
+    ``(tensor, placed)``; nothing outlasts the process."""
+    import ctypes
+    import mmap
+    import torch
+    numel = 1
+    for d in shape:
+        numel *= int(d)
+    nbytes = max(numel * torch.empty((), dtype=dtype).element_size(), 1)
+    if numa_node >= 0:
+        try:
+            size = -(-nbytes // mmap.PAGESIZE) * mmap.PAGESIZE
+            buf = mmap.mmap(-1, size)
+            addr = ctypes.addressof(ctypes.c_char.from_buffer(buf))
+            libc = ctypes.CDLL(None, use_errno=True)
+            mask = (ctypes.c_ulong * 16)()
+            mask[numa_node // 64] = 1 << (numa_node % 64)
+            MPOL_BIND, SYS_MBIND = 2, 237          # x86-64
+            rc = libc.syscall(SYS_MBIND, ctypes.c_void_p(addr), ctypes.c_ulong(size), MPOL_BIND, mask,
+                              ctypes.c_ulong(16 * 64 + 1), 0)
+            if rc != 0:
+                raise OSError(ctypes.get_errno(), "mbind")
+            ctypes.memset(addr, 0, size)             # first touch: the pages are allocated on the node now
+            if int(torch.cuda.cudart().cudaHostRegister(addr, size, 0)) != 0:
+                raise RuntimeError("cudaHostRegister")
+            t = torch.frombuffer(buf, dtype=torch.uint8, count=nbytes).view(dtype)[:numel].view(*shape)
+            return t, True
+        except Exception:
+            pass
+    return torch.empty(tuple(int(d) for d in shape), dtype=dtype).pin_memory(), False
+
+
 def b_chunk(num_cols: int, world: int, rank: int) -> Tuple[int, int, int]:
     """Rows of B a rank uploads when B starts in host memory: ``(first, last, chunk)`` with equal
     chunks of ``ceil(K / world)`` rows (the last one may be short)."""
@@ -131,14 +181,19 @@ class HostShardedSpmm:
     ranks must enqueue the same sequence of slots.
     """
 
-    def __init__(self, fmt, N: int, rank: int, world: int, group=None, slots: int = 2):
+    def __init__(self, fmt, N: int, rank: int, world: int, group=None, slots: int = 2, numa_node: int = -1):
         import copy
         import torch
         self.torch, self.rank, self.world, self.group, self.N = torch, rank, world, group, int(N)
         dev = fmt.device
         self.K = fmt.shape[1]
         self.first, self.last, self.chunk = b_chunk(self.K, world, rank)
-        pin = lambda t: t.cpu().pin_memory()
+
+        def pin(t):   # host copy of a format array, on the GPU's NUMA node when one is given
+            h, _ = pinned_empty(t.shape, t.dtype, numa_node)
+            h.copy_(t)
+            return h
+
         names = ("rows", "cols", "vals") + (("zero_rows",) if fmt.num_zero_rows else ())
         self.h_fmt = {n: pin(getattr(fmt, n)) for n in names}
         self.slots = []
