@@ -123,13 +123,18 @@ def gpu_numa_node(device_index: int) -> int:
         return -1
 
 
+_numa_buffers = []   # mappings registered with the CUDA driver stay mapped (and registered) until the process exits
+
+
 def pinned_empty(shape, dtype, numa_node: int = -1):
     """A pinned (page-locked) host tensor.  With ``numa_node >= 0`` its pages are placed on that NUMA
     node first (anonymous mapping, ``mbind``, first touch) and then registered with the CUDA driver:
     on a two-socket host every GPU then exchanges data with the memory of its own socket instead of
     all GPUs sharing one socket's memory path.  Any failure on that route (no such node, policy not
     permitted in this container) falls back to an ordinary pinned allocation.  Returns
-    ``(tensor, placed)``; nothing outlasts the process."""
+    ``(tensor, placed)``.  A placed buffer is kept mapped and registered for the life of the process
+    (an unmapped but still registered range would make a later registration at the same address
+    fail); nothing outlasts the process."""
     import ctypes
     import mmap
     import torch
@@ -153,6 +158,7 @@ def pinned_empty(shape, dtype, numa_node: int = -1):
             ctypes.memset(addr, 0, size)             # first touch: the pages are allocated on the node now
             if int(torch.cuda.cudart().cudaHostRegister(addr, size, 0)) != 0:
                 raise RuntimeError("cudaHostRegister")
+            _numa_buffers.append(buf)
             t = torch.frombuffer(buf, dtype=torch.uint8, count=nbytes).view(dtype)[:numel].view(*shape)
             return t, True
         except Exception:
