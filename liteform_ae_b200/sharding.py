@@ -157,6 +157,10 @@ def pinned_empty(shape, dtype, numa_node: int = -1):
                 raise OSError(ctypes.get_errno(), "mbind")
             ctypes.memset(addr, 0, size)             # first touch: the pages are allocated on the node now
             if int(torch.cuda.cudart().cudaHostRegister(addr, size, 0)) != 0:
+                try:      # a failed registration leaves its code as the runtime's "last error": take it out
+                    ctypes.CDLL("libcudart.so.12").cudaGetLastError()
+                except OSError:
+                    pass
                 raise RuntimeError("cudaHostRegister")
             _numa_buffers.append(buf)
             t = torch.frombuffer(buf, dtype=torch.uint8, count=nbytes).view(dtype)[:numel].view(*shape)
