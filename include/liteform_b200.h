@@ -82,6 +82,9 @@ const char* lf_last_error(void);
                                           a block, 0 one 2-D tiled copy per 128-byte feature slice */
 #define LF_OPT_BSR_UMMA_PRODUCER 9      /* copy engine 5: who fills shared memory: 0 (default) one warp issuing tiled bulk
                                           copies, 2 or 4 = that many warps issuing per-lane cp.async */
+#define LF_OPT_SPMM_GATHER_RING 10      /* float32 product with 128-bit gathers and more than 64 features: where the
+                                          gathered rows of B land: 16 (default) a ring of 16 rows per warp in shared
+                                          memory, filled by cp.async; 0 registers (8 rows in flight per warp) */
 #define LF_OPT_SPMM_TILE_SEGMENTS 6     /* order of the thread blocks of the composed-format product: 0 bucket after
                                           bucket (default); S > 0: every bucket is cut into S segments of consecutive
                                           rows and the launch runs segment 0 of all buckets, then segment 1, ... */

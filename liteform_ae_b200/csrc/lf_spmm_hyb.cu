@@ -22,8 +22,13 @@
 //   * padded slots issue no gather.  Padding is recognised by its stored value 0 (the builder writes
 //     exact zeros there); a stored ENTRY whose value is exactly 0 is skipped the same way, so
 //     0 * Inf and 0 * NaN from B do not reach C (SciPy would produce NaN there);
+//   * float32 B with more than 64 features per row runs, by default, a second form of the same walk
+//     whose gathers land in a per-lane shared-memory ring (cp.async, 16 rows ahead) instead of
+//     registers: see spmm_hyb_ring_kernel;
 //   * variants of the same code: B in bf16 (8 features per lane), and a broadcasting epilogue that
 //     stores every row into several full-size C matrices (the GPUs of a group) at once.
+#include <type_traits>
+
 #include "lf_bsr8_tma.cuh"
 #include "lf_common.cuh"
 
@@ -295,6 +300,218 @@ spmm_hyb_kernel(const __grid_constant__ SpmmTable<MAXB> tbl, const int32_t* __re
 #undef LF_WALK
 }
 
+// ---- gathers staged through a per-lane ring in shared memory --------------------------------
+// The register kernel above keeps at most 8 gathered rows of B per warp in flight (32 registers per
+// lane), 192 per SM at three thread blocks, and its warps spend their time waiting for them (on
+// the power-law benchmark matrix: 11 stall cycles on the long scoreboard per issued instruction,
+// time down by a quarter from two to three resident blocks).  This variant moves the landing zone
+// of the gathers from registers to shared memory: every lane owns D slots of 16 bytes, fills
+// them with cp.async up to D rows ahead of the row it is adding up, and reads back only bytes it
+// copied itself, so no lane ever waits for another one.  D = 16 at three thread blocks doubles
+// the rows in flight per SM; the wait for B disappears from the stall profile and the kernel
+// runs into the DRAM instead (91 % of the copy bandwidth on that matrix).  What it pays is a
+// second pass of every gathered byte through the load/store unit, so the inner loop is written
+// to issue as few shared-memory instructions as possible: (column, value) pairs are read two at a
+// time, the values stay in registers between the copy and the multiply, and ring slots are
+// compile-time constants.  A warp covers 128 features (one chunk of four per lane); wider feature
+// matrices use further thread blocks along y.  Rows are added up in the same order as in the
+// register kernel.
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int PENDING>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(PENDING) : "memory"); }
+
+// address of element `offset` of a float array: one 32 x 32 + 64 bit multiply-add
+__device__ __forceinline__ const void* row_of_b(const float* base, uint32_t offset) {
+  uint64_t a;
+  asm("mad.wide.u32 %0, %1, 4, %2;" : "=l"(a) : "r"(offset), "l"(reinterpret_cast<uint64_t>(base)));
+  return reinterpret_cast<const void*>(a);
+}
+
+constexpr int kRingFeatures = 128;   // features one warp of the ring kernel covers
+
+constexpr uint32_t kNoGather = 0xffffffffu;   // offset of a slot that gathers nothing (padding, stored zero)
+
+// Everything that is the same for all lanes of a warp is computed once per slot by ONE lane while
+// a strip of 32 slots is staged (offset of the row of B in elements, "gathers nothing" folded into
+// the offset, "an ELL row with another row id starts here" as one bit of a warp vote), so that the
+// loop over the slots, which every lane executes for every slot, is left with one address
+// computation, one copy, one shared-memory load and the multiply-adds.
+template <int D, int WC, int POL>
+__device__ __forceinline__ void walk_slots_ring(const int32_t* __restrict__ rows, const int32_t* __restrict__ cols,
+                                                const float* __restrict__ vals, int wlog, int64_t e0, int64_t e1,
+                                                int64_t ell_rows, bool all_open, const float* __restrict__ B, int ldb,
+                                                float* __restrict__ C, int64_t ldc, int N, int64_t row_base, int lane,
+                                                uint32_t* so, float* sv, int* rd, float4* ring) {
+  constexpr int U = 8;   // rows per commit group; row ids can change every WC <= 8 slots
+  static_assert(D % U == 0 && D >= 2 * U && D <= 32, "ring depth: 16, 24 or 32 rows (two to four groups)");
+  const int first_row = rows[e0], last_row = rows[e1 - 1];
+  const bool head_open = e0 > 0 && rows[e0 - 1] == first_row;
+  const bool tail_open = e1 < ell_rows && rows[e1] == last_row;
+  const int f0 = blockIdx.y * kRingFeatures + lane * 4;
+  const bool active = f0 < N;
+  Chunk<4> acc;
+  acc.zero();
+  int cur = first_row;
+
+  auto flush = [&](int row) {
+    const bool open = all_open || (row == first_row && head_open) || (row == last_row && tail_open);
+    float* dst = C + (int64_t)(row - row_base) * ldc + f0;
+    if (active) {
+      if (open) acc.red(dst);
+      else if (POL >= 1) acc.store_stream(dst);
+      else acc.store(dst);
+    }
+    acc.zero();
+  };
+
+  const float* __restrict__ Bf = B + f0;
+  const int64_t s0 = e0 << wlog, s1 = e1 << wlog;
+  const int n = (int)(s1 - s0);            // a group walks a few hundred slots (one ELL row at the most if wider)
+  const int nstrips = (n + 31) >> 5;
+  // Offsets, values and row ids of two strips of 32 slots live in shared memory; the strip after
+  // those is already on its way in registers.
+  int pc = 0, pr = 0;
+  float pv = 0.f;
+  auto load_strip = [&](int k) {
+    const int64_t idx = s0 + (int64_t)k * 32 + lane;
+    const bool in = idx < s1;
+    const int64_t cidx = in ? idx : s1 - 1;
+    pc = POL >= 1 ? __ldcs(cols + cidx) : cols[cidx];
+    pv = in ? (POL >= 1 ? __ldcs(vals + cidx) : vals[cidx]) : 0.f;
+    pr = rows[cidx >> wlog];
+  };
+  uint32_t chg0 = 0, chg1 = 0;   // bit i: slot i of the even / odd strip carries another row id than the slot before
+  int carry = first_row;         // row id of the last slot of the strip staged before
+  auto store_strip = [&](int k) {
+    const int h = (k & 1) * 32 + lane;
+    so[h] = pv != 0.f ? (uint32_t)pc * (uint32_t)ldb : kNoGather;
+    sv[h] = pv;
+    rd[h] = pr;
+    int before = __shfl_up_sync(0xffffffffu, pr, 1);
+    if (lane == 0) before = carry;
+    const uint32_t m = __ballot_sync(0xffffffffu, pr != before);
+    carry = __shfl_sync(0xffffffffu, pr, 31);
+    if (k & 1) chg1 = m; else chg0 = m;
+  };
+  load_strip(0);
+  store_strip(0);
+  __syncwarp();
+  if (nstrips > 1) load_strip(1);
+
+  const float4* ring_lane = ring + lane;
+  const uint32_t ring_s = (uint32_t)__cvta_generic_to_shared(ring_lane);
+  const uint4* so4 = reinterpret_cast<const uint4*>(so);
+  const float4* sv4 = reinterpret_cast<const float4*>(sv);
+  // start the copies of rows j0 .. j0+7 (j0 a multiple of 8) into ring slots SLOT .. SLOT+7 and close
+  // them as one group; past the end of the range the group is empty, which keeps the number of
+  // groups per iteration constant
+  auto issue_batch = [&](int j0, auto slot_tag) {
+    constexpr int SLOT = decltype(slot_tag)::value;
+    if (j0 < nstrips * 32) {
+      if ((j0 & 31) == 0 && j0 > 0) {   // first rows of strip k: its slots move from registers to shared memory
+        const int k = j0 >> 5;          // (the half they overwrite held strip k-2, consumed D <= 32 rows ago)
+        __syncwarp();
+        store_strip(k);
+        __syncwarp();
+        if (k + 1 < nstrips) load_strip(k + 1);
+      }
+      const uint4 oa = so4[(j0 & 63) >> 2], ob = so4[((j0 & 63) >> 2) + 1];
+      const uint32_t o[U] = {oa.x, oa.y, oa.z, oa.w, ob.x, ob.y, ob.z, ob.w};
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if (o[u] != kNoGather && active) cp_async_16(ring_s + (uint32_t)(SLOT + u) * 512u, row_of_b(Bf, o[u]));
+    }
+    cp_async_commit();
+  };
+
+  // compile-time loop over the D/U batches of the ring
+  auto for_each_batch = [&](auto&& body) {
+    body(std::integral_constant<int, 0>{});
+    body(std::integral_constant<int, U>{});
+    if constexpr (D > 2 * U) body(std::integral_constant<int, 2 * U>{});
+    if constexpr (D > 3 * U) body(std::integral_constant<int, 3 * U>{});
+  };
+
+  for_each_batch([&](auto slot_tag) { issue_batch(decltype(slot_tag)::value, slot_tag); });
+  wait_for_prior_grid();   // no store or atomic to C before the row-clearing launch is complete
+  for (int jc0 = 0; jc0 < n; jc0 += D) {
+    for_each_batch([&](auto slot_tag) {
+      constexpr int SLOT = decltype(slot_tag)::value;
+      const int jc = jc0 + SLOT;
+      if (jc >= n) return;
+      const float4 va = sv4[(jc & 63) >> 2], vb = sv4[((jc & 63) >> 2) + 1];
+      const float val[U] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
+      const uint32_t starts = (((jc >> 5) & 1) ? chg1 : chg0) >> (jc & 31);   // bit u: slot jc+u starts another row
+      cp_async_wait<D / U - 1>();   // all but the newest D/U - 1 groups have landed: rows jc .. jc+7 are here
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (u % WC == 0 && ((starts >> u) & 1u)) {  // an ELL row can only start at a multiple of WC
+          flush(cur);
+          cur = rd[(jc + u) & 63];
+        }
+        if (val[u] != 0.f && active) {
+          Chunk<4> x;
+          x.v = ring_lane[(SLOT + u) * 32];
+          acc.fma(val[u], x);
+        }
+      }
+      issue_batch(jc + D, slot_tag);   // refills exactly the ring slots read above
+    });
+  }
+  flush(cur);
+}
+
+template <int D, int MAXB, int POL, int MINB>
+__global__ void __launch_bounds__(kThreads, MINB)
+spmm_hyb_ring_kernel(const __grid_constant__ SpmmTable<MAXB> tbl, const int32_t* __restrict__ rows_arena,
+                     const int32_t* __restrict__ cols_arena, const float* __restrict__ vals_arena,
+                     const float* __restrict__ B, int ldb, float* __restrict__ C, int64_t ldc, int N,
+                     int64_t row_base) {
+  constexpr int GPC = kThreads / 32;
+  extern __shared__ __align__(16) unsigned char ring_bytes[];
+  __shared__ __align__(16) uint32_t s_off[GPC * 64];
+  __shared__ __align__(16) float s_val[GPC * 64];
+  __shared__ int s_rd[GPC * 64];
+
+  int64_t tile = blockIdx.x;
+  int64_t key = tile;
+  uint32_t seg = 0;
+  if (tbl.seg_tiles > 0) {
+    seg = (uint32_t)blockIdx.x / (uint32_t)tbl.seg_tiles;
+    key = (uint32_t)blockIdx.x - seg * (uint32_t)tbl.seg_tiles;
+  }
+  int lo = 0, hi = tbl.n;
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (tbl.b[mid].tile_begin <= key) lo = mid; else hi = mid;
+  }
+  const BucketDesc& d = tbl.b[lo];
+  tile = tbl.seg_tiles > 0 ? (int64_t)seg * d.tiles_per_seg + (key - d.tile_begin) : key - d.tile_begin;
+  const int wlog = d.wlog;
+  const int g = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t e0 = (tile * GPC + g) * (int64_t)d.rows_per_group;
+  if (e0 >= d.ell_rows) return;
+  const int64_t e1 = min(e0 + d.rows_per_group, d.ell_rows);
+  const int32_t* __restrict__ rows = rows_arena + d.row_off;
+  const int32_t* __restrict__ cols = cols_arena + d.slot_off;
+  const float* __restrict__ vals = vals_arena + d.slot_off;
+  const bool all_open = d.force_atomic != 0;
+  float4* ring = reinterpret_cast<float4*>(ring_bytes) + (size_t)g * D * 32;
+#define LF_WALK(WC_)                                                                                       \
+  walk_slots_ring<D, WC_, POL>(rows, cols, vals, wlog, e0, e1, d.ell_rows, all_open, B, ldb, C, ldc, N,   \
+                               row_base, lane, s_off + g * 64, s_val + g * 64, s_rd + g * 64, ring)
+  switch (wlog) {
+    case 0: LF_WALK(1); break;
+    case 1: LF_WALK(2); break;
+    case 2: LF_WALK(4); break;
+    default: LF_WALK(8); break;
+  }
+#undef LF_WALK
+}
+
 // Rows that no single ELL row owns are cleared before the accumulating launch.
 template <int VEC>
 __global__ void __launch_bounds__(kThreads)
@@ -517,11 +734,12 @@ struct FeatCfg { int G, V, VEC, pass; };
 // (the row-clearing launch): the product kernel may start before that kernel has finished and
 // orders itself with griddepcontrol.wait.
 template <typename... Params, typename... Args>
-cudaError_t launch_dep(void (*kernel)(Params...), dim3 grid, int threads, cudaStream_t st, bool dependent, Args... args) {
+cudaError_t launch_dep_smem(void (*kernel)(Params...), dim3 grid, int threads, size_t smem, cudaStream_t st,
+                            bool dependent, Args... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = dim3((unsigned)threads);
-  cfg.dynamicSmemBytes = 0;
+  cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -529,6 +747,10 @@ cudaError_t launch_dep(void (*kernel)(Params...), dim3 grid, int threads, cudaSt
   cfg.attrs = attr;
   cfg.numAttrs = dependent ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<Params>(args)...);
+}
+template <typename... Params, typename... Args>
+cudaError_t launch_dep(void (*kernel)(Params...), dim3 grid, int threads, cudaStream_t st, bool dependent, Args... args) {
+  return launch_dep_smem(kernel, grid, threads, 0, st, dependent, args...);
 }
 
 FeatCfg pick_cfg(const void* B, int64_t ldb, const void* C, int64_t ldc, int N) {
@@ -564,6 +786,7 @@ FeatCfg pick_cfg_bf16(int N) {
 }
 
 // Process-wide tuning knobs (lf_set_option); the environment gives the initial values.
+constexpr int kDefaultGatherRing = 16;
 int g_slots_per_group = 0;
 int g_cache_policy = -1;
 
@@ -610,6 +833,17 @@ int min_blocks() {
     g_min_blocks = (v >= 2 && v <= 4) ? v : 3;
   }
   return g_min_blocks;
+}
+
+// Depth of the shared-memory gather ring (rows in flight per warp): 0 = gathers land in registers.
+int g_gather_ring = -1;
+int gather_ring() {
+  if (g_gather_ring < 0) {
+    const char* e = getenv("LF_SPMM_GATHER_RING");
+    const int v = e ? atoi(e) : kDefaultGatherRing;
+    g_gather_ring = (v == 0 || v == 16) ? v : kDefaultGatherRing;
+  }
+  return g_gather_ring;
 }
 
 int cache_policy() {
@@ -668,6 +902,23 @@ int launch_hyb(const SpmmTable<MAXB>& tbl, int64_t tiles, const lf_hyb* A, const
   if (dests.n > 0)   // broadcasting launch: one compiled variant
     return launch_hyb_pol<MAXB, 1, 3, true>(tbl, tiles, A, B, ldb, C, ldc, N, cfg, st, dests, dep);
   const int pol = cache_policy(), minb = min_blocks();
+  const int ring = gather_ring();
+  // the ring kernel addresses a row of B by a 32-bit element offset (column * ldb)
+  if (ring > 0 && cfg.VEC == 4 && cfg.G == 32 && (int64_t)A->num_cols * ldb < (int64_t)kNoGather) {
+    // one warp per 128 features; the ring of a thread block takes depth * 4 KiB of shared memory
+    dim3 grid((unsigned)tiles, (unsigned)((N + kRingFeatures - 1) / kRingFeatures));
+    const size_t smem = (size_t)(kThreads / 32) * ring * 32 * sizeof(float4);
+#define LF_RING(D_, P_, M_)                                                                                     \
+  do {                                                                                                          \
+    auto kern = spmm_hyb_ring_kernel<D_, MAXB, P_, M_>;                                                         \
+    LF_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));          \
+    LF_CUDA_CHECK(launch_dep_smem(kern, grid, kThreads, smem, st, dep, tbl, A->rows, A->cols, A->vals, B,       \
+                                  (int)ldb, C, ldc, N, A->row_begin));                                          \
+    return LF_OK;                                                                                               \
+  } while (0)
+    if (pol == 0) LF_RING(16, 0, 3); else LF_RING(16, 1, 3);
+#undef LF_RING
+  }
 #define LF_CASE(P_, M_) if (pol == P_ && minb == M_) return launch_hyb_pol<MAXB, P_, M_, false>(tbl, tiles, A, B, ldb, C, ldc, N, cfg, st, dests, dep)
   LF_CASE(0, 2); LF_CASE(0, 3); LF_CASE(0, 4);
   LF_CASE(1, 2); LF_CASE(1, 3); LF_CASE(1, 4);
@@ -710,6 +961,10 @@ int lf_set_option(int32_t option, int32_t value) {
     case LF_OPT_SPMM_MIN_BLOCKS:
       LF_REQUIRE(value >= 2 && value <= 4, "min blocks %d out of range", value);
       g_min_blocks = value;
+      return LF_OK;
+    case LF_OPT_SPMM_GATHER_RING:
+      LF_REQUIRE(value == 0 || value == 16, "gather ring depth %d is not 0 or 16", value);
+      g_gather_ring = value;
       return LF_OK;
     case LF_OPT_SPMM_TILE_SEGMENTS:
       LF_REQUIRE(value >= 0 && value <= 4096, "segment count %d out of range", value);

@@ -9,6 +9,8 @@ from liteform_ae_b200 import _cabi, bsr, hyb, synth
 
 pytestmark = pytest.mark.gpu
 
+DEFAULT_GATHER_RING = 16  # the library's initial value of LF_OPT_SPMM_GATHER_RING
+
 
 @pytest.fixture
 def restore_defaults():
@@ -24,6 +26,7 @@ def restore_defaults():
     lib.lf_set_option(_cabi.LF_OPT_BSR_PIPE_SHAPE, 0)
     lib.lf_set_option(_cabi.LF_OPT_BSR_PIPE_3D, 1)
     lib.lf_set_option(_cabi.LF_OPT_BSR_UMMA_PRODUCER, 0)
+    lib.lf_set_option(_cabi.LF_OPT_SPMM_GATHER_RING, DEFAULT_GATHER_RING)
 
 
 def test_every_spmm_variant_gives_the_same_product(cuda_device, restore_defaults):
@@ -37,6 +40,8 @@ def test_every_spmm_variant_gives_the_same_product(cuda_device, restore_defaults
         Bd = torch.from_numpy(B).to(cuda_device)
         want = ho.spmm_scipy_csr(csr.indptr, csr.indices, csr.data.astype(np.float64), csr.shape, B.astype(np.float64))
         for pol, minb, slots, segs in itertools.product((0, 1), (2, 3, 4), (0, 8, 64, 4096), (0, 1, 7, 64)):
+            # the occupancy knob belongs to the register kernel; the ring kernel takes the other three
+            assert lib.lf_set_option(_cabi.LF_OPT_SPMM_GATHER_RING, 0 if minb != 3 else 16) == 0
             assert lib.lf_set_option(_cabi.LF_OPT_SPMM_CACHE_POLICY, pol) == 0
             assert lib.lf_set_option(_cabi.LF_OPT_SPMM_MIN_BLOCKS, minb) == 0
             assert lib.lf_set_option(_cabi.LF_OPT_SPMM_SLOTS_PER_GROUP, slots) == 0
@@ -46,6 +51,38 @@ def test_every_spmm_variant_gives_the_same_product(cuda_device, restore_defaults
     assert lib.lf_set_option(_cabi.LF_OPT_SPMM_CACHE_POLICY, 2) == _cabi.LF_ERR_INVALID_ARGUMENT
     assert lib.lf_set_option(_cabi.LF_OPT_SPMM_MIN_BLOCKS, 7) == _cabi.LF_ERR_INVALID_ARGUMENT
     assert lib.lf_set_option(99, 1) == _cabi.LF_ERR_INVALID_ARGUMENT
+
+
+@pytest.mark.parametrize("parts", [1, 3])
+def test_gather_ring_adds_up_in_the_same_order_as_the_register_kernel(cuda_device, restore_defaults, parts):
+    """Gathers that land in a shared-memory ring (cp.async, 16 rows ahead) instead of registers:
+    the slots of a thread group are added in the same order, so rows that one group owns are
+    bit-identical; rows reduced by atomics over several groups agree to rounding."""
+    import torch
+    lib = _cabi.load()
+    csr = synth.skewed_rows(M=6000, seed=8, heavy_rows=5, heavy_len=2500)
+    d = hyb.DeviceCsr.from_host(csr.indptr, csr.indices, csr.data, csr.shape, cuda_device)
+    widths = [[1, 2, 4, 8, 16, 64]] if parts == 1 else [[1, 4, 32], [2, 8], [1, 2, 4, 8, 16]]
+    fmt = hyb.build_hyb_device(d, widths, with_mask=False)
+    for N in (100, 128, 256, 320, 512):
+        B = synth.dense_features(csr.shape[1], N, 3)
+        Bd = torch.from_numpy(B).to(cuda_device)
+        want = ho.spmm_scipy_csr(csr.indptr, csr.indices, csr.data.astype(np.float64), csr.shape, B.astype(np.float64))
+        for slots, pol in itertools.product((0, 8, 40, 4096), (0, 1)):
+            assert lib.lf_set_option(_cabi.LF_OPT_SPMM_SLOTS_PER_GROUP, slots) == 0
+            assert lib.lf_set_option(_cabi.LF_OPT_SPMM_CACHE_POLICY, pol) == 0
+            assert lib.lf_set_option(_cabi.LF_OPT_SPMM_GATHER_RING, 0) == 0
+            base = hyb.spmm_hyb(fmt, Bd)
+            for depth in (16,):
+                assert lib.lf_set_option(_cabi.LF_OPT_SPMM_GATHER_RING, depth) == 0
+                C = torch.full((csr.shape[0], N), float("nan"), device=cuda_device)
+                hyb.spmm_hyb(fmt, Bd, out=C)
+                got = C.cpu().numpy()
+                np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-4, err_msg=f"{N} {slots} {pol} {depth}")
+                if parts == 1:
+                    short = np.diff(csr.indptr) <= 64     # one ELL row, one group, no atomics
+                    assert np.array_equal(got[short], base.cpu().numpy()[short])
+    assert lib.lf_set_option(_cabi.LF_OPT_SPMM_GATHER_RING, 8) == _cabi.LF_ERR_INVALID_ARGUMENT
 
 
 def test_every_block_kernel_variant_gives_the_same_product(cuda_device, restore_defaults):
