@@ -228,6 +228,11 @@ int lf_spmm_hyb_f32(const lf_hyb* A, const float* B /*[dev] K x N*/, int64_t ldb
                     float* C /*[dev] (row_end-row_begin) x N*/, int64_t ldc, int32_t N,
                     int32_t flags, void* stream);
 
+/* Name of the kernel lf_spmm_hyb_f32 launches for these operands under the current options
+ * ("spmm_hyb_ring_kernel" or "spmm_hyb_kernel"); launches nothing.  For logs and benchmarks. */
+const char* lf_spmm_hyb_f32_kernel_name(const lf_hyb* A, const float* B, int64_t ldb, const float* C, int64_t ldc,
+                                        int32_t N);
+
 /* The same product with B in bf16 (raw 16-bit patterns), values and accumulation in float32, C in
  * float32: halves the bytes of every gather.  N and ldb multiples of 8, ldc of 4, B and C 16-byte
  * aligned (LF_ERR_UNSUPPORTED otherwise).  Matches the float64 product of the rounded B to 1e-5 and

@@ -78,6 +78,7 @@ SIGNATURES = {
     "lf_hyb_plan": (C.c_int, [vp, vp, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int32, vp, vp,
                               vp, vp, vp, vp, vp, C.c_size_t, vp]),
     "lf_hyb_fill": (C.c_int, [vp, vp, vp, C.POINTER(LfHyb), vp, C.c_size_t, vp, C.c_size_t, vp]),
+    "lf_spmm_hyb_f32_kernel_name": (C.c_char_p, [C.POINTER(LfHyb), vp, C.c_int64, vp, C.c_int64, C.c_int32]),
     "lf_spmm_hyb_f32": (C.c_int, [C.POINTER(LfHyb), vp, C.c_int64, vp, C.c_int64, C.c_int32, C.c_int32, vp]),
     "lf_spmm_hyb_bf16": (C.c_int, [C.POINTER(LfHyb), vp, C.c_int64, vp, C.c_int64, C.c_int32, C.c_int32, vp]),
     "lf_spmm_hyb_f32_bcast": (C.c_int, [C.POINTER(LfHyb), vp, C.c_int64, vp, C.c_int32, C.c_int64, C.c_int32, vp]),

@@ -339,12 +339,12 @@ constexpr uint32_t kNoGather = 0xffffffffu;   // offset of a slot that gathers n
 // the offset, "an ELL row with another row id starts here" as one bit of a warp vote), so that the
 // loop over the slots, which every lane executes for every slot, is left with one address
 // computation, one copy, one shared-memory load and the multiply-adds.
-template <int D, int WC, int POL>
+template <int D, int WC, int POL, bool MD>
 __device__ __forceinline__ void walk_slots_ring(const int32_t* __restrict__ rows, const int32_t* __restrict__ cols,
                                                 const float* __restrict__ vals, int wlog, int64_t e0, int64_t e1,
                                                 int64_t ell_rows, bool all_open, const float* __restrict__ B, int ldb,
                                                 float* __restrict__ C, int64_t ldc, int N, int64_t row_base, int lane,
-                                                uint32_t* so, float* sv, int* rd, float4* ring) {
+                                                uint32_t* so, float* sv, int* rd, float4* ring, const DestList& dl) {
   constexpr int U = 8;   // rows per commit group; row ids can change every WC <= 8 slots
   static_assert(D % U == 0 && D >= 2 * U && D <= 32, "ring depth: 16, 24 or 32 rows (two to four groups)");
   const int first_row = rows[e0], last_row = rows[e1 - 1];
@@ -358,8 +358,15 @@ __device__ __forceinline__ void walk_slots_ring(const int32_t* __restrict__ rows
 
   auto flush = [&](int row) {
     const bool open = all_open || (row == first_row && head_open) || (row == last_row && tail_open);
-    float* dst = C + (int64_t)(row - row_base) * ldc + f0;
-    if (active) {
+    const int64_t off = (int64_t)(row - row_base) * ldc + f0;
+    if (MD) {   // the same row goes to every destination (peer stores / peer atomics over NVLink)
+      if (active) {
+        for (int k = 0; k < dl.n; ++k) {
+          if (open) acc.red(dl.p[k] + off); else acc.store(dl.p[k] + off);
+        }
+      }
+    } else if (active) {
+      float* dst = C + off;
       if (open) acc.red(dst);
       else if (POL >= 1) acc.store_stream(dst);
       else acc.store(dst);
@@ -464,12 +471,12 @@ __device__ __forceinline__ void walk_slots_ring(const int32_t* __restrict__ rows
   flush(cur);
 }
 
-template <int D, int MAXB, int POL, int MINB>
+template <int D, int MAXB, int POL, int MINB, bool MD>
 __global__ void __launch_bounds__(kThreads, MINB)
 spmm_hyb_ring_kernel(const __grid_constant__ SpmmTable<MAXB> tbl, const int32_t* __restrict__ rows_arena,
                      const int32_t* __restrict__ cols_arena, const float* __restrict__ vals_arena,
                      const float* __restrict__ B, int ldb, float* __restrict__ C, int64_t ldc, int N,
-                     int64_t row_base) {
+                     int64_t row_base, const __grid_constant__ DestList dests) {
   constexpr int GPC = kThreads / 32;
   extern __shared__ __align__(16) unsigned char ring_bytes[];
   __shared__ __align__(16) uint32_t s_off[GPC * 64];
@@ -501,8 +508,8 @@ spmm_hyb_ring_kernel(const __grid_constant__ SpmmTable<MAXB> tbl, const int32_t*
   const bool all_open = d.force_atomic != 0;
   float4* ring = reinterpret_cast<float4*>(ring_bytes) + (size_t)g * D * 32;
 #define LF_WALK(WC_)                                                                                       \
-  walk_slots_ring<D, WC_, POL>(rows, cols, vals, wlog, e0, e1, d.ell_rows, all_open, B, ldb, C, ldc, N,   \
-                               row_base, lane, s_off + g * 64, s_val + g * 64, s_rd + g * 64, ring)
+  walk_slots_ring<D, WC_, POL, MD>(rows, cols, vals, wlog, e0, e1, d.ell_rows, all_open, B, ldb, C, ldc, N, \
+                                   row_base, lane, s_off + g * 64, s_val + g * 64, s_rd + g * 64, ring, dests)
   switch (wlog) {
     case 0: LF_WALK(1); break;
     case 1: LF_WALK(2); break;
@@ -893,32 +900,39 @@ int launch_hyb_pol(const SpmmTable<MAXB>& tbl, int64_t tiles, const lf_hyb* A, c
   return LF_OK;
 }
 
+// The ring kernel exists for 128-bit gathers over full warps and addresses a row of B by a 32-bit
+// element offset (column * ldb).
+bool ring_applies(const lf_hyb* A, const FeatCfg& cfg, int64_t ldb) {
+  return cfg.VEC == 4 && cfg.G == 32 && (int64_t)A->num_cols * ldb < (int64_t)kNoGather;
+}
+
 template <int MAXB>
 int launch_hyb(const SpmmTable<MAXB>& tbl, int64_t tiles, const lf_hyb* A, const void* Bv, int64_t ldb,
                float* C, int64_t ldc, int N, FeatCfg cfg, cudaStream_t st, const DestList& dests, bool dep) {
   if (cfg.VEC == 8)   // bf16 B: one compiled variant per feature layout
     return launch_hyb_bf16<MAXB>(tbl, tiles, A, (const uint16_t*)Bv, ldb, C, ldc, N, cfg, st, dests, dep);
   const float* B = (const float*)Bv;
-  if (dests.n > 0)   // broadcasting launch: one compiled variant
-    return launch_hyb_pol<MAXB, 1, 3, true>(tbl, tiles, A, B, ldb, C, ldc, N, cfg, st, dests, dep);
   const int pol = cache_policy(), minb = min_blocks();
   const int ring = gather_ring();
-  // the ring kernel addresses a row of B by a 32-bit element offset (column * ldb)
-  if (ring > 0 && cfg.VEC == 4 && cfg.G == 32 && (int64_t)A->num_cols * ldb < (int64_t)kNoGather) {
+  if (ring > 0 && ring_applies(A, cfg, ldb)) {
     // one warp per 128 features; the ring of a thread block takes depth * 4 KiB of shared memory
     dim3 grid((unsigned)tiles, (unsigned)((N + kRingFeatures - 1) / kRingFeatures));
     const size_t smem = (size_t)(kThreads / 32) * ring * 32 * sizeof(float4);
-#define LF_RING(D_, P_, M_)                                                                                     \
+#define LF_RING(D_, P_, M_, MD_)                                                                                \
   do {                                                                                                          \
-    auto kern = spmm_hyb_ring_kernel<D_, MAXB, P_, M_>;                                                         \
+    auto kern = spmm_hyb_ring_kernel<D_, MAXB, P_, M_, MD_>;                                                    \
     LF_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));          \
     LF_CUDA_CHECK(launch_dep_smem(kern, grid, kThreads, smem, st, dep, tbl, A->rows, A->cols, A->vals, B,       \
-                                  (int)ldb, C, ldc, N, A->row_begin));                                          \
+                                  (int)ldb, C, ldc, N, MD_ ? (int64_t)0 : A->row_begin, dests));                \
     return LF_OK;                                                                                               \
   } while (0)
-    if (pol == 0) LF_RING(16, 0, 3); else LF_RING(16, 1, 3);
+    if (dests.n > 0) LF_RING(16, 1, 3, true);   // broadcasting launch: one compiled variant
+    else if (pol == 0) LF_RING(16, 0, 3, false);
+    else LF_RING(16, 1, 3, false);
 #undef LF_RING
   }
+  if (dests.n > 0)   // broadcasting launch: one compiled variant
+    return launch_hyb_pol<MAXB, 1, 3, true>(tbl, tiles, A, B, ldb, C, ldc, N, cfg, st, dests, dep);
 #define LF_CASE(P_, M_) if (pol == P_ && minb == M_) return launch_hyb_pol<MAXB, P_, M_, false>(tbl, tiles, A, B, ldb, C, ldc, N, cfg, st, dests, dep)
   LF_CASE(0, 2); LF_CASE(0, 3); LF_CASE(0, 4);
   LF_CASE(1, 2); LF_CASE(1, 3); LF_CASE(1, 4);
@@ -1004,6 +1018,13 @@ int lf_spmm_hyb_f32(const lf_hyb* A, const float* B, int64_t ldb, float* C, int6
   none.n = 0;
   none.pad_ = 0;
   return spmm_hyb_impl(A, B, false, ldb, C, ldc, N, flags, stream, none);
+}
+
+const char* lf_spmm_hyb_f32_kernel_name(const lf_hyb* A, const float* B, int64_t ldb, const float* C, int64_t ldc,
+                                        int32_t N) {
+  if (!A || N < 1) return "";
+  const FeatCfg cfg = pick_cfg(B, ldb, C, ldc, N);
+  return gather_ring() > 0 && ring_applies(A, cfg, ldb) ? "spmm_hyb_ring_kernel" : "spmm_hyb_kernel";
 }
 
 int lf_spmm_hyb_bf16(const lf_hyb* A, const uint16_t* B, int64_t ldb, float* C, int64_t ldc, int32_t N,

@@ -325,6 +325,14 @@ def spmm_hyb(fmt: HybFormat, B, out=None, accumulate: bool = False):
     return out
 
 
+def spmm_hyb_kernel_name(fmt: HybFormat, B, out) -> str:
+    """``lf_spmm_hyb_f32_kernel_name``: the kernel ``spmm_hyb(fmt, B, out=out)`` launches for float32 B."""
+    s = fmt.c_struct()
+    name = _cabi.load().lf_spmm_hyb_f32_kernel_name(C.byref(s), B.data_ptr(), B.stride(0), out.data_ptr(),
+                                                    out.stride(0), int(B.shape[1]))
+    return name.decode()
+
+
 def spmm_csr(csr: DeviceCsr, B, out=None, row_range=None):
     """``lf_spmm_csr_f32`` on rows ``row_range`` (default: all)."""
     torch = _torch()

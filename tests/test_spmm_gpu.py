@@ -226,17 +226,19 @@ def test_full_size_linearity_and_checksum(cuda_device):
                                rtol=RTOL, atol=ATOL)
 
 
-def test_broadcasting_spmm_two_destinations_on_one_gpu(cuda_device):
+@pytest.mark.parametrize("N", [64, 128, 200])
+def test_broadcasting_spmm_two_destinations_on_one_gpu(cuda_device, N):
     """lf_spmm_hyb_f32_bcast with both destinations on this GPU (the peer case needs two GPUs and is
-    exercised by bench.py --gather fused): every shard writes its rows into both full-size buffers."""
+    exercised by bench.py --gather fused): every shard writes its rows into both full-size buffers.
+    64 features run the register kernel, 128 and 200 the shared-memory-ring kernel."""
     import torch
     for P, name in ((1, "skew_8192_s3"), (2, "powerlaw_8192_s1")):
-        csr, d, fmt, B, Bd = _setup(name, P, 64, cuda_device)
-        full = [torch.full((csr.shape[0], 64), float("nan"), device=cuda_device) for _ in range(2)]
+        csr, d, fmt, B, Bd = _setup(name, P, N, cuda_device)
+        full = [torch.full((csr.shape[0], N), float("nan"), device=cuda_device) for _ in range(2)]
         cuts = hyb.shard_rows(d, 3)
         for a, b in zip(cuts[:-1], cuts[1:]):
             part = hyb.build_hyb_device(d, fmt.bucket_widths, row_range=(a, b), with_mask=False)
-            hyb.spmm_hyb_bcast(part, Bd, [t.data_ptr() for t in full], 64)
+            hyb.spmm_hyb_bcast(part, Bd, [t.data_ptr() for t in full], N)
         want = _ref(csr, B)
         for t in full:
             np.testing.assert_allclose(t.cpu().numpy(), want, rtol=RTOL, atol=ATOL)
