@@ -323,20 +323,20 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int PENDING>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(PENDING) : "memory"); }
 
-// address of element `offset` of a float array: one 32 x 32 + 64 bit multiply-add
-__device__ __forceinline__ const void* row_of_b(const float* base, uint32_t offset) {
+// address of row `col` of a matrix whose rows are `pitch_bytes` apart: one 32 x 32 + 64 bit multiply-add
+__device__ __forceinline__ const void* row_of_b(const float* base, uint32_t col, uint32_t pitch_bytes) {
   uint64_t a;
-  asm("mad.wide.u32 %0, %1, 4, %2;" : "=l"(a) : "r"(offset), "l"(reinterpret_cast<uint64_t>(base)));
+  asm("mad.wide.u32 %0, %1, %2, %3;" : "=l"(a) : "r"(col), "r"(pitch_bytes), "l"(reinterpret_cast<uint64_t>(base)));
   return reinterpret_cast<const void*>(a);
 }
 
 constexpr int kRingFeatures = 128;   // features one warp of the ring kernel covers
 
-constexpr uint32_t kNoGather = 0xffffffffu;   // offset of a slot that gathers nothing (padding, stored zero)
+constexpr uint32_t kNoGather = 0xffffffffu;   // column of a slot that gathers nothing (padding, stored zero)
 
 // Everything that is the same for all lanes of a warp is computed once per slot by ONE lane while
-// a strip of 32 slots is staged (offset of the row of B in elements, "gathers nothing" folded into
-// the offset, "an ELL row with another row id starts here" as one bit of a warp vote), so that the
+// a strip of 32 slots is staged ("gathers nothing" folded into the column index, "an ELL row with
+// another row id starts here" as one bit of a warp vote), so that the
 // loop over the slots, which every lane executes for every slot, is left with one address
 // computation, one copy, one shared-memory load and the multiply-adds.
 template <int D, int WC, int POL, bool MD>
@@ -394,7 +394,7 @@ __device__ __forceinline__ void walk_slots_ring(const int32_t* __restrict__ rows
   int carry = first_row;         // row id of the last slot of the strip staged before
   auto store_strip = [&](int k) {
     const int h = (k & 1) * 32 + lane;
-    so[h] = pv != 0.f ? (uint32_t)pc * (uint32_t)ldb : kNoGather;
+    so[h] = pv != 0.f ? (uint32_t)pc : kNoGather;
     sv[h] = pv;
     rd[h] = pr;
     int before = __shfl_up_sync(0xffffffffu, pr, 1);
@@ -410,6 +410,7 @@ __device__ __forceinline__ void walk_slots_ring(const int32_t* __restrict__ rows
 
   const float4* ring_lane = ring + lane;
   const uint32_t ring_s = (uint32_t)__cvta_generic_to_shared(ring_lane);
+  const uint32_t pitch = (uint32_t)ldb * 4u;   // ldb < 2^30 is checked by the launch
   const uint4* so4 = reinterpret_cast<const uint4*>(so);
   const float4* sv4 = reinterpret_cast<const float4*>(sv);
   // start the copies of rows j0 .. j0+7 (j0 a multiple of 8) into ring slots SLOT .. SLOT+7 and close
@@ -429,7 +430,7 @@ __device__ __forceinline__ void walk_slots_ring(const int32_t* __restrict__ rows
       const uint32_t o[U] = {oa.x, oa.y, oa.z, oa.w, ob.x, ob.y, ob.z, ob.w};
 #pragma unroll
       for (int u = 0; u < U; ++u)
-        if (o[u] != kNoGather && active) cp_async_16(ring_s + (uint32_t)(SLOT + u) * 512u, row_of_b(Bf, o[u]));
+        if (o[u] != kNoGather && active) cp_async_16(ring_s + (uint32_t)(SLOT + u) * 512u, row_of_b(Bf, o[u], pitch));
     }
     cp_async_commit();
   };
@@ -713,6 +714,165 @@ spmm_csr_kernel(const int64_t* __restrict__ indptr, const int32_t* __restrict__ 
   flush(cur, (cur == first_row && head_open) || s1 < nb);
 }
 
+// The CSR product with the gathers staged through the same per-lane shared-memory ring as
+// spmm_hyb_ring_kernel: a warp takes `spg` consecutive entries and 128 features, copies rows of B
+// 16 entries ahead of the one it is adding up, and follows the row boundaries exactly like the
+// register kernel above (same order of additions, same flush rules).
+template <int D>
+__global__ void __launch_bounds__(kThreads, 3)
+spmm_csr_ring_kernel(const int64_t* __restrict__ indptr, const int32_t* __restrict__ indices,
+                     const float* __restrict__ data, int64_t row_begin, int64_t row_end,
+                     const float* __restrict__ B, int ldb, float* __restrict__ C, int64_t ldc, int N, int spg) {
+  constexpr int GPC = kThreads / 32, U = 8;
+  static_assert(D == 2 * U, "two commit groups of eight rows");
+  extern __shared__ __align__(16) unsigned char ring_bytes[];
+  __shared__ __align__(16) uint32_t s_off[GPC * 64];
+  __shared__ __align__(16) float s_val[GPC * 64];
+  __shared__ int64_t s_bd[kThreads];
+  const int g = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t base = indptr[row_begin];
+  const int64_t total = indptr[row_end] - base;
+  const int64_t s0 = ((int64_t)blockIdx.x * GPC + g) * (int64_t)spg;
+  if (s0 >= total) return;
+  const int64_t s1 = min(s0 + spg, total);
+  uint32_t* so = s_off + g * 64;
+  float* sv = s_val + g * 64;
+  int64_t* bd = s_bd + g * 32;
+
+  // 33-ary search, one probe per lane: the row that holds entry s0
+  int64_t lo = row_begin, hi = row_end;   // indptr[lo] - base <= s0, answer in [lo, hi)
+  while (hi - lo > 1) {
+    const int64_t span = hi - lo;
+    int64_t q = lo + ((int64_t)(lane + 1) * span) / 33;
+    if (q <= lo) q = lo + 1;
+    const bool le = indptr[q] - base <= s0;
+    const int cnt = __popc(__ballot_sync(0xffffffffu, le));   // probes are monotone
+    const int64_t qlo = __shfl_sync(0xffffffffu, q, cnt > 0 ? cnt - 1 : 0);
+    const int64_t qhi = __shfl_sync(0xffffffffu, q, cnt < 32 ? cnt : 31);
+    if (cnt > 0) lo = qlo;
+    if (cnt < 32) hi = qhi;
+  }
+  int64_t cur = lo;
+  const int64_t first_row = cur;
+  const bool head_open = indptr[cur] - base < s0;
+
+  int kb = 0;   // boundaries of the next 32 rows, refilled when used up
+  auto refill = [&]() {
+    __syncwarp();
+    const int64_t r = cur + 1 + lane;
+    bd[lane] = indptr[r < row_end ? r : row_end] - base;
+    __syncwarp();
+    kb = 0;
+  };
+  refill();
+  int64_t nb = bd[0];   // first entry of the next row
+
+  const int f0 = blockIdx.y * kRingFeatures + lane * 4;
+  const bool active = f0 < N;
+  Chunk<4> acc;
+  acc.zero();
+  auto flush = [&](int64_t row, bool open) {
+    float* dst = C + (row - row_begin) * ldc + f0;
+    if (active) {
+      if (open) acc.red(dst); else acc.store_stream(dst);
+    }
+    acc.zero();
+  };
+
+  const float* __restrict__ Bf = B + f0;
+  const int n = (int)(s1 - s0);
+  const int nstrips = (n + 31) >> 5;
+  int pc = 0;
+  float pv = 0.f;
+  auto load_strip = [&](int k) {
+    const int64_t idx = s0 + (int64_t)k * 32 + lane;
+    const bool in = idx < s1;
+    pc = in ? __ldcs(indices + base + idx) : 0;
+    pv = in ? (data ? __ldcs(data + base + idx) : 1.f) : 0.f;
+  };
+  auto store_strip = [&](int k) {
+    const int h = (k & 1) * 32 + lane;
+    so[h] = pv != 0.f ? (uint32_t)pc : kNoGather;
+    sv[h] = pv;
+  };
+  load_strip(0);
+  store_strip(0);
+  __syncwarp();
+  if (nstrips > 1) load_strip(1);
+
+  const float4* ring_lane = reinterpret_cast<const float4*>(ring_bytes) + (size_t)g * D * 32 + lane;
+  const uint32_t ring_s = (uint32_t)__cvta_generic_to_shared(ring_lane);
+  const uint32_t pitch = (uint32_t)ldb * 4u;
+  const uint4* so4 = reinterpret_cast<const uint4*>(so);
+  const float4* sv4 = reinterpret_cast<const float4*>(sv);
+  auto issue_batch = [&](int j0, auto slot_tag) {
+    constexpr int SLOT = decltype(slot_tag)::value;
+    if (j0 < nstrips * 32) {
+      if ((j0 & 31) == 0 && j0 > 0) {
+        const int k = j0 >> 5;
+        __syncwarp();
+        store_strip(k);
+        __syncwarp();
+        if (k + 1 < nstrips) load_strip(k + 1);
+      }
+      const uint4 oa = so4[(j0 & 63) >> 2], ob = so4[((j0 & 63) >> 2) + 1];
+      const uint32_t o[U] = {oa.x, oa.y, oa.z, oa.w, ob.x, ob.y, ob.z, ob.w};
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if (o[u] != kNoGather && active) cp_async_16(ring_s + (uint32_t)(SLOT + u) * 512u, row_of_b(Bf, o[u], pitch));
+    }
+    cp_async_commit();
+  };
+  auto for_each_batch = [&](auto&& body) {
+    body(std::integral_constant<int, 0>{});
+    body(std::integral_constant<int, U>{});
+  };
+
+  for_each_batch([&](auto slot_tag) { issue_batch(decltype(slot_tag)::value, slot_tag); });
+  wait_for_prior_grid();   // csr_prepare_kernel has cleared the rows that receive atomics
+  for (int jc0 = 0; jc0 < n; jc0 += D) {
+    for_each_batch([&](auto slot_tag) {
+      constexpr int SLOT = decltype(slot_tag)::value;
+      const int jc = jc0 + SLOT;
+      if (jc >= n) return;
+      const float4 va = sv4[(jc & 63) >> 2], vb = sv4[((jc & 63) >> 2) + 1];
+      const float val[U] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
+      const int64_t pos0 = s0 + jc;
+      cp_async_wait<D / U - 1>();
+      if (nb >= pos0 + U) {   // no row ends inside these eight entries
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          if (val[u] != 0.f && active) {
+            Chunk<4> x;
+            x.v = ring_lane[(SLOT + u) * 32];
+            acc.fma(val[u], x);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int64_t pos = pos0 + u;
+          if (pos < s1) {
+            while (pos == nb) {   // the current row ended here (and empty rows may follow)
+              flush(cur, cur == first_row && head_open);
+              ++cur;
+              if (++kb == 32) refill();
+              nb = bd[kb];
+            }
+            if (val[u] != 0.f && active) {
+              Chunk<4> x;
+              x.v = ring_lane[(SLOT + u) * 32];
+              acc.fma(val[u], x);
+            }
+          }
+        }
+      }
+      issue_batch(jc + D, slot_tag);
+    });
+  }
+  flush(cur, (cur == first_row && head_open) || s1 < nb);
+}
+
 // Ragged all-gather of C over peer mappings: the rows of this rank's block are read once and
 // stored into the same rows of every destination (plain 128-bit peer stores over NVLink).
 template <int VEC>
@@ -900,11 +1060,9 @@ int launch_hyb_pol(const SpmmTable<MAXB>& tbl, int64_t tiles, const lf_hyb* A, c
   return LF_OK;
 }
 
-// The ring kernel exists for 128-bit gathers over full warps and addresses a row of B by a 32-bit
-// element offset (column * ldb).
-bool ring_applies(const lf_hyb* A, const FeatCfg& cfg, int64_t ldb) {
-  return cfg.VEC == 4 && cfg.G == 32 && (int64_t)A->num_cols * ldb < (int64_t)kNoGather;
-}
+// The ring kernels exist for 128-bit gathers over full warps; they multiply the column by a 32-bit
+// row pitch in bytes.
+bool ring_applies(const FeatCfg& cfg, int64_t ldb) { return cfg.VEC == 4 && cfg.G == 32 && ldb < (1ll << 30); }
 
 template <int MAXB>
 int launch_hyb(const SpmmTable<MAXB>& tbl, int64_t tiles, const lf_hyb* A, const void* Bv, int64_t ldb,
@@ -914,7 +1072,7 @@ int launch_hyb(const SpmmTable<MAXB>& tbl, int64_t tiles, const lf_hyb* A, const
   const float* B = (const float*)Bv;
   const int pol = cache_policy(), minb = min_blocks();
   const int ring = gather_ring();
-  if (ring > 0 && ring_applies(A, cfg, ldb)) {
+  if (ring > 0 && ring_applies(cfg, ldb)) {
     // one warp per 128 features; the ring of a thread block takes depth * 4 KiB of shared memory
     dim3 grid((unsigned)tiles, (unsigned)((N + kRingFeatures - 1) / kRingFeatures));
     const size_t smem = (size_t)(kThreads / 32) * ring * 32 * sizeof(float4);
@@ -1024,7 +1182,7 @@ const char* lf_spmm_hyb_f32_kernel_name(const lf_hyb* A, const float* B, int64_t
                                         int32_t N) {
   if (!A || N < 1) return "";
   const FeatCfg cfg = pick_cfg(B, ldb, C, ldc, N);
-  return gather_ring() > 0 && ring_applies(A, cfg, ldb) ? "spmm_hyb_ring_kernel" : "spmm_hyb_kernel";
+  return gather_ring() > 0 && ring_applies(cfg, ldb) ? "spmm_hyb_ring_kernel" : "spmm_hyb_kernel";
 }
 
 int lf_spmm_hyb_bf16(const lf_hyb* A, const uint16_t* B, int64_t ldb, float* C, int64_t ldc, int32_t N,
@@ -1276,6 +1434,15 @@ int lf_spmm_csr_f32(const int64_t* indptr, const int32_t* indices, const float* 
   if (nnz == 0) return LF_OK;
   const int64_t blocks = ceil_div64(nnz, (int64_t)spg * gpc);
   LF_REQUIRE(blocks < (1ll << 31), "too many thread blocks");
+  if (gather_ring() > 0 && ring_applies(cfg, ldb)) {
+    dim3 rgrid((unsigned)blocks, (unsigned)((N + kRingFeatures - 1) / kRingFeatures));
+    const size_t smem = (size_t)(kThreads / 32) * 16 * 32 * sizeof(float4);
+    auto kern = spmm_csr_ring_kernel<16>;
+    LF_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    LF_CUDA_CHECK(launch_dep_smem(kern, rgrid, kThreads, smem, st, true, indptr, indices, data, row_begin, row_end, B,
+                                  (int)ldb, C, ldc, N, spg));
+    return LF_OK;
+  }
   dim3 grid((unsigned)blocks, (unsigned)((N + cfg.pass - 1) / cfg.pass));
 #define LF_LAUNCH(G_, V_, VEC_)                                                                              \
   LF_CUDA_CHECK(launch_dep(spmm_csr_kernel<G_, V_, VEC_>, grid, kThreads, st, true, indptr, indices, data, row_begin, \

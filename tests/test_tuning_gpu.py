@@ -85,6 +85,29 @@ def test_gather_ring_adds_up_in_the_same_order_as_the_register_kernel(cuda_devic
     assert lib.lf_set_option(_cabi.LF_OPT_SPMM_GATHER_RING, 8) == _cabi.LF_ERR_INVALID_ARGUMENT
 
 
+@pytest.mark.parametrize("N", [100, 128, 384])
+def test_csr_product_with_and_without_the_gather_ring(cuda_device, restore_defaults, N):
+    """lf_spmm_csr_f32 has the same two forms; rows that one thread group owns are bit-identical."""
+    import torch
+    lib = _cabi.load()
+    csr = synth.skewed_rows(M=6000, seed=9, heavy_rows=4, heavy_len=2000)
+    d = hyb.DeviceCsr.from_host(csr.indptr, csr.indices, csr.data, csr.shape, cuda_device)
+    B = synth.dense_features(csr.shape[1], N, 6)
+    Bd = torch.from_numpy(B).to(cuda_device)
+    want = ho.spmm_scipy_csr(csr.indptr, csr.indices, csr.data.astype(np.float64), csr.shape, B.astype(np.float64))
+    got = {}
+    for depth in (0, 16):
+        assert lib.lf_set_option(_cabi.LF_OPT_SPMM_GATHER_RING, depth) == 0
+        for rr in ((0, csr.shape[0]), (123, 4567)):
+            C = torch.full((rr[1] - rr[0], N), float("nan"), device=cuda_device)
+            hyb.spmm_csr(d, Bd, out=C, row_range=rr)
+            got[depth, rr] = C.cpu().numpy()
+            np.testing.assert_allclose(got[depth, rr], want[rr[0]:rr[1]], rtol=1e-5, atol=1e-4)
+    full = (0, csr.shape[0])
+    same = (got[0, full] == got[16, full]).all(axis=1)
+    assert same.mean() > 0.9     # all but the rows cut by a group boundary (reduced by atomics in any order)
+
+
 def test_every_block_kernel_variant_gives_the_same_product(cuda_device, restore_defaults):
     import scipy.sparse as sp
     import torch
