@@ -989,12 +989,12 @@ def run_ours(args, rank, local_rank, world):
 # captured on).  The figure is reported only while kernel_source_hash() still matches.
 _NCU = "ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum -c 2 on `bench.py --workload %s --steps 2 --warmup 3 --no-cpu --no-e2e`"
 TRAFFIC_BYTES_PER_LAUNCH = {
-    ("powerlaw", "hyb", "f32", 128, 1, 1): (3140107008 + 542763520, _NCU % "powerlaw" + ", full size", "3e1b3539f0b7a0d6"),
-    ("powerlaw", "hyb", "f32", 128, 2, 1): (3419185408 + 971536128, _NCU % "powerlaw --parts 2" + ", full size", "3e1b3539f0b7a0d6"),
-    ("powerlaw", "hyb", "f32", 128, 4, 1): (3234430208 + 1476699648, _NCU % "powerlaw --parts 4" + ", full size", "3e1b3539f0b7a0d6"),
-    ("powerlaw", "hyb", "f32", 128, 8, 1): (3312404992 + 1992815616, _NCU % "powerlaw --parts 8" + ", full size", "3e1b3539f0b7a0d6"),
-    ("uniform", "hyb", "f32", 64, 1, 1): (33723750912 + 1074079232, _NCU % "uniform" + ", full size", "3e1b3539f0b7a0d6"),
-    ("skew", "hyb", "f32", 256, 1, 1): (19901111040 + 1107648512, _NCU % "skew" + ", full size", "3e1b3539f0b7a0d6"),
+    ("powerlaw", "hyb", "f32", 128, 1, 1): (3140912384 + 543225088, _NCU % "powerlaw" + ", full size", "9c854d398bd0b961"),
+    ("powerlaw", "hyb", "f32", 128, 2, 1): (3421384192 + 971631104, _NCU % "powerlaw --parts 2" + ", full size", "9c854d398bd0b961"),
+    ("powerlaw", "hyb", "f32", 128, 4, 1): (3233884928 + 1477203200, _NCU % "powerlaw --parts 4" + ", full size", "9c854d398bd0b961"),
+    ("powerlaw", "hyb", "f32", 128, 8, 1): (3308103424 + 1993027840, _NCU % "powerlaw --parts 8" + ", full size", "9c854d398bd0b961"),
+    ("uniform", "hyb", "f32", 64, 1, 1): (33723548160 + 1075213312, _NCU % "uniform" + ", full size", "9c854d398bd0b961"),
+    ("skew", "hyb", "f32", 256, 1, 1): (19900887808 + 1108450304, _NCU % "skew" + ", full size", "9c854d398bd0b961"),
     ("blocks", "bsr8", "f32", 128, 1, 1): (2 * 1433762688, "ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum -c 2 on `bench.py --workload blocks --rows 1048576 --steps 2 --warmup 3 --no-cpu --no-e2e --no-build-timing`: "
                                            "captured at 2^20 rows, doubled (traffic is proportional to the rows at a fixed band)", "b233a3695787bdd6"),
     ("blocks", "bsr8", "bf16", 128, 1, 1): (2 * 989854976, "ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum -c 2 on `bench.py --workload blocks --dtype bf16 --rows 1048576 --steps 2 --warmup 3 --no-cpu --no-e2e --no-build-timing`: "
