@@ -342,7 +342,7 @@ bsr8_spmm_16bit_kernel(const int64_t* __restrict__ indptr, const int32_t* __rest
   using Cfg = H16Cfg<D>;
   extern __shared__ __align__(128) uint8_t smem_raw[];
   const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3, warp = threadIdx.x >> 5;
-  const int64_t work = (int64_t)blockIdx.x * kWarps + warp;
+  const int64_t work = (int64_t)blockIdx.x * (blockDim.x >> 5) + warp;   // 8 warps per block or fewer
   int64_t grp;
   int tile;
   split_work(work, tiles, 0, grp, tile);
@@ -911,6 +911,26 @@ static int launch_16bit(bool bf16, const int64_t* indptr, const int32_t* indices
     return bsr8_16bit_pipe_launch(bf16, indptr, indices, blocks, r0, r1, B, ldb, C, ldc, N, g_bsr_pipe_shape,
                                   g_bsr_rows_per_warp, g_bsr_pipe_3d != 0, st);
   if (copy_engine() == 2 || copy_engine() == 3) return bsr8_16bit_tma_launch(copy_engine() == 3, bf16, indptr, indices, blocks, r0, r1, B, ldb, C, ldc, N, D, rpw, st);
+  if (g_bsr_pipe_shape > 0) {
+    // ring shape: warps per thread block * 10 + depth of each warp's ring (fewer warps, deeper rings:
+    // more of the shared memory holds copies in flight)
+    const int W = g_bsr_pipe_shape / 10, RD = g_bsr_pipe_shape % 10;
+    LF_REQUIRE(W >= 2 && W <= 8 && (RD == 3 || RD == 4 || RD == 5 || RD == 6 || RD == 8), "ring shape %d", g_bsr_pipe_shape);
+    const int64_t wgrid = ceil_div64(ceil_div64(r1 - r0, rpw) * tiles, W);
+    LF_REQUIRE(wgrid < (1ll << 31), "too many thread blocks");
+#define LF_BSR16W(B_, D_)                                                                                     \
+  do {                                                                                                        \
+    auto k = bsr8_spmm_16bit_kernel<B_, D_, 2>;                                                               \
+    const int smem = W * D_ * H16Cfg<D_>::kStage;                                                             \
+    if (int s = set_smem(k, smem)) return s;                                                                  \
+    k<<<(unsigned)wgrid, W * 32, smem, st>>>(indptr, indices, blocks, r0, r1, B, (int)ldb, C, ldc, N, tiles, rpw); \
+  } while (0)
+    if (bf16) { if (RD == 3) LF_BSR16W(true, 3); else if (RD == 4) LF_BSR16W(true, 4); else if (RD == 5) LF_BSR16W(true, 5); else if (RD == 6) LF_BSR16W(true, 6); else LF_BSR16W(true, 8); }
+    else      { if (RD == 3) LF_BSR16W(false, 3); else if (RD == 4) LF_BSR16W(false, 4); else if (RD == 5) LF_BSR16W(false, 5); else if (RD == 6) LF_BSR16W(false, 6); else LF_BSR16W(false, 8); }
+#undef LF_BSR16W
+    LF_CUDA_CHECK(cudaGetLastError());
+    return LF_OK;
+  }
 #define LF_BSR16(B_, D_, M_)                                                                                  \
   do {                                                                                                        \
     auto k = bsr8_spmm_16bit_kernel<B_, D_, M_>;                                                              \
