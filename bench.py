@@ -995,10 +995,10 @@ TRAFFIC_BYTES_PER_LAUNCH = {
     ("powerlaw", "hyb", "f32", 128, 8, 1): (3308103424 + 1993027840, _NCU % "powerlaw --parts 8" + ", full size", "9c854d398bd0b961"),
     ("uniform", "hyb", "f32", 64, 1, 1): (33723548160 + 1075213312, _NCU % "uniform" + ", full size", "9c854d398bd0b961"),
     ("skew", "hyb", "f32", 256, 1, 1): (19900887808 + 1108450304, _NCU % "skew" + ", full size", "9c854d398bd0b961"),
-    ("blocks", "bsr8", "f32", 128, 1, 1): (2 * 1433762688, "ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum -c 2 on `bench.py --workload blocks --rows 1048576 --steps 2 --warmup 3 --no-cpu --no-e2e --no-build-timing`: "
-                                           "captured at 2^20 rows, doubled (traffic is proportional to the rows at a fixed band)", "b233a3695787bdd6"),
-    ("blocks", "bsr8", "bf16", 128, 1, 1): (2 * 989854976, "ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum -c 2 on `bench.py --workload blocks --dtype bf16 --rows 1048576 --steps 2 --warmup 3 --no-cpu --no-e2e --no-build-timing`: "
-                                            "captured at 2^20 rows, doubled (traffic is proportional to the rows at a fixed band)", "b233a3695787bdd6"),
+    ("blocks", "bsr8", "f32", 128, 1, 1): (2 * (918055168 + 508351488), "ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum -c 2 on `bench.py --workload blocks --rows 1048576 --steps 2 --warmup 3 --no-cpu --no-e2e --no-build-timing`: "
+                                           "captured at 2^20 rows, doubled (traffic is proportional to the rows at a fixed band)", "36ec43bea9176c95"),
+    ("blocks", "bsr8", "bf16", 128, 1, 1): (2 * (484502016 + 493679872), "ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum -c 2 on `bench.py --workload blocks --dtype bf16 --rows 1048576 --steps 2 --warmup 3 --no-cpu --no-e2e --no-build-timing`: "
+                                            "captured at 2^20 rows, doubled (traffic is proportional to the rows at a fixed band)", "36ec43bea9176c95"),
 }
 
 

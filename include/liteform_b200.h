@@ -82,6 +82,8 @@ const char* lf_last_error(void);
                                           a block, 0 one 2-D tiled copy per 128-byte feature slice */
 #define LF_OPT_BSR_UMMA_PRODUCER 9      /* copy engine 5: who fills shared memory: 0 (default) one warp issuing tiled bulk
                                           copies, 2 or 4 = that many warps issuing per-lane cp.async */
+#define LF_OPT_BSR_BLOCK_WARPS 11       /* copy engine 1, more than 64 features: warps per thread block, 1..8 (0 = automatic:
+                                          4 for 16-bit inputs up to 128 features, else 8) */
 #define LF_OPT_SPMM_GATHER_RING 10      /* float32 product with 128-bit gathers and more than 64 features: where the
                                           gathered rows of B land: 16 (default) a ring of 16 rows per warp in shared
                                           memory, filled by cp.async; 0 registers (8 rows in flight per warp) */

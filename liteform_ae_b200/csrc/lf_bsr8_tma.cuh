@@ -45,6 +45,7 @@ int bsr8_16bit_umma_launch(bool bf16, const int64_t* indptr, const int32_t* indi
 extern int g_bsr_umma_producer;   // LF_OPT_BSR_UMMA_PRODUCER
 int bsr8_umma_timeouts(cudaStream_t st, int* count);
 
+extern int g_bsr_block_warps;   // LF_OPT_BSR_BLOCK_WARPS
 extern int g_bsr_pipe_shape;    // LF_OPT_BSR_PIPE_SHAPE
 extern int g_bsr_pipe_3d;       // LF_OPT_BSR_PIPE_3D
 

@@ -76,7 +76,7 @@ bsr8_spmm_f32_kernel(const int64_t* __restrict__ indptr, const int32_t* __restri
   // the A blocks they share come from HBM once.  With many tiles the B rows all of them gather
   // (band x N) outgrow the L2; then (tile_major_groups > 0) all row groups of tile 0 run first,
   // then tile 1, ...: B is read from HBM once per tile and A once per tile.
-  const int64_t work = (int64_t)blockIdx.x * kWarps + warp;
+  const int64_t work = (int64_t)blockIdx.x * (blockDim.x >> 5) + warp;   // 8 warps per block or fewer
   int64_t grp;
   int tile;
   split_work(work, tiles, tile_major_groups, grp, tile);
@@ -758,6 +758,9 @@ int g_bsr_tile_order = 0;
 // thread-block pipeline: blocks per stage * 10 + stages (0 = default), and whether one 3-D tiled
 // copy per block may be used (1) or one 2-D copy per feature slice (0)
 int g_bsr_pipe_shape = 0;
+// warps per thread block of the cp.async-ring kernels for more than 64 features (LF_OPT_BSR_BLOCK_WARPS)
+int g_bsr_block_warps = 0;
+static int block_warps(int automatic) { return g_bsr_block_warps ? g_bsr_block_warps : automatic; }
 int g_bsr_pipe_3d = 1;
 // tcgen05 path: who fills shared memory: 0 one warp issuing tiled bulk copies, 2 / 4 that many warps issuing cp.async
 int g_bsr_umma_producer = 0;
@@ -842,12 +845,16 @@ int lf_spmm_bsr8_f32(const int64_t* indptr, const int32_t* indices, const float*
   if (T == 2 && (copy_engine() == 2 || copy_engine() == 3))
     return bsr8_f32_tma_launch(copy_engine() == 3, indptr, indices, blocks, block_row_begin, block_row_end, B, ldb, C, ldc, N, D, rpw,
                                tile_major > 0, st);
+  const int W = block_warps(8);   // float32: no gain from smaller thread blocks (0.92 / 0.95 ms at N = 128)
+  const int64_t wgrid = ceil_div64(groups * tiles, W);
+  LF_REQUIRE(wgrid < (1ll << 31), "too many thread blocks");
 #define LF_BSR(T_, D_, M_)                                                                                   \
   do {                                                                                                       \
     auto k = bsr8_spmm_f32_kernel<T_, D_, M_>;                                                               \
-    if (int s = set_smem(k, F32Cfg<T_, D_>::kSmem)) return s;                                                \
-    k<<<(unsigned)grid, kThreadsBsr, F32Cfg<T_, D_>::kSmem, st>>>(indptr, indices, blocks, block_row_begin,  \
-                                                                  block_row_end, B, (int)ldb, C, ldc, N, tiles, rpw, tile_major); \
+    const int smem = W * D_ * F32Cfg<T_, D_>::kStage;                                                        \
+    if (int s = set_smem(k, smem)) return s;                                                                 \
+    k<<<(unsigned)wgrid, W * 32, smem, st>>>(indptr, indices, blocks, block_row_begin, block_row_end, B,    \
+                                             (int)ldb, C, ldc, N, tiles, rpw, tile_major);                   \
   } while (0)
   if (T == 2) { if (D == 3) LF_BSR(2, 3, 2); else LF_BSR(2, 4, 1); }
   else        { if (D == 3) LF_BSR(1, 3, 3); else LF_BSR(1, 4, 3); }
@@ -911,32 +918,19 @@ static int launch_16bit(bool bf16, const int64_t* indptr, const int32_t* indices
     return bsr8_16bit_pipe_launch(bf16, indptr, indices, blocks, r0, r1, B, ldb, C, ldc, N, g_bsr_pipe_shape,
                                   g_bsr_rows_per_warp, g_bsr_pipe_3d != 0, st);
   if (copy_engine() == 2 || copy_engine() == 3) return bsr8_16bit_tma_launch(copy_engine() == 3, bf16, indptr, indices, blocks, r0, r1, B, ldb, C, ldc, N, D, rpw, st);
-  if (g_bsr_pipe_shape > 0) {
-    // ring shape: warps per thread block * 10 + depth of each warp's ring (fewer warps, deeper rings:
-    // more of the shared memory holds copies in flight)
-    const int W = g_bsr_pipe_shape / 10, RD = g_bsr_pipe_shape % 10;
-    LF_REQUIRE(W >= 2 && W <= 8 && (RD == 3 || RD == 4 || RD == 5 || RD == 6 || RD == 8), "ring shape %d", g_bsr_pipe_shape);
-    const int64_t wgrid = ceil_div64(ceil_div64(r1 - r0, rpw) * tiles, W);
-    LF_REQUIRE(wgrid < (1ll << 31), "too many thread blocks");
-#define LF_BSR16W(B_, D_)                                                                                     \
-  do {                                                                                                        \
-    auto k = bsr8_spmm_16bit_kernel<B_, D_, 2>;                                                               \
-    const int smem = W * D_ * H16Cfg<D_>::kStage;                                                             \
-    if (int s = set_smem(k, smem)) return s;                                                                  \
-    k<<<(unsigned)wgrid, W * 32, smem, st>>>(indptr, indices, blocks, r0, r1, B, (int)ldb, C, ldc, N, tiles, rpw); \
-  } while (0)
-    if (bf16) { if (RD == 3) LF_BSR16W(true, 3); else if (RD == 4) LF_BSR16W(true, 4); else if (RD == 5) LF_BSR16W(true, 5); else if (RD == 6) LF_BSR16W(true, 6); else LF_BSR16W(true, 8); }
-    else      { if (RD == 3) LF_BSR16W(false, 3); else if (RD == 4) LF_BSR16W(false, 4); else if (RD == 5) LF_BSR16W(false, 5); else if (RD == 6) LF_BSR16W(false, 6); else LF_BSR16W(false, 8); }
-#undef LF_BSR16W
-    LF_CUDA_CHECK(cudaGetLastError());
-    return LF_OK;
-  }
+  // Warps per thread block: the ring of a warp takes D stages of shared memory, so smaller thread
+  // blocks pack the SM in finer steps (four blocks of four warps instead of two of eight) and
+  // leave and enter it in smaller units.  Measured on the banded benchmark matrix (bf16, 8 / 4
+  // warps): N = 128 0.532 / 0.516 ms, N = 256 1.039 / 1.050 ms, N = 512 2.219 / 2.348 ms.
+  const int W = block_warps(tiles == 1 ? 4 : 8);
+  const int64_t wgrid = ceil_div64(ceil_div64(r1 - r0, rpw) * tiles, W);
+  LF_REQUIRE(wgrid < (1ll << 31), "too many thread blocks");
 #define LF_BSR16(B_, D_, M_)                                                                                  \
   do {                                                                                                        \
     auto k = bsr8_spmm_16bit_kernel<B_, D_, M_>;                                                              \
-    if (int s = set_smem(k, H16Cfg<D_>::kSmem)) return s;                                                     \
-    k<<<(unsigned)grid, kThreadsBsr, H16Cfg<D_>::kSmem, st>>>(indptr, indices, blocks, r0, r1, B, (int)ldb, C, \
-                                                              ldc, N, tiles, rpw);                            \
+    const int smem = W * D_ * H16Cfg<D_>::kStage;                                                             \
+    if (int s = set_smem(k, smem)) return s;                                                                  \
+    k<<<(unsigned)wgrid, W * 32, smem, st>>>(indptr, indices, blocks, r0, r1, B, (int)ldb, C, ldc, N, tiles, rpw); \
   } while (0)
   if (bf16) { if (D == 3) LF_BSR16(true, 3, 2); else LF_BSR16(true, 4, 1); }
   else      { if (D == 3) LF_BSR16(false, 3, 2); else LF_BSR16(false, 4, 1); }

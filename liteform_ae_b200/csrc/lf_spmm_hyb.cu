@@ -1146,6 +1146,10 @@ int lf_set_option(int32_t option, int32_t value) {
       LF_REQUIRE(value >= 0 && value <= 5, "copy engine %d out of range", value);
       g_bsr_copy_engine = value;
       return LF_OK;
+    case LF_OPT_BSR_BLOCK_WARPS:
+      LF_REQUIRE(value == 0 || (value >= 1 && value <= 8), "warps per thread block %d out of range", value);
+      g_bsr_block_warps = value;
+      return LF_OK;
     case LF_OPT_BSR_PIPE_SHAPE:
       LF_REQUIRE(value >= 0 && value <= 99, "pipeline shape %d out of range", value);
       g_bsr_pipe_shape = value;

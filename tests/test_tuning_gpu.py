@@ -27,6 +27,7 @@ def restore_defaults():
     lib.lf_set_option(_cabi.LF_OPT_BSR_PIPE_3D, 1)
     lib.lf_set_option(_cabi.LF_OPT_BSR_UMMA_PRODUCER, 0)
     lib.lf_set_option(_cabi.LF_OPT_SPMM_GATHER_RING, DEFAULT_GATHER_RING)
+    lib.lf_set_option(_cabi.LF_OPT_BSR_BLOCK_WARPS, 0)
 
 
 def test_every_spmm_variant_gives_the_same_product(cuda_device, restore_defaults):
@@ -135,7 +136,15 @@ def test_every_block_kernel_variant_gives_the_same_product(cuda_device, restore_
             assert lib.lf_bsr_set_tuning(2, 0, 0) == 0
             np.testing.assert_allclose(bsr.spmm_bsr8(a32, Bd).cpu().numpy(), want, rtol=1e-5, atol=1e-4)
         assert lib.lf_set_option(_cabi.LF_OPT_BSR_TILE_ORDER, 0) == 0
+        assert lib.lf_set_option(_cabi.LF_OPT_BSR_COPY_ENGINE, 1) == 0
+        assert lib.lf_bsr_set_tuning(0, 0, 0) == 0
+        for warps in (1, 3, 4, 8):      # thread blocks of fewer warps: same warp-private rings, same result
+            assert lib.lf_set_option(_cabi.LF_OPT_BSR_BLOCK_WARPS, warps) == 0
+            np.testing.assert_allclose(bsr.spmm_bsr8(a32, Bd).cpu().numpy(), want, rtol=1e-5, atol=1e-4)
+            np.testing.assert_allclose(bsr.spmm_bsr8(a16, B16).cpu().numpy(), want16, rtol=1e-5, atol=1e-4)
+        assert lib.lf_set_option(_cabi.LF_OPT_BSR_BLOCK_WARPS, 0) == 0
     assert lib.lf_bsr_set_tuning(3, 0, 0) == _cabi.LF_ERR_INVALID_ARGUMENT
+    assert lib.lf_set_option(_cabi.LF_OPT_BSR_BLOCK_WARPS, 9) == _cabi.LF_ERR_INVALID_ARGUMENT
     assert lib.lf_set_option(_cabi.LF_OPT_BSR_COPY_ENGINE, 6) == _cabi.LF_ERR_INVALID_ARGUMENT
 
 
