@@ -324,7 +324,7 @@ template <int PENDING>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(PENDING) : "memory"); }
 
 // address of row `col` of a matrix whose rows are `pitch_bytes` apart: one 32 x 32 + 64 bit multiply-add
-__device__ __forceinline__ const void* row_of_b(const float* base, uint32_t col, uint32_t pitch_bytes) {
+__device__ __forceinline__ const void* row_of_b(const void* base, uint32_t col, uint32_t pitch_bytes) {
   uint64_t a;
   asm("mad.wide.u32 %0, %1, %2, %3;" : "=l"(a) : "r"(col), "r"(pitch_bytes), "l"(reinterpret_cast<uint64_t>(base)));
   return reinterpret_cast<const void*>(a);
@@ -339,10 +339,13 @@ constexpr uint32_t kNoGather = 0xffffffffu;   // column of a slot that gathers n
 // another row id starts here" as one bit of a warp vote), so that the
 // loop over the slots, which every lane executes for every slot, is left with one address
 // computation, one copy, one shared-memory load and the multiply-adds.
-template <int D, int WC, int POL, bool MD>
+// VEC = 4: B in float32, a lane owns 4 features; VEC = 8: B in bf16, a lane owns 8 features -- 16 bytes
+// per lane and row either way, so the ring is the same.
+template <int D, int WC, int POL, bool MD, int VEC>
 __device__ __forceinline__ void walk_slots_ring(const int32_t* __restrict__ rows, const int32_t* __restrict__ cols,
                                                 const float* __restrict__ vals, int wlog, int64_t e0, int64_t e1,
-                                                int64_t ell_rows, bool all_open, const float* __restrict__ B, int ldb,
+                                                int64_t ell_rows, bool all_open,
+                                                const typename BTraits<VEC>::elem* __restrict__ B, int ldb,
                                                 float* __restrict__ C, int64_t ldc, int N, int64_t row_base, int lane,
                                                 uint32_t* so, float* sv, int* rd, float4* ring, const DestList& dl) {
   constexpr int U = 8;   // rows per commit group; row ids can change every WC <= 8 slots
@@ -350,9 +353,9 @@ __device__ __forceinline__ void walk_slots_ring(const int32_t* __restrict__ rows
   const int first_row = rows[e0], last_row = rows[e1 - 1];
   const bool head_open = e0 > 0 && rows[e0 - 1] == first_row;
   const bool tail_open = e1 < ell_rows && rows[e1] == last_row;
-  const int f0 = blockIdx.y * kRingFeatures + lane * 4;
+  const int f0 = blockIdx.y * (32 * VEC) + lane * VEC;
   const bool active = f0 < N;
-  Chunk<4> acc;
+  Chunk<VEC> acc;
   acc.zero();
   int cur = first_row;
 
@@ -374,7 +377,7 @@ __device__ __forceinline__ void walk_slots_ring(const int32_t* __restrict__ rows
     acc.zero();
   };
 
-  const float* __restrict__ Bf = B + f0;
+  const typename BTraits<VEC>::elem* __restrict__ Bf = B + f0;
   const int64_t s0 = e0 << wlog, s1 = e1 << wlog;
   const int n = (int)(s1 - s0);            // a group walks a few hundred slots (one ELL row at the most if wider)
   const int nstrips = (n + 31) >> 5;
@@ -410,7 +413,7 @@ __device__ __forceinline__ void walk_slots_ring(const int32_t* __restrict__ rows
 
   const float4* ring_lane = ring + lane;
   const uint32_t ring_s = (uint32_t)__cvta_generic_to_shared(ring_lane);
-  const uint32_t pitch = (uint32_t)ldb * 4u;   // ldb < 2^30 is checked by the launch
+  const uint32_t pitch = (uint32_t)ldb * (uint32_t)sizeof(typename BTraits<VEC>::elem);   // ldb < 2^30 is checked by the launch
   const uint4* so4 = reinterpret_cast<const uint4*>(so);
   const float4* sv4 = reinterpret_cast<const float4*>(sv);
   // start the copies of rows j0 .. j0+7 (j0 a multiple of 8) into ring slots SLOT .. SLOT+7 and close
@@ -461,9 +464,11 @@ __device__ __forceinline__ void walk_slots_ring(const int32_t* __restrict__ rows
           cur = rd[(jc + u) & 63];
         }
         if (val[u] != 0.f && active) {
-          Chunk<4> x;
-          x.v = ring_lane[(SLOT + u) * 32];
-          acc.fma(val[u], x);
+          typename BTraits<VEC>::raw x;
+          const float4 raw = ring_lane[(SLOT + u) * 32];
+          if constexpr (VEC == 8) x.v = make_uint4(__float_as_uint(raw.x), __float_as_uint(raw.y), __float_as_uint(raw.z), __float_as_uint(raw.w));
+          else x.v = raw;
+          chunk_fma(acc, val[u], x);
         }
       }
       issue_batch(jc + D, slot_tag);   // refills exactly the ring slots read above
@@ -472,12 +477,12 @@ __device__ __forceinline__ void walk_slots_ring(const int32_t* __restrict__ rows
   flush(cur);
 }
 
-template <int D, int MAXB, int POL, int MINB, bool MD>
+template <int D, int MAXB, int POL, int MINB, bool MD, int VEC>
 __global__ void __launch_bounds__(kThreads, MINB)
 spmm_hyb_ring_kernel(const __grid_constant__ SpmmTable<MAXB> tbl, const int32_t* __restrict__ rows_arena,
                      const int32_t* __restrict__ cols_arena, const float* __restrict__ vals_arena,
-                     const float* __restrict__ B, int ldb, float* __restrict__ C, int64_t ldc, int N,
-                     int64_t row_base, const __grid_constant__ DestList dests) {
+                     const typename BTraits<VEC>::elem* __restrict__ B, int ldb, float* __restrict__ C, int64_t ldc,
+                     int N, int64_t row_base, const __grid_constant__ DestList dests) {
   constexpr int GPC = kThreads / 32;
   extern __shared__ __align__(16) unsigned char ring_bytes[];
   __shared__ __align__(16) uint32_t s_off[GPC * 64];
@@ -509,8 +514,8 @@ spmm_hyb_ring_kernel(const __grid_constant__ SpmmTable<MAXB> tbl, const int32_t*
   const bool all_open = d.force_atomic != 0;
   float4* ring = reinterpret_cast<float4*>(ring_bytes) + (size_t)g * D * 32;
 #define LF_WALK(WC_)                                                                                       \
-  walk_slots_ring<D, WC_, POL, MD>(rows, cols, vals, wlog, e0, e1, d.ell_rows, all_open, B, ldb, C, ldc, N, \
-                                   row_base, lane, s_off + g * 64, s_val + g * 64, s_rd + g * 64, ring, dests)
+  walk_slots_ring<D, WC_, POL, MD, VEC>(rows, cols, vals, wlog, e0, e1, d.ell_rows, all_open, B, ldb, C, ldc, N, \
+                                        row_base, lane, s_off + g * 64, s_val + g * 64, s_rd + g * 64, ring, dests)
   switch (wlog) {
     case 0: LF_WALK(1); break;
     case 1: LF_WALK(2); break;
@@ -1025,6 +1030,18 @@ int cache_policy() {
 template <int MAXB>
 int launch_hyb_bf16(const SpmmTable<MAXB>& tbl, int64_t tiles, const lf_hyb* A, const uint16_t* B, int64_t ldb,
                     float* C, int64_t ldc, int N, FeatCfg cfg, cudaStream_t st, const DestList& dests, bool dep) {
+  // (with 16 lanes per row -- up to 128 features -- half of every warp of the ring kernel would idle:
+  // measured 0.61 ms against 0.49 ms for the register kernel on the power-law benchmark matrix)
+  if (gather_ring() > 0 && cfg.G == 32 && ldb < (1ll << 30) && dests.n == 0) {
+    // more than 128 bf16 features: full warps, one thread block along y per 256 features
+    dim3 rgrid((unsigned)tiles, (unsigned)((N + 255) / 256));
+    const size_t smem = (size_t)(kThreads / 32) * 16 * 32 * sizeof(float4);
+    auto kern = spmm_hyb_ring_kernel<16, MAXB, 1, 3, false, 8>;
+    LF_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    LF_CUDA_CHECK(launch_dep_smem(kern, rgrid, kThreads, smem, st, dep, tbl, A->rows, A->cols, A->vals, B, (int)ldb, C,
+                                  ldc, N, A->row_begin, dests));
+    return LF_OK;
+  }
   dim3 grid((unsigned)tiles, (unsigned)((N + cfg.pass - 1) / cfg.pass));
 #define LF_LAUNCH(G_, V_)                                                                                   \
   LF_CUDA_CHECK(launch_dep(spmm_hyb_kernel<G_, V_, 8, MAXB, 1, 3, false>, grid, kThreads, st, dep, tbl, A->rows, \
@@ -1078,7 +1095,7 @@ int launch_hyb(const SpmmTable<MAXB>& tbl, int64_t tiles, const lf_hyb* A, const
     const size_t smem = (size_t)(kThreads / 32) * ring * 32 * sizeof(float4);
 #define LF_RING(D_, P_, M_, MD_)                                                                                \
   do {                                                                                                          \
-    auto kern = spmm_hyb_ring_kernel<D_, MAXB, P_, M_, MD_>;                                                    \
+    auto kern = spmm_hyb_ring_kernel<D_, MAXB, P_, M_, MD_, 4>;                                                 \
     LF_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));          \
     LF_CUDA_CHECK(launch_dep_smem(kern, grid, kThreads, smem, st, dep, tbl, A->rows, A->cols, A->vals, B,       \
                                   (int)ldb, C, ldc, N, MD_ ? (int64_t)0 : A->row_begin, dests));                \
