@@ -995,10 +995,10 @@ TRAFFIC_BYTES_PER_LAUNCH = {
     ("powerlaw", "hyb", "f32", 128, 8, 1): (3314097664 + 1993026816, _NCU % "powerlaw --parts 8" + ", full size", "6db6834e0b6734a7"),
     ("uniform", "hyb", "f32", 64, 1, 1): (33723668480 + 1074183936, _NCU % "uniform" + ", full size", "6db6834e0b6734a7"),
     ("skew", "hyb", "f32", 256, 1, 1): (19904076800 + 1108611840, _NCU % "skew" + ", full size", "6db6834e0b6734a7"),
-    ("blocks", "bsr8", "f32", 128, 1, 1): (2 * (918055168 + 508351488), "ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum -c 2 on `bench.py --workload blocks --rows 1048576 --steps 2 --warmup 3 --no-cpu --no-e2e --no-build-timing`: "
-                                           "captured at 2^20 rows, doubled (traffic is proportional to the rows at a fixed band)", "36ec43bea9176c95"),
-    ("blocks", "bsr8", "bf16", 128, 1, 1): (2 * (484502016 + 493679872), "ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum -c 2 on `bench.py --workload blocks --dtype bf16 --rows 1048576 --steps 2 --warmup 3 --no-cpu --no-e2e --no-build-timing`: "
-                                            "captured at 2^20 rows, doubled (traffic is proportional to the rows at a fixed band)", "36ec43bea9176c95"),
+    ("blocks", "bsr8", "f32", 128, 1, 1): (2 * (931068672 + 508342528), "ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum -c 2 on `bench.py --workload blocks --rows 1048576 --steps 2 --warmup 3 --no-cpu --no-e2e --no-build-timing`: "
+                                           "captured at 2^20 rows, doubled (traffic is proportional to the rows at a fixed band)", "0805c80c8db254c0"),
+    ("blocks", "bsr8", "bf16", 128, 1, 1): (2 * (484701184 + 493565184), "ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum -c 2 on `bench.py --workload blocks --dtype bf16 --rows 1048576 --steps 2 --warmup 3 --no-cpu --no-e2e --no-build-timing`: "
+                                            "captured at 2^20 rows, doubled (traffic is proportional to the rows at a fixed band)", "0805c80c8db254c0"),
 }
 
 

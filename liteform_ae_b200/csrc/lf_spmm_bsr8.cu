@@ -57,8 +57,7 @@ constexpr int kDefaultCopyEngine = 1;
 template <int T, int D>
 struct F32Cfg {
   static constexpr int kRowBytes = 256 * T;
-  static constexpr int kStage = 8 * kRowBytes + 256;
-  static constexpr int kSmem = kWarps * D * kStage;
+  static constexpr int kStage = 8 * kRowBytes + 256;   // a thread block of W warps takes W * D stages
 };
 
 // A warp walks the blocks of R consecutive block rows as one stream, so the copy ring stays full
@@ -329,8 +328,7 @@ bsr8_spmm_f32_narrow_kernel(const int64_t* __restrict__ indptr, const int32_t* _
 template <int D>
 struct H16Cfg {
   static constexpr int kRowBytes = 256;
-  static constexpr int kStage = 16 * kRowBytes + 256;
-  static constexpr int kSmem = kWarps * D * kStage;
+  static constexpr int kStage = 16 * kRowBytes + 256;   // a thread block of W warps takes W * D stages
 };
 
 template <bool BF16, int D, int MINB>
