@@ -308,14 +308,14 @@ spmm_hyb_kernel(const __grid_constant__ SpmmTable<MAXB> tbl, const int32_t* __re
 // of the gathers from registers to shared memory: every lane owns D slots of 16 bytes, fills
 // them with cp.async up to D rows ahead of the row it is adding up, and reads back only bytes it
 // copied itself, so no lane ever waits for another one.  D = 16 at three thread blocks doubles
-// the rows in flight per SM; the wait for B disappears from the stall profile and the kernel
-// runs into the DRAM instead (91 % of the copy bandwidth on that matrix).  What it pays is a
-// second pass of every gathered byte through the load/store unit, so the inner loop is written
-// to issue as few shared-memory instructions as possible: (column, value) pairs are read two at a
-// time, the values stay in registers between the copy and the multiply, and ring slots are
-// compile-time constants.  A warp covers 128 features (one chunk of four per lane); wider feature
-// matrices use further thread blocks along y.  Rows are added up in the same order as in the
-// register kernel.
+// the rows in flight per SM; the wait for B leaves the stall profile and the kernel runs into the
+// DRAM instead (98 % of the copy bandwidth on that matrix).  What it pays is a second pass of
+// every gathered byte through the load/store unit, so the loop over the slots is written to issue
+// as few instructions as possible: what is the same for all lanes is computed once per slot while
+// a strip is staged, columns and values are read back four at a time, ring slots are compile-time
+// constants and the address of a row is one multiply-add.  A warp covers 128 float32 (256 bf16)
+// features, one 16-byte chunk per lane; wider feature matrices use further thread blocks along
+// y.  Rows are added up in the same order as in the register kernel.
 __device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
@@ -336,9 +336,9 @@ constexpr uint32_t kNoGather = 0xffffffffu;   // column of a slot that gathers n
 
 // Everything that is the same for all lanes of a warp is computed once per slot by ONE lane while
 // a strip of 32 slots is staged ("gathers nothing" folded into the column index, "an ELL row with
-// another row id starts here" as one bit of a warp vote), so that the
-// loop over the slots, which every lane executes for every slot, is left with one address
-// computation, one copy, one shared-memory load and the multiply-adds.
+// another row id starts here" as one bit of a warp vote), so that the loop over the slots, which
+// every lane executes for every slot, is left with one address computation, one copy, one
+// shared-memory load and the multiply-adds.
 // VEC = 4: B in float32, a lane owns 4 features; VEC = 8: B in bf16, a lane owns 8 features -- 16 bytes
 // per lane and row either way, so the ring is the same.
 template <int D, int WC, int POL, bool MD, int VEC>
