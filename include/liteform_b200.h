@@ -84,9 +84,11 @@ const char* lf_last_error(void);
                                           copies, 2 or 4 = that many warps issuing per-lane cp.async */
 #define LF_OPT_BSR_BLOCK_WARPS 11       /* copy engine 1, more than 64 features: warps per thread block, 1..8 (0 = automatic:
                                           4 for 16-bit inputs up to 128 features, else 8) */
-#define LF_OPT_SPMM_GATHER_RING 10      /* float32 product with 128-bit gathers and more than 64 features: where the
-                                          gathered rows of B land: 16 (default) a ring of 16 rows per warp in shared
-                                          memory, filled by cp.async; 0 registers (8 rows in flight per warp) */
+#define LF_OPT_SPMM_RING_MIN_SLOTS 12    /* products with up to 64 float32 / 128 bf16 features: stored slots from which the
+                                          ring form (two launches) replaces the register kernel (default 2^20) */
+#define LF_OPT_SPMM_GATHER_RING 10      /* products with 128-bit gathers: where the gathered rows of B land: 16 (default) a
+                                          ring of 16 rows (or steps of 2 / 4 narrow rows) per warp in shared memory,
+                                          filled by cp.async; 0 registers (8 rows in flight per warp) */
 #define LF_OPT_SPMM_TILE_SEGMENTS 6     /* order of the thread blocks of the composed-format product: 0 bucket after
                                           bucket (default); S > 0: every bucket is cut into S segments of consecutive
                                           rows and the launch runs segment 0 of all buckets, then segment 1, ... */

@@ -30,6 +30,7 @@ LF_OPT_BSR_PIPE_3D = 8
 LF_OPT_BSR_UMMA_PRODUCER = 9
 LF_OPT_SPMM_GATHER_RING = 10
 LF_OPT_BSR_BLOCK_WARPS = 11
+LF_OPT_SPMM_RING_MIN_SLOTS = 12
 LF_DTYPE_F32, LF_DTYPE_BF16, LF_DTYPE_F16 = 0, 1, 2
 LF_SPMM_OVERWRITE = 0
 LF_SPMM_ACCUMULATE = 1

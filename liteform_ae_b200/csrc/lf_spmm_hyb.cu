@@ -22,9 +22,10 @@
 //   * padded slots issue no gather.  Padding is recognised by its stored value 0 (the builder writes
 //     exact zeros there); a stored ENTRY whose value is exactly 0 is skipped the same way, so
 //     0 * Inf and 0 * NaN from B do not reach C (SciPy would produce NaN there);
-//   * float32 B with more than 64 features per row runs, by default, a second form of the same walk
-//     whose gathers land in a per-lane shared-memory ring (cp.async, 16 rows ahead) instead of
-//     registers: see spmm_hyb_ring_kernel;
+//   * by default the products with 128-bit gathers run a second form of the same walk whose gathers
+//     land in a per-lane shared-memory ring (cp.async, 16 rows ahead) instead of registers: see
+//     spmm_hyb_ring_kernel (rows of B that fill a warp) and spmm_hyb_ring_rows_kernel (rows of 8
+//     or 16 lanes, several slots per step);
 //   * variants of the same code: B in bf16 (8 features per lane), and a broadcasting epilogue that
 //     stores every row into several full-size C matrices (the GPUs of a group) at once.
 #include <type_traits>
@@ -525,6 +526,209 @@ spmm_hyb_ring_kernel(const __grid_constant__ SpmmTable<MAXB> tbl, const int32_t*
 #undef LF_WALK
 }
 
+// ---- the same ring for rows of B that fill half or a quarter of a warp ------------------------
+// Up to 64 float32 (128 bf16) features a row of B is 8 or 16 lanes wide.  A warp then takes R = 4 or
+// 2 consecutive slots per step: lanes [h * 32/R, (h+1) * 32/R) copy and multiply the row of slot
+// R * step + h, every lane keeps the partial sum of its own quarter / half, and a flush adds the R
+// partial sums with shuffles before the first 32/R lanes write the row.  All R slots of a step lie
+// in one ELL row (buckets at least R wide; narrower buckets go to the register kernel in a launch
+// of their own), so row changes stay the same for all lanes.  Columns and values of a strip are
+// staged per part (part h of a strip holds slots h, h + R, ...) so that a lane still reads the
+// next four of its own with one 128-bit load.
+__device__ __forceinline__ void chunk_add_from_lane_xor(Chunk<4>& a, int m) {
+  a.v.x += __shfl_xor_sync(0xffffffffu, a.v.x, m);
+  a.v.y += __shfl_xor_sync(0xffffffffu, a.v.y, m);
+  a.v.z += __shfl_xor_sync(0xffffffffu, a.v.z, m);
+  a.v.w += __shfl_xor_sync(0xffffffffu, a.v.w, m);
+}
+__device__ __forceinline__ void chunk_add_from_lane_xor(Chunk<8>& a, int m) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i) a.a[i] += __shfl_xor_sync(0xffffffffu, a.a[i], m);
+}
+
+template <int R, int VEC, int WCS, int POL>
+__device__ __forceinline__ void walk_slots_ring_rows(const int32_t* __restrict__ rows, const int32_t* __restrict__ cols,
+                                                     const float* __restrict__ vals, int wlog, int64_t e0, int64_t e1,
+                                                     int64_t ell_rows, bool all_open,
+                                                     const typename BTraits<VEC>::elem* __restrict__ B, int ldb,
+                                                     float* __restrict__ C, int64_t ldc, int N, int64_t row_base,
+                                                     int lane, uint32_t* so, float* sv, int* rd, float4* ring) {
+  constexpr int U = 8, D = 16;               // steps per commit group, steps in flight
+  constexpr int G = 32 / R;                  // lanes per row of B
+  constexpr int SPS = 32 / R;                // steps per strip of 32 slots
+  constexpr int NB = (D * R + 31) / 32 + 1;  // strips held in shared memory: the one being added up and those ahead
+  static_assert(R == 2 || R == 4, "two or four rows per step");
+  const int sub = lane / G, gl = lane % G;
+  const int first_row = rows[e0], last_row = rows[e1 - 1];
+  const bool head_open = e0 > 0 && rows[e0 - 1] == first_row;
+  const bool tail_open = e1 < ell_rows && rows[e1] == last_row;
+  const int f0 = blockIdx.y * (G * VEC) + gl * VEC;
+  const bool active = f0 < N;
+  Chunk<VEC> acc;
+  acc.zero();
+  int cur = first_row;
+
+  auto flush = [&](int row) {
+#pragma unroll
+    for (int m = 16; m >= G; m >>= 1) chunk_add_from_lane_xor(acc, m);   // sum over the R parts of the warp
+    const bool open = all_open || (row == first_row && head_open) || (row == last_row && tail_open);
+    if (active && sub == 0) {
+      float* dst = C + (int64_t)(row - row_base) * ldc + f0;
+      if (open) acc.red(dst);
+      else if (POL >= 1) acc.store_stream(dst);
+      else acc.store(dst);
+    }
+    acc.zero();
+  };
+
+  const typename BTraits<VEC>::elem* __restrict__ Bf = B + f0;
+  const int64_t s0 = e0 << wlog, s1 = e1 << wlog;
+  const int n = (int)(s1 - s0);
+  const int nsteps = n / R;                  // the bucket is at least R wide: whole steps
+  const int nstrips = (n + 31) >> 5;
+  int pc = 0, pr = 0;
+  float pv = 0.f;
+  auto load_strip = [&](int k) {
+    const int64_t idx = s0 + (int64_t)k * 32 + lane;
+    const bool in = idx < s1;
+    const int64_t cidx = in ? idx : s1 - 1;
+    pc = POL >= 1 ? __ldcs(cols + cidx) : cols[cidx];
+    pv = in ? (POL >= 1 ? __ldcs(vals + cidx) : vals[cidx]) : 0.f;
+    pr = rows[cidx >> wlog];
+  };
+  uint32_t chg0 = 0, chg1 = 0, chg2 = 0;   // per resident strip: bit i = slot i carries another row id than the slot before
+  int carry = first_row;
+  auto store_strip = [&](int k) {
+    const int hb = k % NB;
+    const int at = hb * 32 + (lane % R) * SPS + lane / R;   // part (slot % R), position slot / R
+    so[at] = pv != 0.f ? (uint32_t)pc : kNoGather;
+    sv[at] = pv;
+    rd[hb * 32 + lane] = pr;
+    int before = __shfl_up_sync(0xffffffffu, pr, 1);
+    if (lane == 0) before = carry;
+    const uint32_t m = __ballot_sync(0xffffffffu, pr != before);
+    carry = __shfl_sync(0xffffffffu, pr, 31);
+    if (hb == 0) chg0 = m; else if (hb == 1) chg1 = m; else chg2 = m;
+  };
+  load_strip(0);
+  store_strip(0);
+  __syncwarp();
+  if (nstrips > 1) load_strip(1);
+
+  const float4* ring_lane = ring + lane;
+  const uint32_t ring_s = (uint32_t)__cvta_generic_to_shared(ring_lane);
+  const uint32_t pitch = (uint32_t)ldb * (uint32_t)sizeof(typename BTraits<VEC>::elem);
+  const uint4* so4 = reinterpret_cast<const uint4*>(so);
+  const float4* sv4 = reinterpret_cast<const float4*>(sv);
+  // steps j0 .. j0+7 (j0 a multiple of 8) into ring slots SLOT .. SLOT+7, closed as one group
+  auto issue_batch = [&](int j0, auto slot_tag) {
+    constexpr int SLOT = decltype(slot_tag)::value;
+    if (j0 < nstrips * SPS) {
+      const int k = j0 / SPS, q0 = j0 % SPS;
+      if (q0 == 0 && j0 > 0) {   // first steps of strip k: its slots move from registers to shared memory
+        __syncwarp();
+        store_strip(k);
+        __syncwarp();
+        if (k + 1 < nstrips) load_strip(k + 1);
+      }
+      const int at = (k % NB) * 32 + sub * SPS + q0;
+      const uint4 oa = so4[at >> 2], ob = so4[(at >> 2) + 1];
+      const uint32_t o[U] = {oa.x, oa.y, oa.z, oa.w, ob.x, ob.y, ob.z, ob.w};
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if (o[u] != kNoGather && active) cp_async_16(ring_s + (uint32_t)(SLOT + u) * 512u, row_of_b(Bf, o[u], pitch));
+    }
+    cp_async_commit();
+  };
+  auto for_each_batch = [&](auto&& body) {
+    body(std::integral_constant<int, 0>{});
+    body(std::integral_constant<int, U>{});
+  };
+
+  for_each_batch([&](auto slot_tag) { issue_batch(decltype(slot_tag)::value, slot_tag); });
+  wait_for_prior_grid();   // no store or atomic to C before the row-clearing launch is complete
+  for (int jc0 = 0; jc0 < nsteps; jc0 += D) {
+    for_each_batch([&](auto slot_tag) {
+      constexpr int SLOT = decltype(slot_tag)::value;
+      const int jc = jc0 + SLOT;
+      if (jc >= nsteps) return;
+      const int k = jc / SPS, q0 = jc % SPS, hb = k % NB;
+      const int at = hb * 32 + sub * SPS + q0;
+      const float4 va = sv4[at >> 2], vb = sv4[(at >> 2) + 1];
+      const float val[U] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
+      const uint32_t starts = (hb == 0 ? chg0 : (hb == 1 ? chg1 : chg2)) >> (q0 * R);   // bit u*R: step jc+u starts another row
+      cp_async_wait<D / U - 1>();
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (u % WCS == 0 && ((starts >> (u * R)) & 1u)) {  // an ELL row can only start at a multiple of width / R steps
+          flush(cur);
+          cur = rd[hb * 32 + (q0 + u) * R];
+        }
+        if (val[u] != 0.f && active) {
+          typename BTraits<VEC>::raw x;
+          const float4 raw = ring_lane[(SLOT + u) * 32];
+          if constexpr (VEC == 8) x.v = make_uint4(__float_as_uint(raw.x), __float_as_uint(raw.y), __float_as_uint(raw.z), __float_as_uint(raw.w));
+          else x.v = raw;
+          chunk_fma(acc, val[u], x);
+        }
+      }
+      issue_batch(jc + D, slot_tag);
+    });
+  }
+  flush(cur);
+}
+
+template <int R, int VEC, int MAXB, int POL>
+__global__ void __launch_bounds__(kThreads, 3)
+spmm_hyb_ring_rows_kernel(const __grid_constant__ SpmmTable<MAXB> tbl, const int32_t* __restrict__ rows_arena,
+                          const int32_t* __restrict__ cols_arena, const float* __restrict__ vals_arena,
+                          const typename BTraits<VEC>::elem* __restrict__ B, int ldb, float* __restrict__ C,
+                          int64_t ldc, int N, int64_t row_base) {
+  constexpr int GPC = kThreads / 32;
+  constexpr int NB = (16 * R + 31) / 32 + 1;
+  constexpr int LR = R == 2 ? 1 : 2;
+  extern __shared__ __align__(16) unsigned char ring_bytes[];
+  __shared__ __align__(16) uint32_t s_off[GPC * NB * 32];
+  __shared__ __align__(16) float s_val[GPC * NB * 32];
+  __shared__ int s_rd[GPC * NB * 32];
+
+  int64_t tile = blockIdx.x;
+  int64_t key = tile;
+  uint32_t seg = 0;
+  if (tbl.seg_tiles > 0) {
+    seg = (uint32_t)blockIdx.x / (uint32_t)tbl.seg_tiles;
+    key = (uint32_t)blockIdx.x - seg * (uint32_t)tbl.seg_tiles;
+  }
+  int lo = 0, hi = tbl.n;
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (tbl.b[mid].tile_begin <= key) lo = mid; else hi = mid;
+  }
+  const BucketDesc& d = tbl.b[lo];
+  tile = tbl.seg_tiles > 0 ? (int64_t)seg * d.tiles_per_seg + (key - d.tile_begin) : key - d.tile_begin;
+  const int wlog = d.wlog;
+  const int g = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t e0 = (tile * GPC + g) * (int64_t)d.rows_per_group;
+  if (e0 >= d.ell_rows) return;
+  const int64_t e1 = min(e0 + d.rows_per_group, d.ell_rows);
+  const int32_t* __restrict__ rows = rows_arena + d.row_off;
+  const int32_t* __restrict__ cols = cols_arena + d.slot_off;
+  const float* __restrict__ vals = vals_arena + d.slot_off;
+  const bool all_open = d.force_atomic != 0;
+  float4* ring = reinterpret_cast<float4*>(ring_bytes) + (size_t)g * 16 * 32;
+#define LF_WALK(WCS_)                                                                                            \
+  walk_slots_ring_rows<R, VEC, WCS_, POL>(rows, cols, vals, wlog, e0, e1, d.ell_rows, all_open, B, ldb, C, ldc, N, \
+                                          row_base, lane, s_off + g * NB * 32, s_val + g * NB * 32,               \
+                                          s_rd + g * NB * 32, ring)
+  switch (wlog - LR) {   // width / R steps per ELL row
+    case 0: LF_WALK(1); break;
+    case 1: LF_WALK(2); break;
+    case 2: LF_WALK(4); break;
+    default: LF_WALK(8); break;
+  }
+#undef LF_WALK
+}
+
 // Rows that no single ELL row owns are cleared before the accumulating launch.
 template <int VEC>
 __global__ void __launch_bounds__(kThreads)
@@ -959,6 +1163,8 @@ FeatCfg pick_cfg_bf16(int N) {
 
 // Process-wide tuning knobs (lf_set_option); the environment gives the initial values.
 constexpr int kDefaultGatherRing = 16;
+// stored slots from which rows of B narrower than a warp take the two-launch ring path (LF_OPT_SPMM_RING_MIN_SLOTS)
+int g_ring_rows_min_slots = 1 << 20;
 int g_slots_per_group = 0;
 int g_cache_policy = -1;
 
@@ -1030,8 +1236,8 @@ int cache_policy() {
 template <int MAXB>
 int launch_hyb_bf16(const SpmmTable<MAXB>& tbl, int64_t tiles, const lf_hyb* A, const uint16_t* B, int64_t ldb,
                     float* C, int64_t ldc, int N, FeatCfg cfg, cudaStream_t st, const DestList& dests, bool dep) {
-  // (with 16 lanes per row -- up to 128 features -- half of every warp of the ring kernel would idle:
-  // measured 0.61 ms against 0.49 ms for the register kernel on the power-law benchmark matrix)
+  // (rows of 8 or 16 lanes -- up to 128 features -- reach spmm_hyb_ring_rows_kernel from the bucket
+  // loop of the caller; what arrives here with such rows is the register-kernel share)
   if (gather_ring() > 0 && cfg.G == 32 && ldb < (1ll << 30) && dests.n == 0) {
     // more than 128 bf16 features: full warps, one thread block along y per 256 features
     dim3 rgrid((unsigned)tiles, (unsigned)((N + 255) / 256));
@@ -1075,6 +1281,26 @@ int launch_hyb_pol(const SpmmTable<MAXB>& tbl, int64_t tiles, const lf_hyb* A, c
   }
 #undef LF_LAUNCH
   return LF_OK;
+}
+
+// Rows of B that are 8 or 16 lanes wide: the ring kernel that takes several slots per step.
+template <int MAXB>
+int launch_hyb_ring_rows(const SpmmTable<MAXB>& tbl, int64_t tiles, const lf_hyb* A, const void* B, bool bf16,
+                         int64_t ldb, float* C, int64_t ldc, int N, int lanes_per_row, cudaStream_t st, bool dep) {
+  const int vec = bf16 ? 8 : 4;
+  dim3 grid((unsigned)tiles, (unsigned)((N + lanes_per_row * vec - 1) / (lanes_per_row * vec)));
+  const size_t smem = (size_t)(kThreads / 32) * 16 * 32 * sizeof(float4);
+#define LF_ROWS(R_, VEC_, T_)                                                                                   \
+  do {                                                                                                          \
+    auto kern = spmm_hyb_ring_rows_kernel<R_, VEC_, MAXB, 1>;                                                   \
+    LF_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));          \
+    LF_CUDA_CHECK(launch_dep_smem(kern, grid, kThreads, smem, st, dep, tbl, A->rows, A->cols, A->vals,          \
+                                  (const T_*)B, (int)ldb, C, ldc, N, A->row_begin));                            \
+    return LF_OK;                                                                                               \
+  } while (0)
+  if (bf16) { if (lanes_per_row == 16) LF_ROWS(2, 8, uint16_t); else LF_ROWS(4, 8, uint16_t); }
+  else      { if (lanes_per_row == 16) LF_ROWS(2, 4, float); else LF_ROWS(4, 4, float); }
+#undef LF_ROWS
 }
 
 // The ring kernels exist for 128-bit gathers over full warps; they multiply the column by a 32-bit
@@ -1155,6 +1381,10 @@ int lf_set_option(int32_t option, int32_t value) {
       LF_REQUIRE(value == 0 || value == 16, "gather ring depth %d is not 0 or 16", value);
       g_gather_ring = value;
       return LF_OK;
+    case LF_OPT_SPMM_RING_MIN_SLOTS:
+      LF_REQUIRE(value >= 0, "slot threshold %d out of range", value);
+      g_ring_rows_min_slots = value;
+      return LF_OK;
     case LF_OPT_SPMM_TILE_SEGMENTS:
       LF_REQUIRE(value >= 0 && value <= 4096, "segment count %d out of range", value);
       g_tile_segments = value;
@@ -1203,6 +1433,9 @@ const char* lf_spmm_hyb_f32_kernel_name(const lf_hyb* A, const float* B, int64_t
                                         int32_t N) {
   if (!A || N < 1) return "";
   const FeatCfg cfg = pick_cfg(B, ldb, C, ldc, N);
+  if (gather_ring() > 0 && cfg.VEC == 4 && cfg.G < 32 && ldb < (1ll << 30) && cache_policy() == 1 &&
+      A->slot_off && A->slot_off[A->num_buckets] >= g_ring_rows_min_slots)
+    return "spmm_hyb_ring_rows_kernel";   // buckets narrower than 32 / lanes-per-row slots: spmm_hyb_kernel
   return gather_ring() > 0 && ring_applies(cfg, ldb) ? "spmm_hyb_ring_kernel" : "spmm_hyb_kernel";
 }
 
@@ -1277,64 +1510,83 @@ static int spmm_hyb_impl(const lf_hyb* A, const void* B, bool b_is_bf16, int64_t
     }
   }
 
-  // one launch per LF_MAX_BUCKETS_PER_LAUNCH non-empty buckets (one launch in every practical case)
-  const int gpc = kThreads / cfg.G;
-  int spg = slots_per_group();
-  if (!spg) {
-    const int64_t want_tiles = (int64_t)sm_count() * min_blocks() * 8;
-    for (spg = 256; spg > 32; spg >>= 1) {
-      int64_t t = 0;
-      for (int k = 0; k < A->num_buckets; ++k) {
-        const int w = A->widths[k];
-        const int rpg = spg / w > 0 ? spg / w : 1;
-        t += ceil_div64(A->ell_rows[k], (int64_t)rpg * gpc);
-      }
-      if (t >= want_tiles) break;
-    }
-  }
+  // Rows of B narrower than a warp (8 or 16 lanes): buckets at least as wide as the slots of a step
+  // go to the ring kernel that takes several slots per step, the narrower ones to the register
+  // kernel in a launch of their own.
+  // Small products stay with the one launch of the register kernel (a 16384-row matrix: 0.013 ms
+  // against 0.023 ms for the two launches).
+  const int rows_per_step = 32 / cfg.G;
+  const bool split = gather_ring() > 0 && cfg.VEC != 1 && rows_per_step > 1 && dests.n == 0 && ldb < (1ll << 30) &&
+                     cache_policy() == 1 && A->slot_off[A->num_buckets] >= g_ring_rows_min_slots;
   const int segs = tile_segments();
-  int i = 0;
-  while (i < A->num_buckets) {
-    static thread_local SpmmTable<LF_MAX_BUCKETS_PER_LAUNCH> big;
-    int n = 0;
-    int64_t tiles = 0, seg_tiles = 0;
-    for (; i < A->num_buckets && n < LF_MAX_BUCKETS_PER_LAUNCH; ++i) {
-      if (A->ell_rows[i] == 0) continue;
-      BucketDesc d;
-      int wlog = 0;
-      while ((1 << wlog) < A->widths[i]) ++wlog;
-      d.row_off = A->row_off[i];
-      d.slot_off = A->slot_off[i];
-      d.ell_rows = A->ell_rows[i];
-      d.wlog = wlog;
-      d.rows_per_group = (spg >> wlog) > 0 ? (spg >> wlog) : 1;
-      d.force_atomic = all_atomic ? 1 : 0;
-      const int64_t my_tiles = ceil_div64(d.ell_rows, (int64_t)d.rows_per_group * gpc);
-      const int64_t per_seg = segs > 0 ? ceil_div64(my_tiles, segs) : 0;
-      d.tile_begin = segs > 0 ? seg_tiles : tiles;
-      d.tiles_per_seg = (int32_t)per_seg;
-      tiles += my_tiles;
-      seg_tiles += per_seg;
-      big.b[n] = d;
-      ++n;
+  for (int pass = 0; pass < (split ? 2 : 1); ++pass) {
+    const bool ring_rows = split && pass == 0;
+    // one launch per LF_MAX_BUCKETS_PER_LAUNCH non-empty buckets (one launch in every practical case)
+    const int gpc = ring_rows ? kThreads / 32 : kThreads / cfg.G;
+    auto in_pass = [&](int k) {
+      if (A->ell_rows[k] == 0) return false;
+      if (!split) return true;
+      return (A->widths[k] >= rows_per_step) == ring_rows;
+    };
+    int spg = slots_per_group();
+    if (!spg) {
+      const int64_t want_tiles = (int64_t)sm_count() * min_blocks() * 8;
+      for (spg = 256; spg > 32; spg >>= 1) {
+        int64_t t = 0;
+        for (int k = 0; k < A->num_buckets; ++k) {
+          if (!in_pass(k)) continue;
+          const int w = A->widths[k];
+          const int rpg = spg / w > 0 ? spg / w : 1;
+          t += ceil_div64(A->ell_rows[k], (int64_t)rpg * gpc);
+        }
+        if (t >= want_tiles) break;
+      }
     }
-    if (n == 0) break;
-    const int64_t grid_tiles = segs > 0 ? seg_tiles * segs : tiles;   // interleaved: a few idle thread blocks at bucket ends
-    LF_REQUIRE(grid_tiles < (1ll << 31) && seg_tiles < (1ll << 31), "too many thread blocks for one launch");
-    int s;
-    if (n <= 16) {
-      SpmmTable<16> small;
-      small.n = n;
-      small.seg_tiles = (int32_t)(segs > 0 ? seg_tiles : 0);
-      for (int k = 0; k < n; ++k) small.b[k] = big.b[k];
-      s = launch_hyb<16>(small, grid_tiles, A, B, ldb, C, ldc, N, cfg, st, dests, cleared_by_kernel);
-    } else {
-      big.n = n;
-      big.seg_tiles = (int32_t)(segs > 0 ? seg_tiles : 0);
-      s = launch_hyb<LF_MAX_BUCKETS_PER_LAUNCH>(big, grid_tiles, A, B, ldb, C, ldc, N, cfg, st, dests, cleared_by_kernel);
+    int i = 0;
+    while (i < A->num_buckets) {
+      static thread_local SpmmTable<LF_MAX_BUCKETS_PER_LAUNCH> big;
+      int n = 0;
+      int64_t tiles = 0, seg_tiles = 0;
+      for (; i < A->num_buckets && n < LF_MAX_BUCKETS_PER_LAUNCH; ++i) {
+        if (!in_pass(i)) continue;
+        BucketDesc d;
+        int wlog = 0;
+        while ((1 << wlog) < A->widths[i]) ++wlog;
+        d.row_off = A->row_off[i];
+        d.slot_off = A->slot_off[i];
+        d.ell_rows = A->ell_rows[i];
+        d.wlog = wlog;
+        d.rows_per_group = (spg >> wlog) > 0 ? (spg >> wlog) : 1;
+        d.force_atomic = all_atomic ? 1 : 0;
+        const int64_t my_tiles = ceil_div64(d.ell_rows, (int64_t)d.rows_per_group * gpc);
+        const int64_t per_seg = segs > 0 ? ceil_div64(my_tiles, segs) : 0;
+        d.tile_begin = segs > 0 ? seg_tiles : tiles;
+        d.tiles_per_seg = (int32_t)per_seg;
+        tiles += my_tiles;
+        seg_tiles += per_seg;
+        big.b[n] = d;
+        ++n;
+      }
+      if (n == 0) break;
+      const int64_t grid_tiles = segs > 0 ? seg_tiles * segs : tiles;   // interleaved: a few idle thread blocks at bucket ends
+      LF_REQUIRE(grid_tiles < (1ll << 31) && seg_tiles < (1ll << 31), "too many thread blocks for one launch");
+      int s;
+      if (n <= 16) {
+        SpmmTable<16> small;
+        small.n = n;
+        small.seg_tiles = (int32_t)(segs > 0 ? seg_tiles : 0);
+        for (int k = 0; k < n; ++k) small.b[k] = big.b[k];
+        s = ring_rows ? launch_hyb_ring_rows<16>(small, grid_tiles, A, B, b_is_bf16, ldb, C, ldc, N, cfg.G, st, cleared_by_kernel)
+                      : launch_hyb<16>(small, grid_tiles, A, B, ldb, C, ldc, N, cfg, st, dests, cleared_by_kernel);
+      } else {
+        big.n = n;
+        big.seg_tiles = (int32_t)(segs > 0 ? seg_tiles : 0);
+        s = ring_rows ? launch_hyb_ring_rows<LF_MAX_BUCKETS_PER_LAUNCH>(big, grid_tiles, A, B, b_is_bf16, ldb, C, ldc, N, cfg.G, st, cleared_by_kernel)
+                      : launch_hyb<LF_MAX_BUCKETS_PER_LAUNCH>(big, grid_tiles, A, B, ldb, C, ldc, N, cfg, st, dests, cleared_by_kernel);
+      }
+      if (s) return s;
+      cleared_by_kernel = false;   // a further launch follows a product kernel, not the clearing one
     }
-    if (s) return s;
-    cleared_by_kernel = false;   // a further launch follows a product kernel, not the clearing one
   }
   return LF_OK;
 }

@@ -28,6 +28,7 @@ def restore_defaults():
     lib.lf_set_option(_cabi.LF_OPT_BSR_UMMA_PRODUCER, 0)
     lib.lf_set_option(_cabi.LF_OPT_SPMM_GATHER_RING, DEFAULT_GATHER_RING)
     lib.lf_set_option(_cabi.LF_OPT_BSR_BLOCK_WARPS, 0)
+    lib.lf_set_option(_cabi.LF_OPT_SPMM_RING_MIN_SLOTS, 1 << 20)
 
 
 def test_every_spmm_variant_gives_the_same_product(cuda_device, restore_defaults):
@@ -84,6 +85,40 @@ def test_gather_ring_adds_up_in_the_same_order_as_the_register_kernel(cuda_devic
                     short = np.diff(csr.indptr) <= 64     # one ELL row, one group, no atomics
                     assert np.array_equal(got[short], base.cpu().numpy()[short])
     assert lib.lf_set_option(_cabi.LF_OPT_SPMM_GATHER_RING, 8) == _cabi.LF_ERR_INVALID_ARGUMENT
+
+
+@pytest.mark.parametrize("parts", [1, 3])
+def test_gather_ring_with_rows_narrower_than_a_warp(cuda_device, restore_defaults, parts):
+    """Up to 64 float32 / 128 bf16 features a warp of the ring kernel takes 2 or 4 slots per step and adds
+    the partial sums at the flush; buckets narrower than that run the register kernel in a second launch."""
+    import torch
+    lib = _cabi.load()
+    assert lib.lf_set_option(_cabi.LF_OPT_SPMM_RING_MIN_SLOTS, 0) == 0    # small matrices take the ring form too
+    csr = synth.skewed_rows(M=6000, seed=8, heavy_rows=5, heavy_len=2500)
+    d = hyb.DeviceCsr.from_host(csr.indptr, csr.indices, csr.data, csr.shape, cuda_device)
+    for widths in ([[1, 2, 4, 8, 16, 64]], [[4, 32]], [[1]], [[2, 16]]) if parts == 1 else ([[1, 4, 32], [2, 8], [1, 2, 4, 8, 16]],):
+        fmt = hyb.build_hyb_device(d, widths, with_mask=False)
+        for N in (4, 20, 32, 48, 64):
+            B = synth.dense_features(csr.shape[1], N, 3)
+            Bd = torch.from_numpy(B).to(cuda_device)
+            want = ho.spmm_scipy_csr(csr.indptr, csr.indices, csr.data.astype(np.float64), csr.shape, B.astype(np.float64))
+            for slots, depth in itertools.product((0, 8, 40, 4096), (0, 16)):
+                assert lib.lf_set_option(_cabi.LF_OPT_SPMM_SLOTS_PER_GROUP, slots) == 0
+                assert lib.lf_set_option(_cabi.LF_OPT_SPMM_GATHER_RING, depth) == 0
+                C = torch.full((csr.shape[0], N), float("nan"), device=cuda_device)
+                hyb.spmm_hyb(fmt, Bd, out=C)
+                np.testing.assert_allclose(C.cpu().numpy(), want, rtol=1e-5, atol=1e-4, err_msg=f"{widths} {N} {slots} {depth}")
+                C.fill_(1.0)
+                hyb.spmm_hyb(fmt, Bd, out=C, accumulate=True)
+                np.testing.assert_allclose(C.cpu().numpy(), want + 1.0, rtol=1e-5, atol=2e-4, err_msg=f"acc {widths} {N} {slots} {depth}")
+        for N in (64, 128):      # bf16 features: 8 per lane
+            B = synth.dense_features(csr.shape[1], N, 4)
+            B16 = torch.from_numpy(B).to(cuda_device).to(torch.bfloat16)
+            want = ho.spmm_scipy_csr(csr.indptr, csr.indices, csr.data.astype(np.float64), csr.shape,
+                                     B16.float().cpu().numpy().astype(np.float64))
+            for depth in (0, 16):
+                assert lib.lf_set_option(_cabi.LF_OPT_SPMM_GATHER_RING, depth) == 0
+                np.testing.assert_allclose(hyb.spmm_hyb(fmt, B16).cpu().numpy(), want, rtol=1e-5, atol=1e-4)
 
 
 @pytest.mark.parametrize("N", [100, 128, 384])
