@@ -989,12 +989,12 @@ def run_ours(args, rank, local_rank, world):
 # captured on).  The figure is reported only while kernel_source_hash() still matches.
 _NCU = "ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum -c 2 on `bench.py --workload %s --steps 2 --warmup 3 --no-cpu --no-e2e`"
 TRAFFIC_BYTES_PER_LAUNCH = {
-    ("powerlaw", "hyb", "f32", 128, 1, 1): (3140182784 + 542889472, _NCU % "powerlaw" + ", full size", "c7b40a26202c7f61"),
-    ("powerlaw", "hyb", "f32", 128, 2, 1): (3421105152 + 971640064, _NCU % "powerlaw --parts 2" + ", full size", "c7b40a26202c7f61"),
-    ("powerlaw", "hyb", "f32", 128, 4, 1): (3234293760 + 1477067008, _NCU % "powerlaw --parts 4" + ", full size", "c7b40a26202c7f61"),
-    ("powerlaw", "hyb", "f32", 128, 8, 1): (3308547584 + 1991317504, _NCU % "powerlaw --parts 8" + ", full size", "c7b40a26202c7f61"),
-    ("uniform", "hyb", "f32", 64, 1, 1): (33724098560 + 1074065152, _NCU % "uniform" + ", full size", "c7b40a26202c7f61"),
-    ("skew", "hyb", "f32", 256, 1, 1): (19900675328 + 1108198912, _NCU % "skew" + ", full size", "c7b40a26202c7f61"),
+    ("powerlaw", "hyb", "f32", 128, 1, 1): (3139579392 + 542627840, _NCU % "powerlaw" + ", full size", "10e0a7d22469db01"),
+    ("powerlaw", "hyb", "f32", 128, 2, 1): (3419856384 + 971848960, _NCU % "powerlaw --parts 2" + ", full size", "10e0a7d22469db01"),
+    ("powerlaw", "hyb", "f32", 128, 4, 1): (3236526848 + 1477323520, _NCU % "powerlaw --parts 4" + ", full size", "10e0a7d22469db01"),
+    ("powerlaw", "hyb", "f32", 128, 8, 1): (3311143168 + 1991411456, _NCU % "powerlaw --parts 8" + ", full size", "10e0a7d22469db01"),
+    ("uniform", "hyb", "f32", 64, 1, 1): (32675725824 + 1073462016, _NCU % "uniform" + ", full size", "10e0a7d22469db01"),
+    ("skew", "hyb", "f32", 256, 1, 1): (19900642816 + 1108303360, _NCU % "skew" + ", full size", "10e0a7d22469db01"),
     ("blocks", "bsr8", "f32", 128, 1, 1): (2 * (931068672 + 508342528), "ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum -c 2 on `bench.py --workload blocks --rows 1048576 --steps 2 --warmup 3 --no-cpu --no-e2e --no-build-timing`: "
                                            "captured at 2^20 rows, doubled (traffic is proportional to the rows at a fixed band)", "0805c80c8db254c0"),
     ("blocks", "bsr8", "bf16", 128, 1, 1): (2 * (484701184 + 493565184), "ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum -c 2 on `bench.py --workload blocks --dtype bf16 --rows 1048576 --steps 2 --warmup 3 --no-cpu --no-e2e --no-build-timing`: "
