@@ -6,7 +6,7 @@ for the skewed matrix all 64 heavy rows -- against the float64 product of exactl
 float32: rel 1e-5 / abs 1e-4; bf16 inputs with fp32 accumulation: rel 1e-2 of the largest
 magnitude against the unrounded product, 1e-5 / 1e-4 against the product of the rounded inputs.
 Rows with more than 4096 stored entries (the 64 rows of 100 000 entries of the skewed matrix) get
-the absolute part scaled by sqrt(entries / 4096) -- oracle.hyb_oracle.fp32_product_tolerance says
+the absolute part scaled by entries / 4096 -- oracle.hyb_oracle.fp32_product_tolerance says
 why -- and the test also shows that SciPy's float32 product of those rows is no closer.
 """
 import numpy as np
