@@ -121,6 +121,34 @@ def test_gather_ring_with_rows_narrower_than_a_warp(cuda_device, restore_default
                 np.testing.assert_allclose(hyb.spmm_hyb(fmt, B16).cpu().numpy(), want, rtol=1e-5, atol=1e-4)
 
 
+@pytest.mark.parametrize("N", [32, 64, 128, 320])
+def test_ring_kernels_with_strided_operands(cuda_device, restore_defaults, N):
+    """B and C as column windows of wider matrices (leading dimensions larger than N, bases off the
+    row start): the ring kernels multiply the column by the row pitch and must leave the rest of C alone."""
+    import torch
+    lib = _cabi.load()
+    assert lib.lf_set_option(_cabi.LF_OPT_SPMM_RING_MIN_SLOTS, 0) == 0
+    csr = synth.skewed_rows(M=5000, seed=12, heavy_rows=3, heavy_len=1800)
+    d = hyb.DeviceCsr.from_host(csr.indptr, csr.indices, csr.data, csr.shape, cuda_device)
+    fmt = hyb.build_hyb_device(d, [[1, 2, 4, 8, 32]], with_mask=False)
+    B = synth.dense_features(csr.shape[1], N, 7)
+    want = ho.spmm_scipy_csr(csr.indptr, csr.indices, csr.data.astype(np.float64), csr.shape, B.astype(np.float64))
+    Bbig = torch.zeros((csr.shape[1], N + 40), device=cuda_device)
+    Bbig[:, 8:8 + N] = torch.from_numpy(B).to(cuda_device)
+    for depth in (0, 16):
+        assert lib.lf_set_option(_cabi.LF_OPT_SPMM_GATHER_RING, depth) == 0
+        Cbig = torch.full((csr.shape[0], N + 24), -1.0, device=cuda_device)
+        hyb.spmm_hyb(fmt, Bbig[:, 8:8 + N], out=Cbig[:, 4:4 + N])
+        got = Cbig.cpu().numpy()
+        np.testing.assert_allclose(got[:, 4:4 + N], want, rtol=1e-5, atol=1e-4)
+        assert (got[:, :4] == -1).all() and (got[:, 4 + N:] == -1).all()
+        C2 = torch.full((csr.shape[0], N + 24), -1.0, device=cuda_device)
+        hyb.spmm_csr(d, Bbig[:, 8:8 + N], out=C2[:, 4:4 + N])
+        got = C2.cpu().numpy()
+        np.testing.assert_allclose(got[:, 4:4 + N], want, rtol=1e-5, atol=1e-4)
+        assert (got[:, :4] == -1).all() and (got[:, 4 + N:] == -1).all()
+
+
 @pytest.mark.parametrize("N", [100, 128, 384])
 def test_csr_product_with_and_without_the_gather_ring(cuda_device, restore_defaults, N):
     """lf_spmm_csr_f32 has the same two forms; rows that one thread group owns are bit-identical."""
